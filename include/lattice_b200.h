@@ -1,0 +1,312 @@
+/*
+ * lattice_b200 -- C ABI of the sm_100a sparse-convolution inference path.
+ *
+ * Every entry point replaces one function of the reference project's native
+ * extension (`mlx_lattice._ext`, built from native/bindings) for the hot path
+ * coordinate hash -> kernel map -> sparse-conv contraction -> sparse pooling.
+ * The citation on each declaration names the reference interface it stands in
+ * for (paths relative to the reference checkout).
+ *
+ * Conventions
+ *  - All array arguments are DEVICE pointers on the current CUDA device unless a
+ *    parameter name ends in `_host`. Arrays are dense row-major.
+ *  - Static capacities + device-side counts, exactly like the reference: outputs
+ *    are sized by the worst case, `counts[2] = {edge_count, out_count}` and
+ *    `active_rows[1]` live on the device, and no call reads them back. Nothing
+ *    here synchronises the stream, so calls can be captured into a CUDA graph.
+ *  - `stream` is a `cudaStream_t` passed as `void*` (NULL = default stream).
+ *  - Scratch memory is caller-provided: ask `lat_*_workspace_bytes`, pass a
+ *    256-byte-aligned device buffer of at least that size. The library never
+ *    allocates device memory in these calls.
+ *  - Return value: LAT_OK or an error code; `lat_last_error()` returns the
+ *    message of the last failing call on the calling thread (the reference
+ *    throws std::invalid_argument / std::runtime_error with the same texts).
+ *  - Device-side problems that can only be seen while a kernel runs (hash table
+ *    full, more edges than capacity, a wait that gave up) never trap: the kernel
+ *    records a bit in the caller's `status` word (device int32, may be NULL) and
+ *    returns. Read it back after synchronising.
+ */
+#ifndef LATTICE_B200_H
+#define LATTICE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct lat_triple {
+    int32_t x, y, z;
+} lat_triple;
+
+enum {
+    LAT_OK = 0,
+    LAT_INVALID_ARGUMENT = 1, /* contract violation (reference: std::invalid_argument) */
+    LAT_CUDA_ERROR = 2,       /* a CUDA runtime call or launch failed */
+    LAT_UNSUPPORTED = 3,      /* no sm_100 device (reference: std::runtime_error) */
+    LAT_WORKSPACE_TOO_SMALL = 4,
+};
+
+/* bits of the device status word */
+enum {
+    LAT_STATUS_HASH_FULL = 1,      /* probe sequence exhausted the table */
+    LAT_STATUS_EDGE_OVERFLOW = 2,  /* more edges/rows than the output capacity */
+    LAT_STATUS_BAD_INDEX = 4,      /* row id or kernel id outside its range */
+    LAT_STATUS_WAIT_TIMEOUT = 8,   /* a bounded in-kernel wait gave up */
+    LAT_STATUS_DUPLICATE_INPUT = 16 /* overlapping transposed map met duplicate input coords */
+};
+
+enum { LAT_F32 = 0, LAT_F16 = 1 };
+enum { LAT_REDUCE_SUM = 0, LAT_REDUCE_MAX = 1, LAT_REDUCE_AVG = 2 };
+enum { LAT_WEIGHT_KERNEL_MAJOR = 0, LAT_WEIGHT_DENSE_5D = 1 };
+enum { LAT_JOIN_INNER = 0, LAT_JOIN_LEFT = 1, LAT_JOIN_RIGHT = 2, LAT_JOIN_OUTER = 3 };
+
+/* native/bindings/runtime.cpp:27-38 (`version`, `capabilities`). */
+const char* lat_version(void);
+int lat_capabilities(int32_t* has_sm100, int32_t* device_count);
+const char* lat_last_error(void);
+
+/* native/features/coordinates/offsets.cpp:11-45 (`kernel_offsets`): host helper,
+ * writes kernel_volume x 3 int32 to a HOST buffer, x-major / z-fastest. */
+int lat_kernel_offsets_host(lat_triple kernel_size, lat_triple dilation, int32_t* offsets_host);
+
+/* ---- kernel maps -------------------------------------------------------- */
+
+/* Scratch for any relation builder below. `rows` = source capacity,
+ * `out_rows` = output-row capacity of the map (rows for forward/submanifold,
+ * target rows for target maps, rows*K for transposed/generative). */
+size_t lat_relation_workspace_bytes(int32_t rows, int32_t out_rows, int32_t kernel_count);
+
+/* native/bindings/coords.cpp:414-479 (`build_kernel_relation`) ->
+ * make_kernel_relation, native/features/coordinates/relations.cpp:540-581;
+ * algorithm native/features/coordinates/cpu/relation_build_detail.h:3-41.
+ * Output capacities: in_rows/out_rows/kernel_ids [rows*K], row_offsets [rows+1],
+ * out_coords [rows,4], counts [2]. Optional (may be NULL): row_masks
+ * [rows, ceil(K/32)] (bit k of an output row's mask = offset k present),
+ * kernel_row_offsets [K+1] + kernel_edge_ids [rows*K] (the per-offset pair lists
+ * of relations.cpp:461-476 built in the same pass). */
+int lat_build_kernel_relation(
+    const int32_t* coords, int32_t rows, const int32_t* active_rows,
+    lat_triple kernel_size, lat_triple stride, lat_triple padding, lat_triple dilation,
+    int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
+    int32_t* out_coords, int32_t* counts,
+    int32_t* row_masks, int32_t* kernel_row_offsets, int32_t* kernel_edge_ids,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* native/bindings/coords.cpp:480-508 (`build_submanifold_kernel_relation`) ->
+ * relations.cpp:583-597: the forward map with stride 1 and padding 0; outputs are
+ * the input rows themselves (out_coords is a copy of the active input rows). */
+int lat_build_submanifold_kernel_relation(
+    const int32_t* coords, int32_t rows, const int32_t* active_rows,
+    lat_triple kernel_size, lat_triple dilation,
+    int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
+    int32_t* out_coords, int32_t* counts,
+    int32_t* row_masks, int32_t* kernel_row_offsets, int32_t* kernel_edge_ids,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* native/bindings/coords.cpp:546-589 (`build_target_kernel_relation`) ->
+ * relations.cpp:672-722; algorithm cpu/relation_build_detail.h:43-80.
+ * Edge arrays [target_rows*K], row_offsets [target_rows+1]; counts =
+ * {E, target_active}. The caller's target coords are the relation's out coords. */
+int lat_build_target_kernel_relation(
+    const int32_t* coords, int32_t rows, const int32_t* active_rows,
+    const int32_t* target_coords, int32_t target_rows, const int32_t* target_active_rows,
+    lat_triple kernel_size, lat_triple stride, lat_triple padding, lat_triple dilation,
+    int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
+    int32_t* counts,
+    int32_t* row_masks, int32_t* kernel_row_offsets, int32_t* kernel_edge_ids,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* native/bindings/coords.cpp:509-545 (`build_transposed_kernel_relation`) ->
+ * relations.cpp:632-670; algorithm cpu/relation_build_detail.h:122-196. All edge
+ * and output arrays have capacity rows*K (row_offsets rows*K+1, out_coords
+ * [rows*K,4]). Uses the closed form when stride exceeds the offset extent on
+ * every axis (relations.cpp:107-126), else the deduplicating form. */
+int lat_build_transposed_kernel_relation(
+    const int32_t* coords, int32_t rows, const int32_t* active_rows,
+    lat_triple kernel_size, lat_triple stride, lat_triple padding, lat_triple dilation,
+    int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
+    int32_t* out_coords, int32_t* counts,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* native/bindings/coords.cpp (`build_generative_relation`) ->
+ * relations.cpp:599-630; algorithm cpu/relation_build_detail.h:82-120. */
+int lat_build_generative_relation(
+    const int32_t* coords, int32_t rows, const int32_t* active_rows,
+    lat_triple kernel_size, lat_triple stride,
+    int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
+    int32_t* out_coords, int32_t* counts,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* A superset entry (no reference counterpart as one call): the transposed map of
+ * a k = stride conv restricted to a caller-given fine support. For target row t:
+ * in = first_row(floor(t / stride)), kernel id from t - stride*floor(t/stride).
+ * It equals the reference composition conv_transpose3d (mlx_lattice/ops/conv.py:
+ * 153-182) followed by sparse_cat_aligned(join='right') (mlx_lattice/ops/
+ * tensor.py:228-249) and is what `coordinates=` on the transposed op maps to.
+ * Requires kernel_size == stride, padding 0, dilation 1. Capacities as for the
+ * target map with K = 1 edge per target row at most: edge arrays [target_rows]. */
+int lat_build_target_transposed_relation(
+    const int32_t* coords, int32_t rows, const int32_t* active_rows,
+    const int32_t* target_coords, int32_t target_rows, const int32_t* target_active_rows,
+    lat_triple stride,
+    int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
+    int32_t* counts,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* relations.cpp:438-459 (`make_relation_grouped_view`), algorithm
+ * cpu/relation_views_detail.h:84-120: CSR of edge ids by group id, ascending edge
+ * id inside a group, -1 fill. row_offsets [group_count+1], edge_ids [edge_capacity]. */
+size_t lat_grouped_view_workspace_bytes(int32_t edge_capacity, int32_t group_count);
+int lat_build_relation_grouped_view(
+    const int32_t* group_ids, int32_t edge_capacity, const int32_t* counts, int32_t group_count,
+    int32_t* row_offsets, int32_t* edge_ids,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* native/bindings/coords.cpp:590-627 (`build_relation_implicit_gemm_view`) ->
+ * relations.cpp:498-538; algorithm cpu/relation_views_detail.h:122-169.
+ * out_in_map [output_rows, K] (-1 = empty), row_masks [output_rows, ceil(K/32)].
+ * `offsets` is a DEVICE array [K,3]. */
+size_t lat_implicit_gemm_view_workspace_bytes(int32_t source_rows);
+int lat_build_relation_implicit_gemm_view(
+    const int32_t* source_coords, int32_t source_rows, const int32_t* source_active_rows,
+    const int32_t* output_coords, int32_t output_rows, const int32_t* output_active_rows,
+    const int32_t* offsets, int32_t kernel_count, lat_triple stride, lat_triple padding,
+    int32_t* out_in_map, int32_t* row_masks,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* ---- coordinate sets ---------------------------------------------------- */
+
+/* native/bindings/coords.cpp:132-160 (`downsample_coords`): unique
+ * floor(coord/stride) rows in first-seen order; out_coords [rows,4], count [1]. */
+size_t lat_coord_set_workspace_bytes(int32_t rows);
+int lat_downsample_coords(
+    const int32_t* coords, int32_t rows, lat_triple stride,
+    int32_t* out_coords, int32_t* count,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* native/bindings/coords.cpp:176-190 (`lookup_coords`): first row of each query
+ * coordinate among ALL `rows` source rows, -1 when absent. out_rows [query_rows]. */
+int lat_lookup_coords(
+    const int32_t* coords, int32_t rows, const int32_t* queries, int32_t query_rows,
+    int32_t* out_rows,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* native/bindings/coords.cpp:191-222 (`build_sparse_alignment`) ->
+ * native/features/coordinates/lookup.cpp:111-146; algorithm
+ * cpu/set_neighbors_detail.h:59-136. Output capacity: lhs_rows (inner, left),
+ * rhs_rows (right), lhs_rows + rhs_rows (outer). */
+size_t lat_sparse_alignment_workspace_bytes(int32_t lhs_rows, int32_t rhs_rows);
+int lat_build_sparse_alignment(
+    const int32_t* lhs_coords, int32_t lhs_rows, const int32_t* lhs_active_rows,
+    const int32_t* rhs_coords, int32_t rhs_rows, const int32_t* rhs_active_rows,
+    int32_t join,
+    int32_t* out_coords, int32_t* out_count, int32_t* out_lhs_rows, int32_t* out_rhs_rows,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* ---- feature contraction ------------------------------------------------ */
+
+/* native/bindings/convolution.cpp:90-146 (`sparse_conv_features`) ->
+ * native/features/convolution/api.cpp:119-246; arithmetic
+ * native/features/convolution/cpu/algorithms.cpp:180-302.
+ * feats [in_capacity, in_channels] with row stride `feat_row_stride` (elements),
+ * weights either (K, C_in, C_out) or (C_out, Kx, Ky, Kz, C_in) contiguous, out
+ * [out_capacity, out_channels]; rows >= counts[1] are zero. dtype LAT_F32 or
+ * LAT_F16 for feats, weights and out alike; accumulation is float32. The
+ * grouped-view arguments of the reference call are not read by the forward pass
+ * and are therefore not part of this signature. Optional `bias` [out_channels]
+ * (feature dtype) is added after the final cast (mlx_lattice/ops/conv.py:460-469),
+ * optional `row_order` [out_capacity] is a permutation of output rows that the
+ * tensor-core route uses to form its 128-row tiles (any permutation is valid). */
+size_t lat_sparse_conv_workspace_bytes(int32_t n_kernels, int32_t in_channels, int32_t out_channels);
+int lat_sparse_conv_features(
+    int32_t dtype, const void* feats, int32_t in_capacity, int32_t in_channels,
+    int64_t feat_row_stride,
+    const void* weights, int32_t weight_layout, lat_triple kernel_shape, int32_t out_channels,
+    const int32_t* in_rows, const int32_t* out_rows, const int32_t* kernel_ids,
+    int32_t edge_capacity, const int32_t* counts, const int32_t* row_offsets,
+    int32_t out_capacity, int32_t n_kernels,
+    const void* bias, const int32_t* row_order, void* out,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* native/bindings/convolution.cpp:12-89 (`sparse_quantized_conv_features`) ->
+ * native/features/convolution/quantized.cpp:198-268; arithmetic
+ * native/features/convolution/cpu/quantized.cpp:54-140. packed (K, S*bits/32,
+ * C_out) uint32, scales/biases (K, S/group, C_out) in the feature dtype, S =
+ * storage_in_channels; w = code*scale + bias, float32 accumulation, one cast.
+ * The three sorted-plan arrays of the reference call may be empty there and are
+ * replaced here by the optional `row_order`. `bias`/`row_order` as above. */
+int lat_sparse_quantized_conv_features(
+    int32_t dtype, const void* feats, int32_t in_capacity, int64_t feat_row_stride,
+    const uint32_t* packed, const void* scales, const void* biases,
+    const int32_t* in_rows, const int32_t* out_rows, const int32_t* kernel_ids,
+    int32_t edge_capacity, const int32_t* counts, const int32_t* row_offsets,
+    int32_t out_capacity, int32_t n_kernels, int32_t in_channels, int32_t out_channels,
+    int32_t storage_in_channels, int32_t group_size, int32_t bits,
+    const void* bias, const int32_t* row_order, void* out,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* 1 when the tensor-core (tcgen05) route serves this shape, 0 when the CUDA-core
+ * route does. Informational; both routes give results inside the tolerance. */
+int lat_conv_uses_tensor_cores(int32_t dtype, int32_t n_kernels, int32_t in_channels,
+                               int32_t out_channels, int32_t quantized_bits, int32_t group_size);
+
+/* Row permutation that groups output rows with equal offset masks (the idea of
+ * the sorted view, mlx_lattice/core/relations/views.py:467-510, as a native
+ * product). row_masks [rows, 1] (K <= 32). row_order [rows]. */
+size_t lat_mask_order_workspace_bytes(int32_t rows);
+int lat_build_mask_row_order(
+    const int32_t* row_masks, int32_t rows, const int32_t* counts, int32_t* row_order,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* ---- pooling and pointwise feature ops ---------------------------------- */
+
+/* native/bindings/pooling.cpp:17-72 (`sparse_pool_features`) ->
+ * native/features/pooling/api.cpp:8-38; arithmetic
+ * native/features/pooling/cpu/algorithms.cpp:181-244. float32 only, like the
+ * reference. Rows >= counts[1] hold the identity (0, or -inf for max). */
+int lat_sparse_pool_features(
+    const float* feats, int32_t in_capacity, int32_t channels, int64_t feat_row_stride,
+    const int32_t* in_rows, const int32_t* out_rows, const int32_t* kernel_ids,
+    int32_t edge_capacity, const int32_t* row_offsets, const int32_t* counts,
+    int32_t input_exclusive, int32_t reduce, int32_t out_capacity, int32_t n_kernels,
+    float* out, int32_t* status, void* stream);
+
+/* mlx_lattice/ops/pool.py:197-236 (`global_sum_pool` / `global_avg_pool` /
+ * `global_max_pool`): per-batch reduction over contiguous row ranges given by
+ * `batch_offsets` (DEVICE int32 [batches+1], prefix sums of batch_counts).
+ * feats float32 [rows, channels]; out float32 [batches, channels]. */
+int lat_global_pool(
+    const float* feats, int32_t rows, int32_t channels, const int32_t* batch_offsets,
+    int32_t batches, int32_t reduce, float* out, void* stream);
+
+/* mlx_lattice/ops/feature.py:33-51 (`linear`, x @ W.T + b) and the pointwise
+ * branch of conv3d (mlx_lattice/ops/conv.py:79-82,347-355). weight (C_out, C_in). */
+int lat_linear(
+    int32_t dtype, const void* feats, int32_t rows, int32_t in_channels,
+    const void* weight, int32_t out_channels, const void* bias, void* out, void* stream);
+
+/* mlx_lattice/ops/_quantized.py:8-38 (`quantized_matmul`, transpose=True): packed
+ * (C_out, S*bits/32) uint32, scales/biases (C_out, S/group). */
+int lat_quantized_linear(
+    int32_t dtype, const void* feats, int32_t rows, int32_t in_channels,
+    const uint32_t* packed, const void* scales, const void* biases,
+    int32_t out_channels, int32_t storage_in_channels, int32_t group_size, int32_t bits,
+    const void* bias, void* out, void* stream);
+
+/* mlx_lattice/ops/feature.py:166-187 (`batch_norm` with running statistics) with
+ * an optional fused ReLU (`relu`, feature.py:54-56). Any of weight/bias/mean/var
+ * may be NULL. Evaluated in float32, cast once. */
+int lat_batch_norm_relu(
+    int32_t dtype, const void* feats, int64_t elements_rows, int32_t channels,
+    const void* weight, const void* bias, const void* mean, const void* var, float eps,
+    int32_t apply_relu, void* out, void* stream);
+
+/* feature.py:54-56 (`relu`). */
+int lat_relu(int32_t dtype, const void* feats, int64_t elements, void* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LATTICE_B200_H */

@@ -1,0 +1,721 @@
+"""Drop-in for the reference's native extension module ``mlx_lattice._ext``.
+
+Same function names, argument order and return tuples as ``native/bindings``
+(``coords.cpp``, ``convolution.cpp``, ``pooling.cpp``, ``runtime.cpp``), with CUDA
+``torch.Tensor`` in place of ``mx.array``. Torch only owns the device memory and
+names the stream; every computation happens in ``liblattice_b200.so`` through its C
+ABI. Nothing here synchronises the stream or reads device counts back, so a
+sequence of calls can be captured into a CUDA graph.
+"""
+
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+
+from mlx_lattice_b200 import _native
+from mlx_lattice_b200._native import Triple, check
+
+_REDUCE = {'sum': 0, 'max': 1, 'avg': 2}
+_JOIN = {'inner': 0, 'left': 1, 'right': 2, 'outer': 3}
+
+_status_words: dict[int, torch.Tensor] = {}
+
+
+# --------------------------------------------------------------------------- #
+# plumbing
+# --------------------------------------------------------------------------- #
+
+
+def _lib():
+    return _native.load()
+
+
+def _require_cuda(tensor: torch.Tensor, name: str) -> None:
+    if not isinstance(tensor, torch.Tensor):
+        raise ValueError(f'{name} must be a torch.Tensor.')
+    if not tensor.is_cuda:
+        raise RuntimeError(
+            f'{name} must live on a CUDA device: this build has no CPU route.'
+        )
+
+
+def _ptr(tensor: torch.Tensor | None):
+    if tensor is None or tensor.numel() == 0:
+        return None
+    return tensor.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _triple(values: int | Sequence[int]) -> Triple:
+    if isinstance(values, int):
+        values = (values, values, values)
+    x, y, z = (int(v) for v in values)
+    return Triple(x, y, z)
+
+
+def status_word(device: torch.device | None = None) -> torch.Tensor:
+    """Per-device int32 word in which kernels record run-time problems."""
+    index = torch.cuda.current_device() if device is None or device.index is None else device.index
+    word = _status_words.get(index)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=torch.device('cuda', index))
+        _status_words[index] = word
+    return word
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Synchronise and raise if any kernel recorded a problem since the last check."""
+    word = status_word(device)
+    value = int(word.item())
+    if value != 0:
+        word.zero_()
+        reasons = [text for bit, text in _native.STATUS_BITS.items() if value & bit]
+        raise RuntimeError('lattice_b200 device status: ' + '; '.join(reasons))
+
+
+def _workspace(nbytes: int, device: torch.device) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def _coords_arg(coords: torch.Tensor, name: str = 'coords') -> torch.Tensor:
+    _require_cuda(coords, name)
+    if coords.ndim != 2 or coords.shape[1] != 4:
+        raise ValueError('coords must have shape (N, 4).')
+    if coords.dtype != torch.int32:
+        raise ValueError('CUDA sparse kernels require int32 coordinates.')
+    return coords.contiguous()
+
+
+def _active_arg(active_rows: torch.Tensor) -> torch.Tensor:
+    _require_cuda(active_rows, 'active_rows')
+    if tuple(active_rows.shape) != (1,) or active_rows.dtype != torch.int32:
+        raise ValueError('active_rows must have shape (1,) and int32 dtype.')
+    return active_rows
+
+
+def _i32(tensor: torch.Tensor, name: str) -> torch.Tensor:
+    _require_cuda(tensor, name)
+    if tensor.dtype != torch.int32:
+        raise ValueError(f'{name} must be int32.')
+    return tensor.contiguous()
+
+
+def _dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return 0
+    if dtype == torch.float16:
+        return 1
+    raise ValueError('convolution supports float32 and float16 tensors.')
+
+
+def _feats_arg(feats: torch.Tensor) -> tuple[torch.Tensor, int]:
+    _require_cuda(feats, 'feats')
+    if feats.ndim != 2:
+        raise ValueError('feats must have shape (N, C).')
+    if feats.stride(1) != 1:
+        feats = feats.contiguous()
+    return feats, int(feats.stride(0)) if feats.shape[0] > 1 else int(feats.shape[1])
+
+
+# --------------------------------------------------------------------------- #
+# runtime (native/bindings/runtime.cpp:27-38)
+# --------------------------------------------------------------------------- #
+
+
+def version() -> str:
+    return _lib().lat_version().decode()
+
+
+def capabilities() -> dict[str, bool]:
+    import ctypes
+
+    has = ctypes.c_int32(0)
+    count = ctypes.c_int32(0)
+    check(_lib().lat_capabilities(ctypes.byref(has), ctypes.byref(count)))
+    return {'cpu': False, 'metal': False, 'cuda': bool(has.value)}
+
+
+def kernel_offsets(kernel_size, dilation=1) -> tuple[tuple[int, int, int], ...]:
+    import ctypes
+
+    ks, dil = _triple(kernel_size), _triple(dilation)
+    volume = max(ks.x, 0) * max(ks.y, 0) * max(ks.z, 0)
+    buffer = (ctypes.c_int32 * max(3 * volume, 3))()
+    check(_lib().lat_kernel_offsets_host(ks, dil, ctypes.cast(buffer, ctypes.c_void_p)))
+    return tuple(
+        (buffer[3 * k], buffer[3 * k + 1], buffer[3 * k + 2]) for k in range(volume)
+    )
+
+
+# --------------------------------------------------------------------------- #
+# kernel relations (native/bindings/coords.cpp:414-589)
+# --------------------------------------------------------------------------- #
+
+
+def _relation_buffers(edge_capacity: int, out_capacity: int, device, with_out_coords=True):
+    def new(n):
+        return torch.empty(n, dtype=torch.int32, device=device)
+
+    return (
+        new(edge_capacity),
+        new(edge_capacity),
+        new(edge_capacity),
+        new(out_capacity + 1),
+        torch.empty((out_capacity, 4), dtype=torch.int32, device=device)
+        if with_out_coords
+        else None,
+        new(2),
+    )
+
+
+def _views(in_rows, kernel_ids, counts, in_capacity: int, kernel_count: int):
+    in_offsets, in_edges = build_relation_grouped_view(in_rows, counts, in_capacity)
+    k_offsets, k_edges = build_relation_grouped_view(kernel_ids, counts, kernel_count)
+    return in_offsets, in_edges, k_offsets, k_edges
+
+
+def build_kernel_relation_base(
+    coords, active_rows, kernel_size, stride, padding, dilation, *,
+    want_masks=False, want_kernel_lists=False,
+):
+    """The six contract arrays of a forward relation plus, on request, the row
+    masks and the per-offset pair lists produced in the same pass."""
+    coords = _coords_arg(coords)
+    active_rows = _active_arg(active_rows)
+    ks = _triple(kernel_size)
+    rows = int(coords.shape[0])
+    volume = ks.x * ks.y * ks.z
+    if min(ks.x, ks.y, ks.z) <= 0:
+        raise ValueError('kernel_size values must be positive.')
+    device = coords.device
+    in_rows, out_rows, kernel_ids, row_offsets, out_coords, counts = _relation_buffers(
+        rows * volume, rows, device
+    )
+    words = (volume + 31) // 32
+    masks = torch.empty((rows, words), dtype=torch.int32, device=device) if want_masks else None
+    k_offsets = torch.empty(volume + 1, dtype=torch.int32, device=device) if want_kernel_lists else None
+    k_edges = torch.empty(rows * volume, dtype=torch.int32, device=device) if want_kernel_lists else None
+    lib = _lib()
+    nbytes = lib.lat_relation_workspace_bytes(rows, rows, volume)
+    ws = _workspace(nbytes, device)
+    with torch.cuda.device(device):
+        check(lib.lat_build_kernel_relation(
+            _ptr(coords), rows, _ptr(active_rows), ks, _triple(stride), _triple(padding),
+            _triple(dilation), _ptr(in_rows), _ptr(out_rows), _ptr(kernel_ids),
+            _ptr(row_offsets), _ptr(out_coords), _ptr(counts), _ptr(masks), _ptr(k_offsets),
+            _ptr(k_edges), _ptr(ws), ws.numel(), _ptr(status_word(device)), _stream(),
+        ))
+    return (in_rows, out_rows, kernel_ids, row_offsets, out_coords, counts), masks, (k_offsets, k_edges)
+
+
+def build_kernel_relation(coords, active_rows, kernel_size, stride, padding, dilation):
+    """``_ext.build_kernel_relation`` (``native/bindings/coords.cpp:414-479``):
+    returns the 10-tuple (in_rows, out_rows, kernel_ids, output_row_offsets,
+    out_coords, counts, in_row_offsets, in_edge_ids, kernel_row_offsets,
+    kernel_edge_ids)."""
+    base, _, (k_offsets, k_edges) = build_kernel_relation_base(
+        coords, active_rows, kernel_size, stride, padding, dilation, want_kernel_lists=True
+    )
+    in_rows, out_rows, kernel_ids, row_offsets, out_coords, counts = base
+    in_offsets, in_edges = build_relation_grouped_view(in_rows, counts, int(coords.shape[0]))
+    return (*base, in_offsets, in_edges, k_offsets, k_edges)
+
+
+def build_submanifold_kernel_relation(coords, active_rows, kernel_size, dilation):
+    """``_ext.build_submanifold_kernel_relation`` (``coords.cpp:480-508``)."""
+    return build_kernel_relation(coords, active_rows, kernel_size, 1, 0, dilation)
+
+
+def build_target_kernel_relation_base(
+    coords, active_rows, target_coords, target_active_rows, kernel_size, stride, padding,
+    dilation, *, want_masks=False, want_kernel_lists=False,
+):
+    coords = _coords_arg(coords)
+    target = _coords_arg(target_coords, 'target_coords')
+    active_rows = _active_arg(active_rows)
+    target_active = _active_arg(target_active_rows)
+    ks = _triple(kernel_size)
+    if min(ks.x, ks.y, ks.z) <= 0:
+        raise ValueError('kernel_size values must be positive.')
+    rows, target_rows = int(coords.shape[0]), int(target.shape[0])
+    volume = ks.x * ks.y * ks.z
+    device = coords.device
+    in_rows, out_rows, kernel_ids, row_offsets, _, counts = _relation_buffers(
+        target_rows * volume, target_rows, device, with_out_coords=False
+    )
+    words = (volume + 31) // 32
+    masks = torch.empty((target_rows, words), dtype=torch.int32, device=device) if want_masks else None
+    k_offsets = torch.empty(volume + 1, dtype=torch.int32, device=device) if want_kernel_lists else None
+    k_edges = torch.empty(target_rows * volume, dtype=torch.int32, device=device) if want_kernel_lists else None
+    lib = _lib()
+    ws = _workspace(lib.lat_relation_workspace_bytes(rows, target_rows, volume), device)
+    with torch.cuda.device(device):
+        check(lib.lat_build_target_kernel_relation(
+            _ptr(coords), rows, _ptr(active_rows), _ptr(target), target_rows,
+            _ptr(target_active), ks, _triple(stride), _triple(padding), _triple(dilation),
+            _ptr(in_rows), _ptr(out_rows), _ptr(kernel_ids), _ptr(row_offsets), _ptr(counts),
+            _ptr(masks), _ptr(k_offsets), _ptr(k_edges), _ptr(ws), ws.numel(),
+            _ptr(status_word(device)), _stream(),
+        ))
+    return (in_rows, out_rows, kernel_ids, row_offsets, target, counts), masks, (k_offsets, k_edges)
+
+
+def build_target_kernel_relation(
+    coords, active_rows, target_coords, target_active_rows, kernel_size, stride, padding, dilation
+):
+    """``_ext.build_target_kernel_relation`` (``coords.cpp:546-589``); the fifth
+    entry is the caller's target coordinates (``relations.cpp:53-70``)."""
+    base, _, (k_offsets, k_edges) = build_target_kernel_relation_base(
+        coords, active_rows, target_coords, target_active_rows, kernel_size, stride, padding,
+        dilation, want_kernel_lists=True,
+    )
+    in_offsets, in_edges = build_relation_grouped_view(base[0], base[5], int(coords.shape[0]))
+    return (*base, in_offsets, in_edges, k_offsets, k_edges)
+
+
+def build_transposed_kernel_relation_base(
+    coords, active_rows, kernel_size, stride, padding, dilation
+):
+    coords = _coords_arg(coords)
+    active_rows = _active_arg(active_rows)
+    ks = _triple(kernel_size)
+    if min(ks.x, ks.y, ks.z) <= 0:
+        raise ValueError('kernel_size values must be positive.')
+    rows = int(coords.shape[0])
+    volume = ks.x * ks.y * ks.z
+    device = coords.device
+    cap = rows * volume
+    bufs = _relation_buffers(cap, cap, device)
+    lib = _lib()
+    ws = _workspace(lib.lat_relation_workspace_bytes(rows, cap, volume), device)
+    with torch.cuda.device(device):
+        check(lib.lat_build_transposed_kernel_relation(
+            _ptr(coords), rows, _ptr(active_rows), ks, _triple(stride), _triple(padding),
+            _triple(dilation), *(_ptr(b) for b in bufs), _ptr(ws), ws.numel(),
+            _ptr(status_word(device)), _stream(),
+        ))
+    return bufs
+
+
+def build_transposed_kernel_relation(coords, active_rows, kernel_size, stride, padding, dilation):
+    """``_ext.build_transposed_kernel_relation`` (``coords.cpp:509-545``)."""
+    bufs = build_transposed_kernel_relation_base(
+        coords, active_rows, kernel_size, stride, padding, dilation
+    )
+    ks = _triple(kernel_size)
+    return (*bufs, *_views(bufs[0], bufs[2], bufs[5], int(coords.shape[0]), ks.x * ks.y * ks.z))
+
+
+def build_generative_relation_base(coords, active_rows, kernel_size, stride):
+    coords = _coords_arg(coords)
+    active_rows = _active_arg(active_rows)
+    ks = _triple(kernel_size)
+    if min(ks.x, ks.y, ks.z) <= 0:
+        raise ValueError('kernel_size values must be positive.')
+    rows = int(coords.shape[0])
+    volume = ks.x * ks.y * ks.z
+    device = coords.device
+    cap = rows * volume
+    bufs = _relation_buffers(cap, cap, device)
+    lib = _lib()
+    ws = _workspace(256, device)
+    with torch.cuda.device(device):
+        check(lib.lat_build_generative_relation(
+            _ptr(coords), rows, _ptr(active_rows), ks, _triple(stride),
+            *(_ptr(b) for b in bufs), _ptr(ws), ws.numel(), _ptr(status_word(device)), _stream(),
+        ))
+    return bufs
+
+
+def build_generative_relation(coords, active_rows, kernel_size, stride):
+    """``_ext.build_generative_relation`` (``native/bindings/coords.cpp``)."""
+    bufs = build_generative_relation_base(coords, active_rows, kernel_size, stride)
+    ks = _triple(kernel_size)
+    return (*bufs, *_views(bufs[0], bufs[2], bufs[5], int(coords.shape[0]), ks.x * ks.y * ks.z))
+
+
+def build_target_transposed_relation_base(
+    coords, active_rows, target_coords, target_active_rows, stride
+):
+    """Transposed map of a ``kernel_size == stride`` conv restricted to a given
+    fine support (one edge per target row at most); see ``include/lattice_b200.h``."""
+    coords = _coords_arg(coords)
+    target = _coords_arg(target_coords, 'target_coords')
+    active_rows = _active_arg(active_rows)
+    target_active = _active_arg(target_active_rows)
+    rows, target_rows = int(coords.shape[0]), int(target.shape[0])
+    device = coords.device
+    in_rows, out_rows, kernel_ids, row_offsets, _, counts = _relation_buffers(
+        target_rows, target_rows, device, with_out_coords=False
+    )
+    lib = _lib()
+    ws = _workspace(lib.lat_relation_workspace_bytes(rows, target_rows, 1), device)
+    with torch.cuda.device(device):
+        check(lib.lat_build_target_transposed_relation(
+            _ptr(coords), rows, _ptr(active_rows), _ptr(target), target_rows,
+            _ptr(target_active), _triple(stride), _ptr(in_rows), _ptr(out_rows),
+            _ptr(kernel_ids), _ptr(row_offsets), _ptr(counts), _ptr(ws), ws.numel(),
+            _ptr(status_word(device)), _stream(),
+        ))
+    return (in_rows, out_rows, kernel_ids, row_offsets, target, counts)
+
+
+def build_relation_grouped_view(group_ids, counts, group_count: int):
+    """Edge ids grouped by ``group_ids`` (``make_relation_grouped_view``,
+    ``native/features/coordinates/relations.cpp:438-459``)."""
+    group_ids = _i32(group_ids, 'group_ids')
+    counts = _i32(counts, 'counts')
+    device = group_ids.device
+    cap = int(group_ids.shape[0])
+    row_offsets = torch.empty(group_count + 1, dtype=torch.int32, device=device)
+    edge_ids = torch.empty(cap, dtype=torch.int32, device=device)
+    lib = _lib()
+    ws = _workspace(lib.lat_grouped_view_workspace_bytes(cap, group_count), device)
+    with torch.cuda.device(device):
+        check(lib.lat_build_relation_grouped_view(
+            _ptr(group_ids), cap, _ptr(counts), group_count, _ptr(row_offsets), _ptr(edge_ids),
+            _ptr(ws), ws.numel(), _ptr(status_word(device)), _stream(),
+        ))
+    return row_offsets, edge_ids
+
+
+def build_relation_implicit_gemm_view(
+    source_coords, source_active_rows, output_coords, output_active_rows, offsets, stride, padding
+):
+    """``_ext.build_relation_implicit_gemm_view`` (``coords.cpp:590-627``):
+    returns (out_in_map [N_out, K], row_masks [N_out, ceil(K/32)])."""
+    src = _coords_arg(source_coords, 'source_coords')
+    out = _coords_arg(output_coords, 'output_coords')
+    offsets = _i32(offsets, 'offsets')
+    if offsets.ndim != 2 or offsets.shape[1] != 3:
+        raise ValueError('offsets must have shape (K, 3).')
+    k = int(offsets.shape[0])
+    device = src.device
+    out_in_map = torch.empty((out.shape[0], k), dtype=torch.int32, device=device)
+    row_masks = torch.empty((out.shape[0], (k + 31) // 32), dtype=torch.int32, device=device)
+    lib = _lib()
+    ws = _workspace(lib.lat_implicit_gemm_view_workspace_bytes(int(src.shape[0])), device)
+    with torch.cuda.device(device):
+        check(lib.lat_build_relation_implicit_gemm_view(
+            _ptr(src), int(src.shape[0]), _ptr(_active_arg(source_active_rows)),
+            _ptr(out), int(out.shape[0]), _ptr(_active_arg(output_active_rows)),
+            _ptr(offsets), k, _triple(stride), _triple(padding), _ptr(out_in_map),
+            _ptr(row_masks), _ptr(ws), ws.numel(), _ptr(status_word(device)), _stream(),
+        ))
+    return out_in_map, row_masks
+
+
+# --------------------------------------------------------------------------- #
+# coordinate sets (native/bindings/coords.cpp:132-222)
+# --------------------------------------------------------------------------- #
+
+
+def downsample_coords(coords, stride):
+    """Returns (coords [N, 4] with a valid prefix, count [1])."""
+    coords = _coords_arg(coords)
+    device = coords.device
+    rows = int(coords.shape[0])
+    out = torch.empty_like(coords)
+    count = torch.empty(1, dtype=torch.int32, device=device)
+    lib = _lib()
+    ws = _workspace(lib.lat_coord_set_workspace_bytes(rows), device)
+    with torch.cuda.device(device):
+        check(lib.lat_downsample_coords(
+            _ptr(coords), rows, _triple(stride), _ptr(out), _ptr(count), _ptr(ws), ws.numel(),
+            _ptr(status_word(device)), _stream(),
+        ))
+    return out, count
+
+
+def lookup_coords(coords, queries):
+    coords = _coords_arg(coords)
+    queries = _coords_arg(queries, 'queries')
+    device = coords.device
+    out = torch.empty(queries.shape[0], dtype=torch.int32, device=device)
+    lib = _lib()
+    ws = _workspace(lib.lat_coord_set_workspace_bytes(int(coords.shape[0])), device)
+    with torch.cuda.device(device):
+        check(lib.lat_lookup_coords(
+            _ptr(coords), int(coords.shape[0]), _ptr(queries), int(queries.shape[0]), _ptr(out),
+            _ptr(ws), ws.numel(), _ptr(status_word(device)), _stream(),
+        ))
+    return out
+
+
+def build_sparse_alignment(lhs_coords, lhs_active_rows, rhs_coords, rhs_active_rows, join):
+    """Returns (coords, active_rows [1], lhs_rows, rhs_rows)
+    (``coords.cpp:191-222``)."""
+    if join not in _JOIN:
+        raise ValueError("join must be 'inner', 'left', 'right', or 'outer'.")
+    lhs = _coords_arg(lhs_coords, 'lhs_coords')
+    rhs = _coords_arg(rhs_coords, 'rhs_coords')
+    device = lhs.device
+    l, r = int(lhs.shape[0]), int(rhs.shape[0])
+    capacity = r if join == 'right' else (l + r if join == 'outer' else l)
+    coords = torch.empty((capacity, 4), dtype=torch.int32, device=device)
+    count = torch.empty(1, dtype=torch.int32, device=device)
+    lhs_rows = torch.empty(capacity, dtype=torch.int32, device=device)
+    rhs_rows = torch.empty(capacity, dtype=torch.int32, device=device)
+    lib = _lib()
+    ws = _workspace(lib.lat_sparse_alignment_workspace_bytes(l, r), device)
+    with torch.cuda.device(device):
+        check(lib.lat_build_sparse_alignment(
+            _ptr(lhs), l, _ptr(_active_arg(lhs_active_rows)), _ptr(rhs), r,
+            _ptr(_active_arg(rhs_active_rows)), _JOIN[join], _ptr(coords), _ptr(count),
+            _ptr(lhs_rows), _ptr(rhs_rows), _ptr(ws), ws.numel(), _ptr(status_word(device)),
+            _stream(),
+        ))
+    return coords, count, lhs_rows, rhs_rows
+
+
+# --------------------------------------------------------------------------- #
+# convolution (native/bindings/convolution.cpp:12-146)
+# --------------------------------------------------------------------------- #
+
+
+def _weight_geometry(weights: torch.Tensor, n_kernels: int, in_channels: int):
+    if weights.ndim == 3:
+        if weights.shape[0] != n_kernels:
+            raise ValueError('weight kernel rows must match the convolution kernel.')
+        if weights.shape[1] != in_channels:
+            raise ValueError('weight input channels must match x.channels.')
+        return 0, Triple(n_kernels, 1, 1), int(weights.shape[2])
+    if weights.ndim == 5:
+        if weights.shape[4] != in_channels:
+            raise ValueError('weight input channels must match x.channels.')
+        kx, ky, kz = (int(v) for v in weights.shape[1:4])
+        if kx * ky * kz != n_kernels:
+            raise ValueError('weight kernel rows must match the convolution kernel.')
+        return 1, Triple(kx, ky, kz), int(weights.shape[0])
+    raise ValueError(
+        'mapped convolution weight must have shape (K, C_in, C_out) '
+        'or (C_out, Kx, Ky, Kz, C_in).'
+    )
+
+
+def sparse_conv_features(
+    feats, weights, in_rows, out_rows, kernel_ids, counts, row_offsets,
+    in_row_offsets=None, in_edge_ids=None, kernel_row_offsets=None, kernel_edge_ids=None,
+    out_capacity=None, n_kernels=None, *, bias=None, row_order=None,
+):
+    """``_ext.sparse_conv_features`` (``convolution.cpp:90-146``). The four grouped
+    view arguments are accepted for signature compatibility; the forward pass does
+    not read them."""
+    feats, stride = _feats_arg(feats)
+    _require_cuda(weights, 'weights')
+    if weights.dtype != feats.dtype:
+        raise ValueError('convolution weights must match feature dtype.')
+    dtype = _dtype_code(feats.dtype)
+    weights = weights.contiguous()
+    in_rows, out_rows, kernel_ids = (_i32(t, n) for t, n in (
+        (in_rows, 'in_rows'), (out_rows, 'out_rows'), (kernel_ids, 'kernel_ids')))
+    if not (in_rows.shape == out_rows.shape == kernel_ids.shape):
+        raise ValueError('in_rows, out_rows and kernel_ids must have the same length.')
+    counts, row_offsets = _i32(counts, 'counts'), _i32(row_offsets, 'row_offsets')
+    out_capacity, n_kernels = int(out_capacity), int(n_kernels)
+    if row_offsets.shape[0] != out_capacity + 1:
+        raise ValueError('row_offsets must have length out_capacity + 1.')
+    c_in = int(feats.shape[1])
+    layout, shape, c_out = _weight_geometry(weights, n_kernels, c_in)
+    device = feats.device
+    out = torch.empty((out_capacity, c_out), dtype=feats.dtype, device=device)
+    lib = _lib()
+    ws = _workspace(lib.lat_sparse_conv_workspace_bytes(n_kernels, c_in, c_out), device)
+    with torch.cuda.device(device):
+        check(lib.lat_sparse_conv_features(
+            dtype, _ptr(feats), int(feats.shape[0]), c_in, stride, _ptr(weights), layout, shape,
+            c_out, _ptr(in_rows), _ptr(out_rows), _ptr(kernel_ids), int(in_rows.shape[0]),
+            _ptr(counts), _ptr(row_offsets), out_capacity, n_kernels, _ptr(bias),
+            _ptr(row_order), _ptr(out), _ptr(ws), ws.numel(), _ptr(status_word(device)),
+            _stream(),
+        ))
+    return out
+
+
+def sparse_quantized_conv_features(
+    feats, weights, scales, biases, in_rows, out_rows, kernel_ids, counts, row_offsets,
+    sorted_kv_out_in_map=None, reorder_rows=None, tile_masks=None,
+    out_capacity=None, n_kernels=None, in_channels=None, out_channels=None,
+    storage_in_channels=None, group_size=None, bits=None, *, bias=None, row_order=None,
+):
+    """``_ext.sparse_quantized_conv_features`` (``convolution.cpp:12-89``). The
+    three sorted-plan arrays may be empty in the reference call; here a non-empty
+    ``reorder_rows`` is used as the row permutation of the tensor-core tiles."""
+    feats, stride = _feats_arg(feats)
+    dtype = _dtype_code(feats.dtype)
+    for tensor, name in ((weights, 'weights'), (scales, 'scales'), (biases, 'biases')):
+        _require_cuda(tensor, name)
+    if weights.dtype != torch.uint32 and weights.dtype != torch.int32:
+        raise ValueError('packed weight must be a three-dimensional uint32 array.')
+    if scales.dtype != feats.dtype or biases.dtype != feats.dtype:
+        raise ValueError('features must match quantized scale dtype.')
+    n_kernels, out_capacity = int(n_kernels), int(out_capacity)
+    in_channels, out_channels = int(in_channels), int(out_channels)
+    storage, group_size, bits = int(storage_in_channels), int(group_size), int(bits)
+    if feats.shape[1] != in_channels:
+        raise ValueError('quantized weight input channels must match x.channels.')
+    if bits not in (4, 8):
+        raise ValueError('quantized convolution supports only 4 or 8 bits.')
+    if group_size not in (32, 64, 128):
+        raise ValueError('quantized convolution group_size must be 32, 64, or 128.')
+    if storage % group_size != 0 or storage < in_channels:
+        raise ValueError('packed storage channels must be divisible by group_size.')
+    words, groups = storage * bits // 32, storage // group_size
+    if tuple(weights.shape) != (n_kernels, words, out_channels):
+        raise ValueError('packed weight must have shape (K, S * bits / 32, C_out).')
+    if tuple(scales.shape) != (n_kernels, groups, out_channels) or scales.shape != biases.shape:
+        raise ValueError('scales and biases must have shape (K, C_out, G).')
+    weights, scales, biases = weights.contiguous(), scales.contiguous(), biases.contiguous()
+    in_rows, out_rows, kernel_ids = (_i32(t, n) for t, n in (
+        (in_rows, 'in_rows'), (out_rows, 'out_rows'), (kernel_ids, 'kernel_ids')))
+    counts, row_offsets = _i32(counts, 'counts'), _i32(row_offsets, 'row_offsets')
+    if row_offsets.shape[0] != out_capacity + 1:
+        raise ValueError('row_offsets must have length out_capacity + 1.')
+    if row_order is None and reorder_rows is not None and reorder_rows.numel() == out_capacity:
+        row_order = _i32(reorder_rows, 'reorder_rows')
+    device = feats.device
+    out = torch.empty((out_capacity, out_channels), dtype=feats.dtype, device=device)
+    lib = _lib()
+    ws = _workspace(lib.lat_sparse_conv_workspace_bytes(n_kernels, in_channels, out_channels), device)
+    with torch.cuda.device(device):
+        check(lib.lat_sparse_quantized_conv_features(
+            dtype, _ptr(feats), int(feats.shape[0]), stride, _ptr(weights), _ptr(scales),
+            _ptr(biases), _ptr(in_rows), _ptr(out_rows), _ptr(kernel_ids),
+            int(in_rows.shape[0]), _ptr(counts), _ptr(row_offsets), out_capacity, n_kernels,
+            in_channels, out_channels, storage, group_size, bits, _ptr(bias), _ptr(row_order),
+            _ptr(out), _ptr(ws), ws.numel(), _ptr(status_word(device)), _stream(),
+        ))
+    return out
+
+
+def conv_uses_tensor_cores(dtype, n_kernels, in_channels, out_channels, bits=0, group_size=0) -> bool:
+    return bool(_lib().lat_conv_uses_tensor_cores(
+        _dtype_code(dtype), n_kernels, in_channels, out_channels, bits, group_size))
+
+
+def build_mask_row_order(row_masks, counts):
+    """Row permutation grouping output rows by equal offset mask (K <= 32)."""
+    row_masks = _i32(row_masks, 'row_masks')
+    if row_masks.ndim != 2 or row_masks.shape[1] != 1:
+        raise ValueError('sorted implicit GEMM view currently supports K <= 32.')
+    rows = int(row_masks.shape[0])
+    device = row_masks.device
+    order = torch.empty(rows, dtype=torch.int32, device=device)
+    lib = _lib()
+    ws = _workspace(lib.lat_mask_order_workspace_bytes(rows), device)
+    with torch.cuda.device(device):
+        check(lib.lat_build_mask_row_order(
+            _ptr(row_masks), rows, _ptr(_i32(counts, 'counts')), _ptr(order), _ptr(ws),
+            ws.numel(), _ptr(status_word(device)), _stream(),
+        ))
+    return order
+
+
+# --------------------------------------------------------------------------- #
+# pooling and pointwise feature ops
+# --------------------------------------------------------------------------- #
+
+
+def sparse_pool_features(
+    feats, in_rows, out_rows, kernel_ids, row_offsets, counts, input_exclusive, reduce,
+    out_capacity, n_kernels,
+):
+    """``_ext.sparse_pool_features`` (``native/bindings/pooling.cpp:17-72``)."""
+    feats, stride = _feats_arg(feats)
+    if feats.dtype != torch.float32:
+        raise ValueError('pooling currently supports float32 tensors.')
+    if reduce not in _REDUCE:
+        raise ValueError("reduce must be 'sum', 'max', or 'avg'.")
+    in_rows, out_rows, kernel_ids = (_i32(t, n) for t, n in (
+        (in_rows, 'in_rows'), (out_rows, 'out_rows'), (kernel_ids, 'kernel_ids')))
+    row_offsets, counts = _i32(row_offsets, 'row_offsets'), _i32(counts, 'counts')
+    out_capacity = int(out_capacity)
+    if row_offsets.shape[0] != out_capacity + 1:
+        raise ValueError('row_offsets must have length out_capacity + 1.')
+    device = feats.device
+    out = torch.empty((out_capacity, feats.shape[1]), dtype=torch.float32, device=device)
+    with torch.cuda.device(device):
+        check(_lib().lat_sparse_pool_features(
+            _ptr(feats), int(feats.shape[0]), int(feats.shape[1]), stride, _ptr(in_rows),
+            _ptr(out_rows), _ptr(kernel_ids), int(in_rows.shape[0]), _ptr(row_offsets),
+            _ptr(counts), int(bool(input_exclusive)), _REDUCE[reduce], out_capacity,
+            int(n_kernels), _ptr(out), _ptr(status_word(device)), _stream(),
+        ))
+    return out
+
+
+def global_pool(feats, batch_offsets, reduce: str):
+    feats, _ = _feats_arg(feats)
+    feats = feats.contiguous()
+    if feats.dtype != torch.float32:
+        raise ValueError('pooling currently supports float32 tensors.')
+    batch_offsets = _i32(batch_offsets, 'batch_offsets')
+    batches = int(batch_offsets.shape[0]) - 1
+    out = torch.empty((batches, feats.shape[1]), dtype=torch.float32, device=feats.device)
+    with torch.cuda.device(feats.device):
+        check(_lib().lat_global_pool(
+            _ptr(feats), int(feats.shape[0]), int(feats.shape[1]), _ptr(batch_offsets), batches,
+            _REDUCE[reduce], _ptr(out), _stream(),
+        ))
+    return out
+
+
+def linear(feats, weight, bias=None):
+    feats, _ = _feats_arg(feats)
+    feats = feats.contiguous()
+    _require_cuda(weight, 'weight')
+    if weight.dtype != feats.dtype:
+        raise ValueError('convolution weights must match feature dtype.')
+    weight = weight.contiguous()
+    out = torch.empty((feats.shape[0], weight.shape[0]), dtype=feats.dtype, device=feats.device)
+    with torch.cuda.device(feats.device):
+        check(_lib().lat_linear(
+            _dtype_code(feats.dtype), _ptr(feats), int(feats.shape[0]), int(feats.shape[1]),
+            _ptr(weight), int(weight.shape[0]), _ptr(bias), _ptr(out), _stream(),
+        ))
+    return out
+
+
+def quantized_linear(
+    feats, packed, scales, biases, out_channels, storage_in_channels, group_size, bits, bias=None
+):
+    feats, _ = _feats_arg(feats)
+    feats = feats.contiguous()
+    out = torch.empty((feats.shape[0], out_channels), dtype=feats.dtype, device=feats.device)
+    with torch.cuda.device(feats.device):
+        check(_lib().lat_quantized_linear(
+            _dtype_code(feats.dtype), _ptr(feats), int(feats.shape[0]), int(feats.shape[1]),
+            _ptr(packed.contiguous()), _ptr(scales.contiguous()), _ptr(biases.contiguous()),
+            int(out_channels), int(storage_in_channels), int(group_size), int(bits), _ptr(bias),
+            _ptr(out), _stream(),
+        ))
+    return out
+
+
+def batch_norm_relu(feats, weight, bias, mean, var, eps: float, apply_relu: bool):
+    feats, _ = _feats_arg(feats)
+    feats = feats.contiguous()
+    out = torch.empty_like(feats)
+    with torch.cuda.device(feats.device):
+        check(_lib().lat_batch_norm_relu(
+            _dtype_code(feats.dtype), _ptr(feats), int(feats.shape[0]), int(feats.shape[1]),
+            _ptr(weight), _ptr(bias), _ptr(mean), _ptr(var), float(eps), int(apply_relu),
+            _ptr(out), _stream(),
+        ))
+    return out
+
+
+def relu(feats):
+    feats, _ = _feats_arg(feats)
+    feats = feats.contiguous()
+    out = torch.empty_like(feats)
+    with torch.cuda.device(feats.device):
+        check(_lib().lat_relu(
+            _dtype_code(feats.dtype), _ptr(feats), feats.numel(), _ptr(out), _stream()
+        ))
+    return out

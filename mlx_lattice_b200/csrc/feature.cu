@@ -1,0 +1,243 @@
+// Pointwise feature operators of the inference path: linear / quantized linear
+// (x @ W.T with float32 accumulation), inference batch-norm with optional fused ReLU,
+// and ReLU. They stand in for the third-party array ops the reference calls
+// (mlx_lattice/ops/feature.py:33-56,166-187, ops/_quantized.py:8-38).
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace lat {
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+
+constexpr int kRowsPerBlock = 32;
+constexpr int kThreads = 256;
+
+// Block: 32 rows staged in shared memory; thread t owns output channel(s) t, t+256, ...
+// and keeps its weight row in registers/L1 across the 32 rows.
+template <typename T, bool Quantized>
+__global__ void __launch_bounds__(kThreads) linear_kernel(
+    const T* feats, int rows, int c_in, const T* weight, const uint32_t* packed,
+    const T* scales, const T* biases, int storage, int group_size, int bits, int c_out,
+    const T* bias, T* out
+) {
+    extern __shared__ float x_tile[];  // [kRowsPerBlock][c_in]
+    int row0 = blockIdx.x * kRowsPerBlock;
+    int valid = min(kRowsPerBlock, rows - row0);
+    for (int i = threadIdx.x; i < kRowsPerBlock * c_in; i += kThreads) {
+        int r = i / c_in;
+        int c = i - r * c_in;
+        x_tile[i] = r < valid ? to_float<T>(feats[static_cast<size_t>(row0 + r) * c_in + c]) : 0.0f;
+    }
+    __syncthreads();
+    int words = Quantized ? storage * bits / 32 : 0;
+    int groups = Quantized ? storage / group_size : 0;
+    for (int co = threadIdx.x; co < c_out; co += kThreads) {
+        float acc[kRowsPerBlock];
+#pragma unroll
+        for (int r = 0; r < kRowsPerBlock; ++r) {
+            acc[r] = 0.0f;
+        }
+        for (int ci = 0; ci < c_in; ++ci) {
+            float w;
+            if (Quantized) {
+                int bit = ci * bits;
+                uint32_t word = __ldg(packed + static_cast<size_t>(co) * words + (bit >> 5));
+                uint32_t code = (word >> (bit & 31)) & ((1u << bits) - 1u);
+                size_t q = static_cast<size_t>(co) * groups + ci / group_size;
+                w = fmaf(static_cast<float>(code), to_float<T>(scales[q]), to_float<T>(biases[q]));
+            } else {
+                w = to_float<T>(weight[static_cast<size_t>(co) * c_in + ci]);
+            }
+#pragma unroll
+            for (int r = 0; r < kRowsPerBlock; ++r) {
+                acc[r] = fmaf(x_tile[r * c_in + ci], w, acc[r]);
+            }
+        }
+        for (int r = 0; r < valid; ++r) {
+            T y = from_float<T>(acc[r]);
+            if (bias != nullptr) {
+                y = from_float<T>(to_float<T>(y) + to_float<T>(bias[co]));
+            }
+            out[static_cast<size_t>(row0 + r) * c_out + co] = y;
+        }
+    }
+}
+
+template <typename T>
+__global__ void batch_norm_relu_kernel(
+    const T* feats, long long rows, int channels, const T* weight, const T* bias,
+    const T* mean, const T* var, float eps, int apply_relu, T* out
+) {
+    long long total = rows * channels;
+    long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (; i < total; i += stride) {
+        int c = static_cast<int>(i % channels);
+        float x = to_float<T>(feats[i]);
+        float m = mean != nullptr ? to_float<T>(mean[c]) : 0.0f;
+        float v = var != nullptr ? to_float<T>(var[c]) : 1.0f;
+        float y = (x - m) * (1.0f / sqrtf(v + eps));
+        if (weight != nullptr) {
+            y *= to_float<T>(weight[c]);
+        }
+        if (bias != nullptr) {
+            y += to_float<T>(bias[c]);
+        }
+        if (apply_relu) {
+            y = fmaxf(y, 0.0f);
+        }
+        out[i] = from_float<T>(y);
+    }
+}
+
+template <typename T>
+__global__ void relu_kernel(const T* feats, long long total, T* out) {
+    long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (; i < total; i += stride) {
+        out[i] = from_float<T>(fmaxf(to_float<T>(feats[i]), 0.0f));
+    }
+}
+
+inline int elementwise_grid(long long total) {
+    long long blocks = (total + 255) / 256;
+    return static_cast<int>(std::max(1LL, std::min(blocks, 148LL * 32)));
+}
+
+template <typename T, bool Quantized>
+int launch_linear(
+    const void* feats, int rows, int c_in, const void* weight, const uint32_t* packed,
+    const void* scales, const void* biases, int storage, int group_size, int bits, int c_out,
+    const void* bias, void* out, cudaStream_t stream
+) {
+    size_t smem = sizeof(float) * kRowsPerBlock * c_in;
+    if (smem > 48 * 1024) {
+        LAT_CUDA_CHECK(cudaFuncSetAttribute(
+            linear_kernel<T, Quantized>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            static_cast<int>(smem)));
+    }
+    int blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
+    linear_kernel<T, Quantized><<<blocks, kThreads, smem, stream>>>(
+        static_cast<const T*>(feats), rows, c_in, static_cast<const T*>(weight), packed,
+        static_cast<const T*>(scales), static_cast<const T*>(biases), storage, group_size, bits,
+        c_out, static_cast<const T*>(bias), static_cast<T*>(out));
+    LAT_LAUNCH_CHECK();
+    return LAT_OK;
+}
+
+} // namespace
+
+} // namespace lat
+
+using namespace lat;
+
+extern "C" {
+
+int lat_linear(
+    int32_t dtype, const void* feats, int32_t rows, int32_t in_channels,
+    const void* weight, int32_t out_channels, const void* bias, void* out, void* stream_ptr
+) {
+    LAT_REQUIRE(dtype == LAT_F32 || dtype == LAT_F16,
+                "convolution supports float32 and float16 tensors.");
+    LAT_REQUIRE(rows >= 0 && in_channels > 0 && out_channels > 0,
+                "weight input channels must match x.channels.");
+    LAT_REQUIRE(in_channels <= 1536, "linear supports at most 1536 input channels.");
+    if (rows == 0) {
+        return LAT_OK;
+    }
+    cudaStream_t stream = as_stream(stream_ptr);
+    if (dtype == LAT_F32) {
+        return launch_linear<float, false>(feats, rows, in_channels, weight, nullptr, nullptr,
+                                           nullptr, 0, 1, 0, out_channels, bias, out, stream);
+    }
+    return launch_linear<__half, false>(feats, rows, in_channels, weight, nullptr, nullptr,
+                                        nullptr, 0, 1, 0, out_channels, bias, out, stream);
+}
+
+int lat_quantized_linear(
+    int32_t dtype, const void* feats, int32_t rows, int32_t in_channels,
+    const uint32_t* packed, const void* scales, const void* biases,
+    int32_t out_channels, int32_t storage_in_channels, int32_t group_size, int32_t bits,
+    const void* bias, void* out, void* stream_ptr
+) {
+    LAT_REQUIRE(dtype == LAT_F32 || dtype == LAT_F16,
+                "convolution supports float32 and float16 tensors.");
+    LAT_REQUIRE(bits == 4 || bits == 8, "quantized weight bits must be 4 or 8.");
+    LAT_REQUIRE(group_size == 32 || group_size == 64 || group_size == 128,
+                "quantized weight group_size must be 32, 64, or 128.");
+    LAT_REQUIRE(rows >= 0 && in_channels > 0 && out_channels > 0 &&
+                    storage_in_channels >= in_channels && storage_in_channels % group_size == 0,
+                "features must have shape (N, quantized_weight.in_channels).");
+    LAT_REQUIRE(in_channels <= 1536, "linear supports at most 1536 input channels.");
+    if (rows == 0) {
+        return LAT_OK;
+    }
+    cudaStream_t stream = as_stream(stream_ptr);
+    if (dtype == LAT_F32) {
+        return launch_linear<float, true>(feats, rows, in_channels, nullptr, packed, scales,
+                                          biases, storage_in_channels, group_size, bits,
+                                          out_channels, bias, out, stream);
+    }
+    return launch_linear<__half, true>(feats, rows, in_channels, nullptr, packed, scales, biases,
+                                       storage_in_channels, group_size, bits, out_channels, bias,
+                                       out, stream);
+}
+
+int lat_batch_norm_relu(
+    int32_t dtype, const void* feats, int64_t rows, int32_t channels,
+    const void* weight, const void* bias, const void* mean, const void* var, float eps,
+    int32_t apply_relu, void* out, void* stream_ptr
+) {
+    LAT_REQUIRE(dtype == LAT_F32 || dtype == LAT_F16,
+                "batch_norm supports float32 and float16 tensors.");
+    LAT_REQUIRE(eps > 0.0f, "eps must be positive.");
+    LAT_REQUIRE(rows >= 0 && channels > 0, "feats must have shape (N, C).");
+    if (rows == 0) {
+        return LAT_OK;
+    }
+    cudaStream_t stream = as_stream(stream_ptr);
+    int grid = elementwise_grid(rows * channels);
+    if (dtype == LAT_F32) {
+        batch_norm_relu_kernel<float><<<grid, 256, 0, stream>>>(
+            static_cast<const float*>(feats), rows, channels, static_cast<const float*>(weight),
+            static_cast<const float*>(bias), static_cast<const float*>(mean),
+            static_cast<const float*>(var), eps, apply_relu, static_cast<float*>(out));
+    } else {
+        batch_norm_relu_kernel<__half><<<grid, 256, 0, stream>>>(
+            static_cast<const __half*>(feats), rows, channels, static_cast<const __half*>(weight),
+            static_cast<const __half*>(bias), static_cast<const __half*>(mean),
+            static_cast<const __half*>(var), eps, apply_relu, static_cast<__half*>(out));
+    }
+    LAT_LAUNCH_CHECK();
+    return LAT_OK;
+}
+
+int lat_relu(int32_t dtype, const void* feats, int64_t elements, void* out, void* stream_ptr) {
+    LAT_REQUIRE(dtype == LAT_F32 || dtype == LAT_F16,
+                "relu supports float32 and float16 tensors.");
+    LAT_REQUIRE(elements >= 0, "feats must have shape (N, C).");
+    if (elements == 0) {
+        return LAT_OK;
+    }
+    cudaStream_t stream = as_stream(stream_ptr);
+    int grid = elementwise_grid(elements);
+    if (dtype == LAT_F32) {
+        relu_kernel<float><<<grid, 256, 0, stream>>>(
+            static_cast<const float*>(feats), elements, static_cast<float*>(out));
+    } else {
+        relu_kernel<__half><<<grid, 256, 0, stream>>>(
+            static_cast<const __half*>(feats), elements, static_cast<__half*>(out));
+    }
+    LAT_LAUNCH_CHECK();
+    return LAT_OK;
+}
+
+} // extern "C"

@@ -1,0 +1,99 @@
+"""Feature execution over a prebuilt relation (``mlx_lattice/ops/_relation_exec.py``)."""
+
+from __future__ import annotations
+
+import torch
+
+from mlx_lattice_b200 import _ext
+from mlx_lattice_b200.core.quantized import QuantizedWeight
+from mlx_lattice_b200.core.relations import KernelRelation
+
+
+def _row_order(relation: KernelRelation, uses_tensor_cores: bool):
+    if not uses_tensor_cores:
+        return None
+    if relation.contract.kind not in ('forward', 'target', 'submanifold'):
+        return None
+    return relation.require_row_order()
+
+
+def sparse_quantized_conv_features_from_relation(
+    feats: torch.Tensor, weight: QuantizedWeight, relation: KernelRelation, bias=None
+) -> torch.Tensor:
+    """Quantized sparse convolution over a prebuilt relation (``:19-61``)."""
+    if relation.n_out_capacity is None or relation.n_kernels is None:
+        raise ValueError('kernel relation is missing static shape metadata.')
+    if relation.n_kernels != weight.weight.shape[0]:
+        raise ValueError('quantized weight kernel rows must match the relation.')
+    tc = _ext.conv_uses_tensor_cores(
+        feats.dtype, relation.n_kernels, weight.in_channels, weight.out_channels,
+        weight.bits, weight.group_size,
+    )
+    return _ext.sparse_quantized_conv_features(
+        feats,
+        weight.weight,
+        weight.scales,
+        weight.biases,
+        relation.edges.in_rows,
+        relation.edges.out_rows,
+        relation.edges.kernel_ids,
+        relation.counts,
+        relation.output_csr.row_offsets,
+        None,
+        None,
+        None,
+        relation.n_out_capacity,
+        relation.n_kernels,
+        weight.in_channels,
+        weight.out_channels,
+        weight.storage_in_channels,
+        weight.group_size,
+        weight.bits,
+        bias=bias,
+        row_order=_row_order(relation, tc),
+    )
+
+
+def sparse_conv_features_from_relation(
+    feats: torch.Tensor, weight: torch.Tensor, relation: KernelRelation, bias=None
+) -> torch.Tensor:
+    """Float sparse convolution over a prebuilt relation (``:84-116``)."""
+    if relation.n_out_capacity is None or relation.n_kernels is None:
+        raise ValueError('kernel relation is missing static shape metadata.')
+    c_out = int(weight.shape[2] if weight.ndim == 3 else weight.shape[0])
+    tc = _ext.conv_uses_tensor_cores(
+        feats.dtype, relation.n_kernels, int(feats.shape[1]), c_out
+    )
+    return _ext.sparse_conv_features(
+        feats,
+        weight,
+        relation.edges.in_rows,
+        relation.edges.out_rows,
+        relation.edges.kernel_ids,
+        relation.counts,
+        relation.output_csr.row_offsets,
+        out_capacity=relation.n_out_capacity,
+        n_kernels=relation.n_kernels,
+        bias=bias,
+        row_order=_row_order(relation, tc),
+    )
+
+
+def sparse_pool_features_from_relation(
+    feats: torch.Tensor, relation: KernelRelation, *, input_exclusive: bool, mode: str
+) -> torch.Tensor:
+    """Sparse pooling over a prebuilt kernel relation (``:256-276``)."""
+    if relation.n_out_capacity is None or relation.n_kernels is None:
+        raise ValueError('kernel relation is missing static shape metadata.')
+    return _ext.sparse_pool_features(
+        feats,
+        relation.edges.in_rows,
+        relation.edges.out_rows,
+        relation.edges.kernel_ids,
+        relation.output_csr.row_offsets,
+        relation.counts,
+        input_exclusive,
+        mode,
+        relation.n_out_capacity,
+        relation.n_kernels,
+    )

@@ -1,0 +1,65 @@
+"""Pointwise feature operators (``mlx_lattice/ops/feature.py:33-56,166-187``)."""
+
+from __future__ import annotations
+
+import torch
+
+from mlx_lattice_b200 import _ext
+from mlx_lattice_b200.core import QuantizedWeight, SparseTensor
+from mlx_lattice_b200.ops._quantized import quantized_matmul
+
+__all__ = ['batch_norm', 'linear', 'relu']
+
+
+def linear(x: SparseTensor, weight, bias: torch.Tensor | None = None) -> SparseTensor:
+    """Dense ``(C_out, C_in)`` or packed linear projection; coordinates preserved."""
+    _check_bias(bias, x.feats.dtype)
+    if isinstance(weight, QuantizedWeight):
+        if bias is not None and bias.shape[0] != weight.out_channels:
+            raise ValueError('bias channels must match output channels.')
+        return x.replace(feats=quantized_matmul(x.feats, weight, bias))
+    if weight.ndim != 2:
+        raise ValueError('weight must have shape (C_out, C_in).')
+    if weight.shape[1] != x.channels:
+        raise ValueError('weight input channels must match x.channels.')
+    if weight.dtype != x.feats.dtype:
+        raise ValueError('convolution weights must match feature dtype.')
+    if bias is not None and bias.shape[0] != weight.shape[0]:
+        raise ValueError('bias channels must match output channels.')
+    return x.replace(feats=_ext.linear(x.feats, weight, bias))
+
+
+def relu(x: SparseTensor) -> SparseTensor:
+    return x.replace(feats=_ext.relu(x.feats))
+
+
+def batch_norm(
+    x: SparseTensor, *, weight=None, bias=None, mean=None, var=None, eps: float = 1e-5,
+    fuse_relu: bool = False,
+) -> SparseTensor:
+    """Per-channel normalisation with given (running) statistics. ``fuse_relu``
+    (an addition to the reference signature) applies ReLU in the same pass."""
+    if eps <= 0:
+        raise ValueError('eps must be positive.')
+    if mean is None or var is None:
+        raise ValueError(
+            'batch statistics over active rows are a training-path feature; '
+            'pass running mean and var.'
+        )
+    for name, vector in (('mean', mean), ('var', var), ('weight', weight), ('bias', bias)):
+        if vector is not None and tuple(vector.shape) != (x.channels,):
+            raise ValueError(f'{name} must have shape (C,).')
+        if vector is not None and vector.dtype != x.feats.dtype:
+            raise ValueError(f'{name} dtype must match features.')
+    return x.replace(
+        feats=_ext.batch_norm_relu(x.feats, weight, bias, mean, var, eps, fuse_relu)
+    )
+
+
+def _check_bias(bias, dtype) -> None:
+    if bias is None:
+        return
+    if bias.ndim != 1:
+        raise ValueError('bias must have shape (C_out,).')
+    if bias.dtype != dtype:
+        raise ValueError('bias dtype must match output features.')

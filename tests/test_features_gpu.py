@@ -1,0 +1,235 @@
+"""Sparse-conv contraction, pooling and pointwise feature ops on the GPU against
+the oracle. Tolerances are the parity contract's: fp16 activations
+max|y - ref| <= 2e-3 * max|ref|; fp32 <= 1e-5 relative."""
+
+import numpy as np
+import pytest
+import torch
+
+from mlx_lattice_b200 import synthetic
+
+pytestmark = pytest.mark.gpu
+
+FP16_TOL = 2e-3
+FP32_TOL = 1e-5
+
+
+def _dev(array, cuda):
+    return torch.from_numpy(np.ascontiguousarray(array)).to(cuda)
+
+
+def _rel_dev(rel, cuda):
+    return {k: _dev(v, cuda) for k, v in rel.items()}
+
+
+def _max_rel_err(got, want):
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    scale = np.abs(want).max()
+    return np.abs(got - want).max() / (scale if scale > 0 else 1.0)
+
+
+def _conv(cuda, feats, weights, rel, out_capacity, n_kernels, bias=None, row_order=None):
+    from mlx_lattice_b200 import _ext
+
+    r = _rel_dev(rel, cuda)
+    out = _ext.sparse_conv_features(
+        _dev(feats, cuda), _dev(weights, cuda), r['in_rows'], r['out_rows'], r['kernel_ids'],
+        r['counts'], r['row_offsets'], out_capacity=out_capacity, n_kernels=n_kernels,
+        bias=None if bias is None else _dev(bias, cuda),
+        row_order=None if row_order is None else _dev(row_order, cuda))
+    return out.cpu().numpy()
+
+
+def _qconv(cuda, feats, q, rel, out_capacity, n_kernels, row_order=None):
+    from mlx_lattice_b200 import _ext
+
+    r = _rel_dev(rel, cuda)
+    out = _ext.sparse_quantized_conv_features(
+        _dev(feats, cuda), _dev(q['weight'].view(np.int32), cuda), _dev(q['scales'], cuda),
+        _dev(q['biases'], cuda), r['in_rows'], r['out_rows'], r['kernel_ids'], r['counts'],
+        r['row_offsets'], None, None, None, out_capacity, n_kernels, q['in_channels'],
+        q['out_channels'], q['storage_in_channels'], q['group_size'], q['bits'],
+        row_order=None if row_order is None else _dev(row_order, cuda))
+    return out.cpu().numpy()
+
+
+@pytest.fixture(scope='module')
+def sphere(oracle):
+    coords = synthetic.sphere_plane_batch(0, 1, 20000, 96)
+    return coords, oracle.build_submanifold_kernel_relation(coords)
+
+
+def test_reference_known_answer_conv(cuda, oracle):
+    # tests/ops/test_conv.py:44-62 of the reference: 3-point line, K=(3,1,1)
+    coords = np.array([[0, 0, 0, 0], [0, 1, 0, 0], [0, 2, 0, 0]], np.int32)
+    rel = oracle.build_kernel_relation(coords, None, kernel_size=(3, 1, 1))
+    feats = np.array([[1.0], [2.0], [3.0]], np.float32)
+    weights = np.array([[[1.0]], [[2.0]], [[3.0]]], np.float32)
+    assert _conv(cuda, feats, weights, rel, 3, 3).ravel().tolist() == [8.0, 14.0, 8.0]
+    half = _conv(cuda, feats.astype(np.float16), weights.astype(np.float16), rel, 3, 3)
+    assert half.dtype == np.float16 and half.ravel().tolist() == [8.0, 14.0, 8.0]
+
+
+@pytest.mark.parametrize('c_in,c_out', [(32, 32), (5, 7), (16, 48), (64, 20)])
+def test_float32_conv(cuda, oracle, sphere, c_in, c_out):
+    coords, rel = sphere
+    n = coords.shape[0]
+    rng = np.random.default_rng(c_in * 100 + c_out)
+    feats = rng.normal(size=(n, c_in)).astype(np.float32)
+    w5 = (rng.normal(size=(c_out, 3, 3, 3, c_in)) * 0.05).astype(np.float32)
+    want = oracle.sparse_conv(feats, w5, rel, n, 27)
+    got = _conv(cuda, feats, w5, rel, n, 27)
+    assert _max_rel_err(got, want) <= FP32_TOL
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-5 * np.abs(want).max())
+    wk = np.ascontiguousarray(w5.transpose(1, 2, 3, 4, 0).reshape(27, c_in, c_out))
+    assert np.array_equal(_conv(cuda, feats, wk, rel, n, 27), got)
+
+
+@pytest.mark.parametrize('c_in,c_out', [(32, 32), (64, 64), (32, 64), (64, 128), (96, 96),
+                                        (128, 256), (256, 256), (8, 24), (4, 32), (32, 20)])
+def test_float16_conv(cuda, oracle, sphere, c_in, c_out):
+    coords, rel = sphere
+    n = coords.shape[0]
+    rng = np.random.default_rng(c_in * 1000 + c_out)
+    feats = rng.normal(size=(n, c_in)).astype(np.float16)
+    w5 = (rng.normal(size=(c_out, 3, 3, 3, c_in)) * 0.05).astype(np.float16)
+    # square 16/32/64 channels: the reference accumulates in float32; other shapes
+    # re-round to float16 after every multiply-add, for which the reference's own
+    # parity tolerance is 2e-2 (tests/cases/conv_cases.py:17)
+    square = c_in == c_out and c_in in (16, 32, 64)
+    want = oracle.sparse_conv(feats, w5, rel, n, 27)
+    got = _conv(cuda, feats, w5, rel, n, 27)
+    assert _max_rel_err(got, want) <= (FP16_TOL if square else 2e-2)
+    exact = oracle.sparse_conv(feats.astype(np.float32), w5.astype(np.float32), rel, n, 27)
+    assert _max_rel_err(got, exact) <= FP16_TOL
+
+
+@pytest.mark.parametrize('bits', [4, 8])
+@pytest.mark.parametrize('c_in,c_out', [(32, 32), (64, 128), (96, 96), (128, 64), (256, 256), (40, 16)])
+def test_quantized_conv_float16(cuda, oracle, restatement, sphere, bits, c_in, c_out):
+    coords, rel = sphere
+    n = coords.shape[0]
+    rng = np.random.default_rng(bits * 7 + c_in + c_out)
+    feats = rng.normal(size=(n, c_in)).astype(np.float16)
+    w5 = (rng.normal(size=(c_out, 3, 3, 3, c_in)) * 0.05).astype(np.float16)
+    q = restatement.quantize_weight(w5, 32, bits)
+    want = oracle.sparse_quantized_conv(
+        feats, q['weight'], q['scales'], q['biases'], rel, n, 27, c_in, c_out,
+        q['storage_in_channels'], 32, bits)
+    got = _qconv(cuda, feats, q, rel, n, 27)
+    assert _max_rel_err(got, want) <= FP16_TOL
+
+
+def test_quantized_conv_float32_and_group64(cuda, oracle, restatement, sphere):
+    coords, rel = sphere
+    n = coords.shape[0]
+    rng = np.random.default_rng(3)
+    feats = rng.normal(size=(n, 64)).astype(np.float32)
+    w5 = (rng.normal(size=(32, 3, 3, 3, 64)) * 0.05).astype(np.float32)
+    q = restatement.quantize_weight(w5, 64, 4)
+    want = oracle.sparse_quantized_conv(
+        feats, q['weight'], q['scales'], q['biases'], rel, n, 27, 64, 32, 64, 64, 4)
+    assert _max_rel_err(_qconv(cuda, feats, q, rel, n, 27), want) <= FP32_TOL
+
+
+def test_strided_quantized_conv_config1_shape(cuda, oracle, restatement):
+    """k=2, s=2, int4 g32, 64 -> 128 on a sphere+plane cloud: padding rows are zero."""
+    coords = synthetic.sphere_plane_batch(1, 2, 15000, 128)
+    n = coords.shape[0]
+    rel = oracle.build_kernel_relation(coords, None, kernel_size=2, stride=2)
+    n_out = int(rel['counts'][1])
+    rng = np.random.default_rng(11)
+    feats = rng.normal(size=(n, 64)).astype(np.float16)
+    w5 = (rng.normal(size=(128, 2, 2, 2, 64)) * 0.05).astype(np.float16)
+    q = restatement.quantize_weight(w5, 32, 4)
+    want = oracle.sparse_quantized_conv(
+        feats, q['weight'], q['scales'], q['biases'], rel, n, 8, 64, 128, 64, 32, 4)
+    got = _qconv(cuda, feats, q, rel, n, 8)
+    assert _max_rel_err(got, want) <= FP16_TOL
+    assert not got[n_out:].any()
+    order = np.random.default_rng(5).permutation(n).astype(np.int32)
+    assert np.array_equal(_qconv(cuda, feats, q, rel, n, 8, row_order=order), got)
+
+
+def test_bias_and_determinism(cuda, oracle, sphere):
+    coords, rel = sphere
+    n = coords.shape[0]
+    rng = np.random.default_rng(17)
+    feats = rng.normal(size=(n, 32)).astype(np.float16)
+    w5 = (rng.normal(size=(64, 3, 3, 3, 32)) * 0.05).astype(np.float16)
+    bias = rng.normal(size=64).astype(np.float16)
+    plain = _conv(cuda, feats, w5, rel, n, 27)
+    with_bias = _conv(cuda, feats, w5, rel, n, 27, bias=bias)
+    assert np.array_equal(with_bias, (plain.astype(np.float32) + bias.astype(np.float32)).astype(np.float16))
+    assert np.array_equal(_conv(cuda, feats, w5, rel, n, 27), plain)
+
+
+@pytest.mark.parametrize('reduce', ['sum', 'max', 'avg'])
+def test_sparse_pool(cuda, oracle, reduce):
+    from mlx_lattice_b200 import _ext
+
+    coords = synthetic.lidar_batch(3, 2, 12000)
+    n = coords.shape[0]
+    rng = np.random.default_rng(23)
+    for spec in (dict(kernel_size=3, stride=2), dict(kernel_size=2, stride=2)):
+        rel = oracle.build_kernel_relation(coords, None, **spec)
+        volume = spec['kernel_size'] ** 3
+        for channels in (96, 7, 130):
+            feats = rng.normal(size=(n, channels)).astype(np.float32)
+            want = oracle.sparse_pool(feats, rel, input_exclusive=False, reduce=reduce,
+                                      out_capacity=n, n_kernels=volume)
+            r = _rel_dev(rel, cuda)
+            got = _ext.sparse_pool_features(
+                _dev(feats, cuda), r['in_rows'], r['out_rows'], r['kernel_ids'], r['row_offsets'],
+                r['counts'], False, reduce, n, volume).cpu().numpy()
+            assert np.array_equal(got, want)
+    with pytest.raises(ValueError, match='pooling currently supports float32'):
+        _ext.sparse_pool_features(
+            _dev(feats.astype(np.float16), cuda), r['in_rows'], r['out_rows'], r['kernel_ids'],
+            r['row_offsets'], r['counts'], False, reduce, n, volume)
+
+
+def test_global_pool_linear_batchnorm(cuda, restatement):
+    from mlx_lattice_b200 import _ext
+
+    rng = np.random.default_rng(29)
+    counts = (4000, 0, 2500, 1)
+    rows = sum(counts)
+    feats = rng.normal(size=(rows, 192)).astype(np.float32)
+    offsets = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32, device=cuda)
+    for mode in ('sum', 'avg'):
+        got = _ext.global_pool(_dev(feats, cuda), offsets, mode).cpu().numpy()
+        want = restatement.global_pool(feats, counts, mode)
+        assert np.allclose(got, want, rtol=1e-5, atol=1e-5 * np.abs(want).max())
+    nonempty = (4000, 2500, 1)
+    offs2 = torch.tensor(np.concatenate([[0], np.cumsum(nonempty)]), dtype=torch.int32, device=cuda)
+    got = _ext.global_pool(_dev(feats[: sum(nonempty)], cuda), offs2, 'max').cpu().numpy()
+    assert np.array_equal(got, restatement.global_pool(feats[: sum(nonempty)], nonempty, 'max'))
+
+    x16 = rng.normal(size=(5000, 96)).astype(np.float16)
+    w = (rng.normal(size=(192, 96)) * 0.1).astype(np.float16)
+    b = rng.normal(size=192).astype(np.float16)
+    got = _ext.linear(_dev(x16, cuda), _dev(w, cuda), _dev(b, cuda)).cpu().numpy()
+    assert _max_rel_err(got, restatement.linear(x16, w, b)) <= FP16_TOL
+    for bits in (4, 8):
+        q = restatement.quantize_weight(w, 32, bits)
+        got = _ext.quantized_linear(
+            _dev(x16, cuda), _dev(q['weight'][0].view(np.int32), cuda), _dev(q['scales'][0], cuda),
+            _dev(q['biases'][0], cuda), 192, 96, 32, bits).cpu().numpy()
+        assert _max_rel_err(got, restatement.quantized_matmul(x16, q)) <= FP16_TOL
+    x32 = rng.normal(size=(3000, 20)).astype(np.float32)
+    w32 = rng.normal(size=(33, 20)).astype(np.float32)
+    got = _ext.linear(_dev(x32, cuda), _dev(w32, cuda)).cpu().numpy()
+    assert _max_rel_err(got, restatement.linear(x32, w32)) <= FP32_TOL
+
+    mean = (rng.normal(size=96) * 0.1).astype(np.float16)
+    var = rng.uniform(0.5, 1.5, size=96).astype(np.float16)
+    gamma = np.ones(96, np.float16)
+    beta = np.zeros(96, np.float16)
+    want = restatement.relu(restatement.batch_norm(x16, gamma, beta, mean, var, 1e-5))
+    got = _ext.batch_norm_relu(
+        _dev(x16, cuda), _dev(gamma, cuda), _dev(beta, cuda), _dev(mean, cuda), _dev(var, cuda),
+        1e-5, True).cpu().numpy()
+    assert _max_rel_err(got, want) <= FP16_TOL
+    assert np.array_equal(_ext.relu(_dev(x16, cuda)).cpu().numpy(), restatement.relu(x16))

@@ -1,21 +1,783 @@
-// Tensor-core (tcgen05 + TMEM) route of the sparse-conv contraction. Placeholder
-// dispatch until the kernel lands: reports every shape as unsupported so that the
-// CUDA-core route serves it.
+// Tensor-core route of the sparse-conv contraction: an output-stationary implicit
+// GEMM on tcgen05 with the accumulator in tensor memory (TMEM).
+//
+// One persistent CTA per SM walks 128-row output tiles (rows taken through an
+// optional permutation). For a tile the implicit GEMM is
+//     D[128, C_out] = sum over units u of  A_u[128, 32] * B_u[32, C_out]
+// where a unit is (kernel offset k present in the tile, 32-channel slice h of C_in),
+// A_u holds the gathered feature rows X[in_row(r, k), 32h .. 32h+31] (zero where the
+// output row has no neighbour at k) and B_u the matching weight slice. Two units make
+// one 64-wide K slab = one pipeline stage: A is [128 rows][128 B], B is [C_out rows]
+// [128 B], both K-major with the 128-byte swizzle that tcgen05 shared-memory
+// descriptors name, so a slab is four M128 x N(C_out) x K16 tcgen05.mma instructions.
+// Offsets that no row of the tile uses are skipped entirely.
+//
+// Warp roles (288 threads):
+//   warps 0-3  producers: read the tile's CSR rows into a [128][K] neighbour table,
+//              gather A with 16-byte cp.async (zero-fill for absent neighbours) and
+//              fill B -- cp.async from fp16 weights, or packed int4/int8 codes
+//              dequantised in registers (code*scale + bias) and stored to shared
+//              memory. Completion is published per stage after cp.async.wait_group
+//              and a generic->async proxy fence, lagging the issue by a few stages.
+//   warps 4-7  epilogue: tcgen05.ld the fp32 accumulator (lane = tile row), add the
+//              optional bias, cast once to fp16 and store each output row exactly once
+//              (no atomics, deterministic).
+//   warp 8     TMEM allocation and the single MMA-issuing thread.
+// The accumulator is a ring of up to eight TMEM stages (512 columns / C_out), so the
+// epilogue of a tile overlaps the MMAs of the following ones. Every mbarrier wait is bounded by a clock budget; on expiry the
+// kernel records LAT_STATUS_WAIT_TIMEOUT, all roles drain and the CTA frees its TMEM.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace lat {
 
-bool tc_conv_supported(int, int, int, int, int, int) { return false; }
+namespace {
 
-size_t tc_conv_workspace_bytes(int, int, int) { return 0; }
+constexpr int kTileRows = 128;
+constexpr int kProducerThreads = 128;
+constexpr int kEpilogueThreads = 128;
+constexpr int kThreads = 288;
+constexpr int kMaxKernel = 32;
+constexpr int kNbrStride = kMaxKernel + 1;  // padded against bank conflicts
+constexpr int kMaxStages = 8;
+constexpr int kMaxAccStages = 8;
+constexpr int kSlabBytesA = kTileRows * 128;
+constexpr long long kWaitBudgetCycles = 4000000000LL;  // about two seconds
+
+struct TcParams {
+    const __half* feats;
+    long long feat_stride;
+    int in_capacity;
+    int c_in;
+    int c_out;
+    int n_kernels;
+    // fp16 weights addressed as base + k*w_stride_k + co*w_stride_co + ci
+    const __half* weights;
+    long long w_stride_k;
+    long long w_stride_co;
+    // packed weights
+    const uint32_t* packed;
+    const __half* scales;
+    const __half* qbiases;
+    int words;       // uint32 words per (k, co)
+    int groups;
+    int group_size;
+    const int32_t* in_rows;
+    const int32_t* kernel_ids;
+    const int32_t* row_offsets;
+    const int32_t* counts;
+    int edge_capacity;
+    int out_capacity;
+    const __half* bias;
+    const int32_t* row_order;
+    __half* out;
+    int32_t* status;
+    int stages;
+    int stage_bytes;
+    int tmem_cols;       // allocated columns (power of two >= 32)
+    int acc_cols;        // columns per accumulator stage
+    int acc_stages;      // accumulator stages in TMEM (power of two)
+    int num_tiles;
+};
+
+// ---- PTX wrappers --------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* ptr) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(ptr));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Bounded wait: returns false (and raises the abort flag) when the clock budget is
+// spent or another role already aborted.
+__device__ __forceinline__ bool
+mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
+    if (mbar_try_wait(bar, parity)) {
+        return true;
+    }
+    long long start = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
+        if (*abort_flag != 0) {
+            return false;
+        }
+        if (clock64() - start > kWaitBudgetCycles) {
+            *abort_flag = 1;
+            raise_status(status, LAT_STATUS_WAIT_TIMEOUT);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
+    uint32_t bytes = valid ? 16u : 0u;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void cp_async_commit() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_wait_dynamic(int pending) {
+    switch (pending) {
+    case 0: cp_async_wait<0>(); break;
+    case 1: cp_async_wait<1>(); break;
+    case 2: cp_async_wait<2>(); break;
+    case 3: cp_async_wait<3>(); break;
+    case 4: cp_async_wait<4>(); break;
+    case 5: cp_async_wait<5>(); break;
+    default: cp_async_wait<6>(); break;
+    }
+}
+
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void producer_sync() {
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+// K-major operand tile with 128-byte swizzle: rows are 128 B apart, groups of eight
+// rows 1024 B apart (stride byte offset), leading byte offset unused (encoded 1),
+// descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t desc = 0;
+    desc |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    desc |= static_cast<uint64_t>(1) << 16;
+    desc |= static_cast<uint64_t>(1024 >> 4) << 32;
+    desc |= static_cast<uint64_t>(1) << 46;
+    desc |= static_cast<uint64_t>(2) << 61;
+    return desc;
+}
+
+// kind::f16 instruction descriptor: fp32 accumulate, fp16 A and B, both K-major.
+__device__ __forceinline__ uint32_t make_instr_desc(int m, int n) {
+    uint32_t d = 0;
+    d |= 1u << 4;                                   // D format: F32
+    d |= 0u << 7;                                   // A format: F16
+    d |= 0u << 10;                                  // B format: F16
+    d |= static_cast<uint32_t>(n >> 3) << 17;       // N / 8
+    d |= static_cast<uint32_t>(m >> 4) << 24;       // M / 16
+    return d;
+}
+
+__device__ __forceinline__ void
+umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}"
+        :
+        : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
+          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_16(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---- in-register dequantisation --------------------------------------------------
+
+// eight int4 codes of one word (channel i in nibble i) -> eight fp16 values
+// code*scale + bias, written as one 16-byte vector in channel order
+__device__ __forceinline__ uint4 dequant_int4(uint32_t word, __half2 scale, __half2 bias) {
+    const uint32_t magic = 0x64006400u;  // fp16 1024.0 in both halves
+    const __half2 k1024 = __halves2half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400));
+    uint32_t raw[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        // halves: (nibble i, nibble i + 4), each as 1024 + code
+        raw[i] = ((word >> (4 * i)) & 0x000F000Fu) | magic;
+    }
+    __half2 v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __half2 code = __hsub2(*reinterpret_cast<__half2*>(&raw[i]), k1024);
+        v[i] = __hfma2(code, scale, bias);
+    }
+    uint32_t a = *reinterpret_cast<uint32_t*>(&v[0]);
+    uint32_t b = *reinterpret_cast<uint32_t*>(&v[1]);
+    uint32_t c = *reinterpret_cast<uint32_t*>(&v[2]);
+    uint32_t d = *reinterpret_cast<uint32_t*>(&v[3]);
+    uint4 out;
+    out.x = __byte_perm(a, b, 0x5410);  // channels 0, 1
+    out.y = __byte_perm(c, d, 0x5410);  // channels 2, 3
+    out.z = __byte_perm(a, b, 0x7632);  // channels 4, 5
+    out.w = __byte_perm(c, d, 0x7632);  // channels 6, 7
+    return out;
+}
+
+// four int8 codes of one word (channel i in byte i) -> four fp16 values (8 bytes)
+__device__ __forceinline__ uint2 dequant_int8(uint32_t word, __half2 scale, __half2 bias) {
+    const __half2 k1024 = __halves2half2(__ushort_as_half(0x6400), __ushort_as_half(0x6400));
+    uint32_t lo = __byte_perm(word, 0x64646464u, 0x4140);  // (1024 + b0, 1024 + b1)
+    uint32_t hi = __byte_perm(word, 0x64646464u, 0x4342);  // (1024 + b2, 1024 + b3)
+    __half2 v0 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&lo), k1024), scale, bias);
+    __half2 v1 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&hi), k1024), scale, bias);
+    uint2 out;
+    out.x = *reinterpret_cast<uint32_t*>(&v0);
+    out.y = *reinterpret_cast<uint32_t*>(&v1);
+    return out;
+}
+
+// ---- the kernel ---------------------------------------------------------------
+
+struct SharedControl {
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
+    uint64_t info_full[kMaxAccStages];
+    uint64_t acc_full[kMaxAccStages];
+    uint64_t acc_empty[kMaxAccStages];
+    uint32_t tmem_base;
+    int abort_flag;
+    int tile_slabs[kMaxAccStages];
+    uint32_t tile_mask;
+    int klist[kMaxKernel];
+    int tile_rows[kMaxAccStages][kTileRows];
+    int nbr[kTileRows * kNbrStride];
+};
+
+template <int kBits>
+__global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // stage buffers first (1024-byte aligned for the swizzle atoms), control block after
+    uint8_t* smem = reinterpret_cast<uint8_t*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    SharedControl& ctl = *reinterpret_cast<SharedControl*>(smem + p.stages * p.stage_bytes);
+    volatile int* abort_flag = &ctl.abort_flag;
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int units_per_offset = p.c_in / 32;
+
+    if (tid == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(&ctl.full[s], kProducerThreads);
+            mbar_init(&ctl.empty[s], 1);
+        }
+        for (int a = 0; a < p.acc_stages; ++a) {
+            mbar_init(&ctl.info_full[a], kProducerThreads);
+            mbar_init(&ctl.acc_full[a], 1);
+            mbar_init(&ctl.acc_empty[a], kEpilogueThreads);
+        }
+        ctl.abort_flag = 0;
+        ctl.tile_mask = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(&ctl.tmem_base)),
+                     "r"(static_cast<uint32_t>(p.tmem_cols))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl.tmem_base;
+
+    const int n_out = min(max(__ldg(p.counts + 1), 0), p.out_capacity);
+    const int edge_total = min(max(__ldg(p.counts), 0), p.edge_capacity);
+
+    if (warp < 4) {
+        // ======================= producers =======================
+        // Once a wait gives up (ok == false) a producer keeps walking the tile loop so
+        // that the three named-barrier syncs per tile stay matched, but does no work.
+        const int lag = p.stages - 2;   // stages whose copies may still be in flight
+        int issued = 0;                 // slabs issued by this thread (all tiles)
+        int published = 0;              // slabs whose completion was published
+        bool ok = true;
+        int local_tile = 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++local_tile) {
+            const int a = local_tile % p.acc_stages;
+            const uint32_t acc_parity = ((local_tile / p.acc_stages) & 1) ^ 1;
+            producer_sync();  // everyone is done with the previous tile's tables
+            if (ok && !mbar_try_wait(&ctl.acc_empty[a], acc_parity)) {
+                // The accumulator stage frees up only after earlier tiles ran, and those
+                // need every slab issued so far: publish them before blocking.
+                cp_async_wait<0>();
+                fence_proxy_async();
+                while (published < issued) {
+                    mbar_arrive(&ctl.full[published % p.stages]);
+                    ++published;
+                }
+                ok = mbar_wait(&ctl.acc_empty[a], acc_parity, abort_flag, p.status);
+            }
+            if (!ok) {
+                producer_sync();
+                producer_sync();
+                continue;
+            }
+            // ---- neighbour table of this tile ----
+            int position = tile * kTileRows + tid;
+            int row = -1;
+            if (position < p.out_capacity) {
+                row = p.row_order != nullptr ? __ldg(p.row_order + position) : position;
+                if (row < 0 || row >= p.out_capacity) {
+                    raise_status(p.status, LAT_STATUS_BAD_INDEX);
+                    row = -1;
+                }
+            }
+            ctl.tile_rows[a][tid] = row;
+            int* my_nbr = ctl.nbr + tid * kNbrStride;
+#pragma unroll 8
+            for (int k = 0; k < kMaxKernel; ++k) {
+                my_nbr[k] = -1;
+            }
+            uint32_t mask = 0;
+            if (row >= 0 && row < n_out) {
+                int begin = __ldg(p.row_offsets + row);
+                int end = __ldg(p.row_offsets + row + 1);
+                for (int e = begin; e < end; ++e) {
+                    if (e < 0 || e >= edge_total) {
+                        continue;
+                    }
+                    int in_row = __ldg(p.in_rows + e);
+                    int k = __ldg(p.kernel_ids + e);
+                    if (in_row < 0 || k < 0) {
+                        continue;
+                    }
+                    if (in_row >= p.in_capacity || k >= p.n_kernels) {
+                        raise_status(p.status, LAT_STATUS_BAD_INDEX);
+                        continue;
+                    }
+                    my_nbr[k] = in_row;
+                    mask |= 1u << k;
+                }
+            }
+            mask = __reduce_or_sync(0xffffffffu, mask);
+            if (lane == 0 && mask != 0) {
+                atomicOr(&ctl.tile_mask, mask);
+            }
+            producer_sync();
+            const uint32_t tile_mask = ctl.tile_mask;
+            if (tid < kMaxKernel) {
+                ctl.klist[tid] = static_cast<int>(__fns(tile_mask, 0, tid + 1));
+            }
+            const int units = __popc(tile_mask) * units_per_offset;
+            const int slabs = (units + 1) >> 1;
+            if (tid == 0) {
+                ctl.tile_slabs[a] = slabs;
+            }
+            producer_sync();
+            if (tid == 0) {
+                ctl.tile_mask = 0;  // for the next tile (ordered by the sync at its top)
+            }
+            mbar_arrive(&ctl.info_full[a]);
+
+            // ---- slabs ----
+            for (int s = 0; s < slabs && ok; ++s, ++issued) {
+                const int stage = issued % p.stages;
+                if (!mbar_wait(&ctl.empty[stage], ((issued / p.stages) & 1) ^ 1, abort_flag,
+                               p.status)) {
+                    ok = false;
+                    break;  // `issued` is not advanced for a slab that was never filled
+                }
+                uint8_t* stage_a = smem + stage * p.stage_bytes;
+                uint8_t* stage_b = stage_a + kSlabBytesA;
+                const uint32_t a_addr = smem_u32(stage_a);
+                const uint32_t b_addr = smem_u32(stage_b);
+                // A: thread -> chunk (tid % 8) of rows tid/8 + 16 j
+                {
+                    const int chunk = tid & 7;
+                    const int unit = 2 * s + (chunk >> 2);
+                    const bool unit_valid = unit < units;
+                    const int k = unit_valid ? ctl.klist[unit / units_per_offset] : 0;
+                    const int h = unit_valid ? unit % units_per_offset : 0;
+                    const int col = h * 32 + (chunk & 3) * 8;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int r = (tid >> 3) + 16 * j;
+                        const int in_row = unit_valid ? ctl.nbr[r * kNbrStride + k] : -1;
+                        const bool valid = in_row >= 0;
+                        const __half* src =
+                            p.feats + (valid ? static_cast<size_t>(in_row) * p.feat_stride + col : 0);
+                        cp_async_16(a_addr + r * 128 + ((chunk ^ (r & 7)) << 4), src, valid);
+                    }
+                }
+                // B: [c_out rows][64 channels of the slab]
+                if (kBits == 0) {
+                    const int chunk = tid & 7;
+                    const int unit = 2 * s + (chunk >> 2);
+                    const bool unit_valid = unit < units;
+                    const int k = unit_valid ? ctl.klist[unit / units_per_offset] : 0;
+                    const int h = unit_valid ? unit % units_per_offset : 0;
+                    const __half* base =
+                        p.weights + static_cast<size_t>(k) * p.w_stride_k + h * 32 + (chunk & 3) * 8;
+                    for (int co = tid >> 3; co < p.c_out; co += 16) {
+                        cp_async_16(b_addr + co * 128 + ((chunk ^ (co & 7)) << 4),
+                                    base + static_cast<size_t>(co) * p.w_stride_co, unit_valid);
+                    }
+                } else {
+                    const int total = p.c_out * 8;
+                    for (int idx = tid; idx < total; idx += kProducerThreads) {
+                        const int co = idx % p.c_out;
+                        const int chunk = idx / p.c_out;
+                        const int unit = 2 * s + (chunk >> 2);
+                        uint4 value = make_uint4(0, 0, 0, 0);
+                        if (unit < units) {
+                            const int k = ctl.klist[unit / units_per_offset];
+                            const int h = unit % units_per_offset;
+                            const int ci = h * 32 + (chunk & 3) * 8;
+                            const size_t q =
+                                (static_cast<size_t>(k) * p.groups + ci / p.group_size) * p.c_out + co;
+                            const __half2 scale = __half2half2(__ldg(p.scales + q));
+                            const __half2 qbias = __half2half2(__ldg(p.qbiases + q));
+                            if (kBits == 4) {
+                                const uint32_t word = __ldg(
+                                    p.packed + (static_cast<size_t>(k) * p.words + (ci >> 3)) * p.c_out + co);
+                                value = dequant_int4(word, scale, qbias);
+                            } else {
+                                const size_t w0 =
+                                    (static_cast<size_t>(k) * p.words + (ci >> 2)) * p.c_out + co;
+                                uint2 lo = dequant_int8(__ldg(p.packed + w0), scale, qbias);
+                                uint2 hi = dequant_int8(__ldg(p.packed + w0 + p.c_out), scale, qbias);
+                                value = make_uint4(lo.x, lo.y, hi.x, hi.y);
+                            }
+                        }
+                        *reinterpret_cast<uint4*>(stage_b + co * 128 + ((chunk ^ (co & 7)) << 4)) = value;
+                    }
+                }
+                cp_async_commit();
+                // publish the slab issued `lag` iterations ago
+                if (issued - published >= lag) {
+                    cp_async_wait_dynamic(lag);
+                    fence_proxy_async();
+                    mbar_arrive(&ctl.full[published % p.stages]);
+                    ++published;
+                }
+            }
+        }
+        // drain: publish everything still pending (also on abort, so counts stay sane)
+        cp_async_wait<0>();
+        fence_proxy_async();
+        while (published < issued) {
+            mbar_arrive(&ctl.full[published % p.stages]);
+            ++published;
+        }
+    } else if (warp < 8) {
+        // ======================= epilogue =======================
+        const int ew = warp - 4;          // TMEM lanes 32*ew .. 32*ew + 31
+        const int tile_row = ew * 32 + lane;
+        bool ok = true;
+        int local_tile = 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++local_tile) {
+            const int a = local_tile % p.acc_stages;
+            const uint32_t parity = (local_tile / p.acc_stages) & 1;
+            if (!mbar_wait(&ctl.info_full[a], parity, abort_flag, p.status) ||
+                !mbar_wait(&ctl.acc_full[a], parity, abort_flag, p.status)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const int slabs = ctl.tile_slabs[a];
+            const int row = ctl.tile_rows[a][tile_row];
+            __half* out_row = row >= 0 ? p.out + static_cast<size_t>(row) * p.c_out : nullptr;
+            const uint32_t taddr =
+                tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(a * p.acc_cols);
+            for (int c0 = 0; c0 < p.c_out; c0 += 32) {
+                uint32_t v[32];
+                const int width = min(32, p.c_out - c0);  // 32 or 16
+                if (slabs > 0) {
+                    if (width == 32) {
+                        tmem_load_32(taddr + c0, v);
+                    } else {
+                        tmem_load_16(taddr + c0, v);
+                    }
+                    tmem_load_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        v[i] = 0u;
+                    }
+                }
+                if (out_row != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        if (i < width) {
+                            __half2 h[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                float x = __uint_as_float(v[i + 2 * j]);
+                                float y = __uint_as_float(v[i + 2 * j + 1]);
+                                __half hx = __float2half_rn(x);
+                                __half hy = __float2half_rn(y);
+                                if (p.bias != nullptr) {
+                                    hx = __float2half_rn(__half2float(hx) +
+                                                         __half2float(__ldg(p.bias + c0 + i + 2 * j)));
+                                    hy = __float2half_rn(__half2float(hy) +
+                                                         __half2float(__ldg(p.bias + c0 + i + 2 * j + 1)));
+                                }
+                                h[j] = __halves2half2(hx, hy);
+                            }
+                            *reinterpret_cast<uint4*>(out_row + c0 + i) = *reinterpret_cast<uint4*>(h);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&ctl.acc_empty[a]);
+        }
+    } else if (lane == 0) {
+        // ======================= MMA issuer =======================
+        const uint32_t idesc = make_instr_desc(kTileRows, p.c_out);
+        bool ok = true;
+        int consumed = 0;
+        int local_tile = 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++local_tile) {
+            const int a = local_tile % p.acc_stages;
+            const uint32_t parity = (local_tile / p.acc_stages) & 1;
+            if (!mbar_wait(&ctl.info_full[a], parity, abort_flag, p.status) ||
+                !mbar_wait(&ctl.acc_empty[a], parity ^ 1, abort_flag, p.status)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const int slabs = ctl.tile_slabs[a];
+            const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(a * p.acc_cols);
+            for (int s = 0; s < slabs; ++s, ++consumed) {
+                const int stage = consumed % p.stages;
+                if (!mbar_wait(&ctl.full[stage], (consumed / p.stages) & 1, abort_flag, p.status)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + stage * p.stage_bytes);
+                const uint64_t desc_a = make_smem_desc(a_addr);
+                const uint64_t desc_b = make_smem_desc(a_addr + kSlabBytesA);
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    // 16 fp16 = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
+                    umma_f16(tmem_d, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (s | kk) != 0 ? 1u : 0u);
+                }
+                umma_commit(&ctl.empty[stage]);
+            }
+            if (!ok) {
+                break;
+            }
+            if (slabs > 0) {
+                umma_commit(&ctl.acc_full[a]);
+            } else {
+                mbar_arrive(&ctl.acc_full[a]);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 8) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(static_cast<uint32_t>(p.tmem_cols))
+                     : "memory");
+    }
+}
+
+// fp16 (K, C_in, C_out) -> (K, C_out, C_in) so that B rows are K-major
+__global__ void transpose_weights_kernel(const __half* in, int K, int c_in, int c_out, __half* out) {
+    size_t total = static_cast<size_t>(K) * c_in * c_out;
+    size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (i >= total) {
+        return;
+    }
+    int ci = static_cast<int>(i % c_in);
+    size_t rest = i / c_in;
+    int co = static_cast<int>(rest % c_out);
+    int k = static_cast<int>(rest / c_out);
+    out[i] = in[(static_cast<size_t>(k) * c_in + ci) * c_out + co];
+}
+
+int pow2_at_least(int value, int floor_value) {
+    int out = floor_value;
+    while (out < value) {
+        out <<= 1;
+    }
+    return out;
+}
+
+} // namespace
+
+bool tc_conv_supported(int dtype, int n_kernels, int in_channels, int out_channels,
+                       int quantized_bits, int group_size) {
+    if (dtype != LAT_F16) {
+        return false;
+    }
+    if (n_kernels < 1 || n_kernels > kMaxKernel) {
+        return false;
+    }
+    if (in_channels % 32 != 0 || in_channels < 32) {
+        return false;
+    }
+    if (out_channels % 16 != 0 || out_channels < 16 || out_channels > 256) {
+        return false;
+    }
+    if (quantized_bits != 0) {
+        if (quantized_bits != 4 && quantized_bits != 8) {
+            return false;
+        }
+        if (group_size % 32 != 0) {
+            return false;
+        }
+    }
+    return true;
+}
+
+size_t tc_conv_workspace_bytes(int n_kernels, int in_channels, int out_channels) {
+    return align_up(sizeof(__half) * static_cast<size_t>(std::max(n_kernels, 1)) *
+                    std::max(in_channels, 1) * std::max(out_channels, 1));
+}
 
 int run_tc_conv(
-    const void*, int, int, long long, const void*, int, const uint32_t*, const void*,
-    const void*, int, int, int, int, const int32_t*, const int32_t*, int, const int32_t*,
-    const int32_t*, int, int, const void*, const int32_t*, void*, void*, size_t, int32_t*,
-    cudaStream_t
+    const void* feats, int in_capacity, int in_channels, long long feat_stride,
+    const void* weights, int weight_layout, const uint32_t* packed, const void* scales,
+    const void* biases, int storage_in_channels, int group_size, int bits, int out_channels,
+    const int32_t* in_rows, const int32_t* kernel_ids, int edge_capacity, const int32_t* counts,
+    const int32_t* row_offsets, int out_capacity, int n_kernels, const void* bias,
+    const int32_t* row_order, void* out, void* workspace, size_t workspace_bytes,
+    int32_t* status, cudaStream_t stream
 ) {
-    return fail(LAT_UNSUPPORTED, "tensor-core convolution route is not built.");
+    if (out_capacity == 0) {
+        return LAT_OK;
+    }
+    LAT_REQUIRE(feat_stride % 8 == 0 && reinterpret_cast<uintptr_t>(feats) % 16 == 0,
+                "feature rows must be 16-byte aligned for the tensor-core route.");
+    TcParams p{};
+    p.feats = static_cast<const __half*>(feats);
+    p.feat_stride = feat_stride;
+    p.in_capacity = in_capacity;
+    p.c_in = in_channels;
+    p.c_out = out_channels;
+    p.n_kernels = n_kernels;
+    if (packed == nullptr) {
+        if (weight_layout == LAT_WEIGHT_DENSE_5D) {
+            // (C_out, K, C_in): rows already K-major
+            p.weights = static_cast<const __half*>(weights);
+            p.w_stride_k = in_channels;
+            p.w_stride_co = static_cast<long long>(n_kernels) * in_channels;
+        } else {
+            Workspace ws(workspace, workspace_bytes);
+            size_t total = static_cast<size_t>(n_kernels) * in_channels * out_channels;
+            __half* wt = ws.take<__half>(total);
+            if (!ws.ok) {
+                return fail(LAT_WORKSPACE_TOO_SMALL, "workspace is too small for the convolution.");
+            }
+            transpose_weights_kernel<<<static_cast<int>((total + 255) / 256), 256, 0, stream>>>(
+                static_cast<const __half*>(weights), n_kernels, in_channels, out_channels, wt);
+            LAT_LAUNCH_CHECK();
+            p.weights = wt;
+            p.w_stride_k = static_cast<long long>(out_channels) * in_channels;
+            p.w_stride_co = in_channels;
+        }
+    } else {
+        p.packed = packed;
+        p.scales = static_cast<const __half*>(scales);
+        p.qbiases = static_cast<const __half*>(biases);
+        p.words = storage_in_channels * bits / 32;
+        p.groups = storage_in_channels / group_size;
+        p.group_size = group_size;
+    }
+    p.in_rows = in_rows;
+    p.kernel_ids = kernel_ids;
+    p.row_offsets = row_offsets;
+    p.counts = counts;
+    p.edge_capacity = edge_capacity;
+    p.out_capacity = out_capacity;
+    p.bias = static_cast<const __half*>(bias);
+    p.row_order = row_order;
+    p.out = static_cast<__half*>(out);
+    p.status = status;
+    p.stage_bytes = kSlabBytesA + out_channels * 128;
+    const int smem_budget = 227 * 1024 - 1024 /*alignment slack*/ -
+                            static_cast<int>(sizeof(SharedControl)) - 256;
+    p.stages = std::max(3, std::min(kMaxStages, smem_budget / p.stage_bytes));
+    p.acc_cols = pow2_at_least(out_channels, 32);
+    p.acc_stages = std::min(kMaxAccStages, 512 / p.acc_cols);
+    p.tmem_cols = p.acc_stages * p.acc_cols;
+    p.num_tiles = (out_capacity + kTileRows - 1) / kTileRows;
+    size_t smem_bytes = 1024 + static_cast<size_t>(p.stages) * p.stage_bytes + sizeof(SharedControl);
+
+    int device = 0;
+    LAT_CUDA_CHECK(cudaGetDevice(&device));
+    int sm_count = 0;
+    LAT_CUDA_CHECK(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+    int grid = std::max(1, std::min(p.num_tiles, sm_count));
+    auto kernel = bits == 4 ? tc_conv_kernel<4> : (bits == 8 ? tc_conv_kernel<8> : tc_conv_kernel<0>);
+    LAT_CUDA_CHECK(cudaFuncSetAttribute(
+        kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes)));
+    kernel<<<grid, kThreads, smem_bytes, stream>>>(p);
+    LAT_LAUNCH_CHECK();
+    return LAT_OK;
 }
 
 } // namespace lat

@@ -66,6 +66,9 @@ enum { LAT_JOIN_INNER = 0, LAT_JOIN_LEFT = 1, LAT_JOIN_RIGHT = 2, LAT_JOIN_OUTER
 const char* lat_version(void);
 int lat_capabilities(int32_t* has_sm100, int32_t* device_count);
 const char* lat_last_error(void);
+/* Number of CUDA kernels this library has launched in the process so far (no
+ * reference counterpart; used by the benchmark to report its launch count). */
+long long lat_launch_count(void);
 
 /* native/features/coordinates/offsets.cpp:11-45 (`kernel_offsets`): host helper,
  * writes kernel_volume x 3 int32 to a HOST buffer, x-major / z-fastest. */

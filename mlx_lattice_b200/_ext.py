@@ -127,6 +127,29 @@ def _feats_arg(feats: torch.Tensor) -> tuple[torch.Tensor, int]:
 # --------------------------------------------------------------------------- #
 
 
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(_lib().lat_launch_count())
+
+
+# Optional profiling hook: when set to a callable, every convolution call is
+# bracketed by CUDA events on the current stream and reported to it as
+# hook(kind, info_dict, start_event, end_event). Off (None) on the product path.
+profile_hook = None
+
+
+def _profiled(kind: str, info: dict, call):
+    if profile_hook is None:
+        return call()
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    start.record()
+    out = call()
+    end.record()
+    profile_hook(kind, info, start, end)
+    return out
+
+
 def version() -> str:
     return _lib().lat_version().decode()
 
@@ -526,14 +549,17 @@ def sparse_conv_features(
     out = torch.empty((out_capacity, c_out), dtype=feats.dtype, device=device)
     lib = _lib()
     ws = _workspace(lib.lat_sparse_conv_workspace_bytes(n_kernels, c_in, c_out), device)
+    info = {'c_in': c_in, 'c_out': c_out, 'n_kernels': n_kernels, 'bits': 0, 'counts': counts,
+            'in_rows': int(feats.shape[0]), 'out_rows': out_capacity,
+            'tensor_cores': conv_uses_tensor_cores(feats.dtype, n_kernels, c_in, c_out)}
     with torch.cuda.device(device):
-        check(lib.lat_sparse_conv_features(
+        _profiled('conv', info, lambda: check(lib.lat_sparse_conv_features(
             dtype, _ptr(feats), int(feats.shape[0]), c_in, stride, _ptr(weights), layout, shape,
             c_out, _ptr(in_rows), _ptr(out_rows), _ptr(kernel_ids), int(in_rows.shape[0]),
             _ptr(counts), _ptr(row_offsets), out_capacity, n_kernels, _ptr(bias),
             _ptr(row_order), _ptr(out), _ptr(ws), ws.numel(), _ptr(status_word(device)),
             _stream(),
-        ))
+        )))
     return out
 
 
@@ -582,14 +608,18 @@ def sparse_quantized_conv_features(
     out = torch.empty((out_capacity, out_channels), dtype=feats.dtype, device=device)
     lib = _lib()
     ws = _workspace(lib.lat_sparse_conv_workspace_bytes(n_kernels, in_channels, out_channels), device)
+    info = {'c_in': in_channels, 'c_out': out_channels, 'n_kernels': n_kernels, 'bits': bits,
+            'counts': counts, 'in_rows': int(feats.shape[0]), 'out_rows': out_capacity,
+            'tensor_cores': conv_uses_tensor_cores(
+                feats.dtype, n_kernels, in_channels, out_channels, bits, group_size)}
     with torch.cuda.device(device):
-        check(lib.lat_sparse_quantized_conv_features(
+        _profiled('conv', info, lambda: check(lib.lat_sparse_quantized_conv_features(
             dtype, _ptr(feats), int(feats.shape[0]), stride, _ptr(weights), _ptr(scales),
             _ptr(biases), _ptr(in_rows), _ptr(out_rows), _ptr(kernel_ids),
             int(in_rows.shape[0]), _ptr(counts), _ptr(row_offsets), out_capacity, n_kernels,
             in_channels, out_channels, storage, group_size, bits, _ptr(bias), _ptr(row_order),
             _ptr(out), _ptr(ws), ws.numel(), _ptr(status_word(device)), _stream(),
-        ))
+        )))
     return out
 
 

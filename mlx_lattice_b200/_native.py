@@ -39,6 +39,7 @@ I = c_int32
 SIGNATURES = {
     'lat_version': (c_char_p, []),
     'lat_last_error': (c_char_p, []),
+    'lat_launch_count': (ctypes.c_longlong, []),
     'lat_capabilities': (I, [POINTER(c_int32), POINTER(c_int32)]),
     'lat_kernel_offsets_host': (I, [Triple, Triple, P]),
     'lat_relation_workspace_bytes': (c_size_t, [I, I, I]),

@@ -1,5 +1,6 @@
 // Error plumbing, runtime queries and the dispatch of the two convolution routes.
 #include <algorithm>
+#include <atomic>
 #include <cstring>
 
 #include "common.cuh"
@@ -8,7 +9,10 @@ namespace lat {
 
 namespace {
 thread_local std::string g_last_error;
+std::atomic<long long> g_launches{0};
 }
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 void set_error(const std::string& message) { g_last_error = message; }
 
@@ -49,6 +53,8 @@ extern "C" {
 const char* lat_version(void) { return "0.1.0+b200"; }
 
 const char* lat_last_error(void) { return g_last_error.c_str(); }
+
+long long lat_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int lat_capabilities(int32_t* has_sm100, int32_t* device_count) {
     int count = 0;

@@ -27,7 +27,13 @@ int fail(int code, const std::string& message);
         }                                                                           \
     } while (0)
 
-#define LAT_LAUNCH_CHECK() LAT_CUDA_CHECK(cudaGetLastError())
+// Every kernel launch site is followed by this macro, so it also counts launches.
+void count_launch();
+#define LAT_LAUNCH_CHECK()                                                          \
+    do {                                                                            \
+        ::lat::count_launch();                                                      \
+        LAT_CUDA_CHECK(cudaGetLastError());                                         \
+    } while (0)
 
 #define LAT_REQUIRE(cond, message)                                                  \
     do {                                                                            \

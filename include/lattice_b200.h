@@ -155,7 +155,7 @@ int lat_build_target_transposed_relation(
     const int32_t* target_coords, int32_t target_rows, const int32_t* target_active_rows,
     lat_triple stride,
     int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
-    int32_t* counts,
+    int32_t* counts, int32_t* row_masks /* optional [target_rows, 1] */,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
 /* relations.cpp:438-459 (`make_relation_grouped_view`), algorithm

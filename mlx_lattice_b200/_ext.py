@@ -363,7 +363,7 @@ def build_generative_relation(coords, active_rows, kernel_size, stride):
 
 
 def build_target_transposed_relation_base(
-    coords, active_rows, target_coords, target_active_rows, stride
+    coords, active_rows, target_coords, target_active_rows, stride, *, want_masks=False
 ):
     """Transposed map of a ``kernel_size == stride`` conv restricted to a given
     fine support (one edge per target row at most); see ``include/lattice_b200.h``."""
@@ -376,15 +376,21 @@ def build_target_transposed_relation_base(
     in_rows, out_rows, kernel_ids, row_offsets, _, counts = _relation_buffers(
         target_rows, target_rows, device, with_out_coords=False
     )
+    step = _triple(stride)
+    masks = None
+    if want_masks and step.x * step.y * step.z <= 32:
+        masks = torch.empty((target_rows, 1), dtype=torch.int32, device=device)
     lib = _lib()
     ws = _workspace(lib.lat_relation_workspace_bytes(rows, target_rows, 1), device)
     with torch.cuda.device(device):
         check(lib.lat_build_target_transposed_relation(
             _ptr(coords), rows, _ptr(active_rows), _ptr(target), target_rows,
-            _ptr(target_active), _triple(stride), _ptr(in_rows), _ptr(out_rows),
-            _ptr(kernel_ids), _ptr(row_offsets), _ptr(counts), _ptr(ws), ws.numel(),
+            _ptr(target_active), step, _ptr(in_rows), _ptr(out_rows),
+            _ptr(kernel_ids), _ptr(row_offsets), _ptr(counts), _ptr(masks), _ptr(ws), ws.numel(),
             _ptr(status_word(device)), _stream(),
         ))
+    if want_masks:
+        return (in_rows, out_rows, kernel_ids, row_offsets, target, counts), masks
     return (in_rows, out_rows, kernel_ids, row_offsets, target, counts)
 
 

@@ -55,7 +55,7 @@ SIGNATURES = {
     'lat_build_generative_relation': (
         I, [P, I, P, Triple, Triple, P, P, P, P, P, P, P, c_size_t, P, P]),
     'lat_build_target_transposed_relation': (
-        I, [P, I, P, P, I, P, Triple, P, P, P, P, P, P, c_size_t, P, P]),
+        I, [P, I, P, P, I, P, Triple, P, P, P, P, P, P, P, c_size_t, P, P]),
     'lat_grouped_view_workspace_bytes': (c_size_t, [I, I]),
     'lat_build_relation_grouped_view': (I, [P, I, P, I, P, P, P, c_size_t, P, P]),
     'lat_implicit_gemm_view_workspace_bytes': (c_size_t, [I]),

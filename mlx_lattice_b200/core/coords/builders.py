@@ -257,11 +257,11 @@ def build_target_transposed_relation(
     _require_positive(step, 'stride')
     source_active = _active_rows(active_rows, coords)
     target_active = _active_rows(target_active_rows, target_coords)
-    base = _ext.build_target_transposed_relation_base(
-        coords, source_active, target_coords, target_active, step
+    base, masks = _ext.build_target_transposed_relation_base(
+        coords, source_active, target_coords, target_active, step, want_masks=True
     )
     return _relation(
-        base, None, None,
+        base, masks, None,
         kernel_offsets=kernel_offsets(step),
         n_in_capacity=int(coords.shape[0]),
         out_coords=target_coords,

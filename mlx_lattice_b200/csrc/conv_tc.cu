@@ -1,29 +1,30 @@
 // Tensor-core route of the sparse-conv contraction: an output-stationary implicit
 // GEMM on tcgen05 with the accumulator in tensor memory (TMEM).
 //
-// One persistent CTA per SM walks 128-row output tiles (rows taken through an
+// One persistent CTA per SM walks 256-row output tiles (rows taken through an
 // optional permutation). For a tile the implicit GEMM is
-//     D[128, C_out] = sum over units u of  A_u[128, 32] * B_u[32, C_out]
+//     D[256, C_out] = sum over units u of  A_u[256, 32] * B_u[32, C_out]
 // where a unit is (kernel offset k present in the tile, 32-channel slice h of C_in),
 // A_u holds the gathered feature rows X[in_row(r, k), 32h .. 32h+31] (zero where the
 // output row has no neighbour at k) and B_u the matching weight slice. Two units make
-// one 64-wide K slab = one pipeline stage: A is [128 rows][128 B], B is [C_out rows]
+// one 64-wide K slab = one pipeline stage: A is [256 rows][128 B], B is [C_out rows]
 // [128 B], both K-major with the 128-byte swizzle that tcgen05 shared-memory
-// descriptors name, so a slab is four M128 x N(C_out) x K16 tcgen05.mma instructions.
+// descriptors name, so a slab is eight M128 x N(C_out) x K16 tcgen05.mma instructions
+// (two row halves share every B slab, which halves the weight work per flop).
 // Offsets that no row of the tile uses are skipped entirely.
 //
-// Warp roles (288 threads):
-//   warps 0-3  producers: read the tile's CSR rows into a [128][K] neighbour table,
+// Warp roles (544 threads):
+//   warps 0-7  producers: read the tile's CSR rows into a [256][K] neighbour table,
 //              gather A with 16-byte cp.async (zero-fill for absent neighbours) and
 //              fill B -- cp.async from fp16 weights, or packed int4/int8 codes
-//              dequantised in registers (code*scale + bias) and stored to shared
-//              memory. Completion is published per stage after cp.async.wait_group
+//              dequantised in registers (code*scale + bias; all loads of a slab are
+//              issued before the first conversion) and stored to shared memory. Completion is published per stage after cp.async.wait_group
 //              and a generic->async proxy fence, lagging the issue by a few stages.
-//   warps 4-7  epilogue: tcgen05.ld the fp32 accumulator (lane = tile row), add the
+//   warps 8-15 epilogue: tcgen05.ld the fp32 accumulator (lane = tile row), add the
 //              optional bias, cast once to fp16 and store each output row exactly once
 //              (no atomics, deterministic).
-//   warp 8     TMEM allocation and the single MMA-issuing thread.
-// The accumulator is a ring of up to eight TMEM stages (512 columns / C_out), so the
+//   warp 16    TMEM allocation and the single MMA-issuing thread.
+// The accumulator is a ring of up to eight TMEM stages (512 columns / 2 C_out), so the
 // epilogue of a tile overlaps the MMAs of the following ones. Every mbarrier wait is bounded by a clock budget; on expiry the
 // kernel records LAT_STATUS_WAIT_TIMEOUT, all roles drain and the CTA frees its TMEM.
 #include <algorithm>
@@ -34,13 +35,14 @@ namespace lat {
 
 namespace {
 
-constexpr int kTileRows = 128;
-constexpr int kProducerThreads = 128;
-constexpr int kEpilogueThreads = 128;
-constexpr int kThreads = 288;
+constexpr int kTileRows = 256;
+constexpr int kProducerThreads = 256;
+constexpr int kEpilogueThreads = 256;
+constexpr int kThreads = 544;
+constexpr int kMmaWarp = 16;
 constexpr int kMaxKernel = 32;
-constexpr int kNbrStride = kMaxKernel + 1;  // padded against bank conflicts
 constexpr int kMaxStages = 8;
+constexpr int kMaxTasks = 8;   // B chunks per producer thread and slab (C_out <= 256)
 constexpr int kMaxAccStages = 8;
 constexpr int kSlabBytesA = kTileRows * 128;
 constexpr long long kWaitBudgetCycles = 4000000000LL;  // about two seconds
@@ -79,6 +81,8 @@ struct TcParams {
     int acc_cols;        // columns per accumulator stage
     int acc_stages;      // accumulator stages in TMEM (power of two)
     int num_tiles;
+    int nbr_stride;      // odd stride (in ints) of the neighbour table rows
+    int ctl_bytes;
 };
 
 // ---- PTX wrappers --------------------------------------------------------------
@@ -171,7 +175,7 @@ __device__ __forceinline__ void tc_fence_after() {
 }
 
 __device__ __forceinline__ void producer_sync() {
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync 1, 256;" ::: "memory");
 }
 
 // K-major operand tile with 128-byte swizzle: rows are 128 B apart, groups of eight
@@ -292,6 +296,8 @@ __device__ __forceinline__ uint2 dequant_int8(uint32_t word, __half2 scale, __ha
 
 // ---- the kernel ---------------------------------------------------------------
 
+// Fixed part of the control block; tile_rows[acc_stages][256] and the neighbour table
+// [256][nbr_stride] follow it in shared memory.
 struct SharedControl {
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
@@ -303,8 +309,6 @@ struct SharedControl {
     int tile_slabs[kMaxAccStages];
     uint32_t tile_mask;
     int klist[kMaxKernel];
-    int tile_rows[kMaxAccStages][kTileRows];
-    int nbr[kTileRows * kNbrStride];
 };
 
 template <int kBits>
@@ -313,7 +317,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
     // stage buffers first (1024-byte aligned for the swizzle atoms), control block after
     uint8_t* smem = reinterpret_cast<uint8_t*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    SharedControl& ctl = *reinterpret_cast<SharedControl*>(smem + p.stages * p.stage_bytes);
+    uint8_t* ctl_base = smem + p.stages * p.stage_bytes;
+    SharedControl& ctl = *reinterpret_cast<SharedControl*>(ctl_base);
+    int* tile_rows = reinterpret_cast<int*>(ctl_base + sizeof(SharedControl));  // [acc][256]
+    int* nbr = tile_rows + p.acc_stages * kTileRows;                            // [256][stride]
     volatile int* abort_flag = &ctl.abort_flag;
 
     const int tid = threadIdx.x;
@@ -335,7 +342,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
         ctl.tile_mask = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          smem_u32(&ctl.tmem_base)),
                      "r"(static_cast<uint32_t>(p.tmem_cols))
@@ -350,7 +357,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
     const int n_out = min(max(__ldg(p.counts + 1), 0), p.out_capacity);
     const int edge_total = min(max(__ldg(p.counts), 0), p.edge_capacity);
 
-    if (warp < 4) {
+    if (warp < 8) {
         // ======================= producers =======================
         // Once a wait gives up (ok == false) a producer keeps walking the tile loop so
         // that the three named-barrier syncs per tile stay matched, but does no work.
@@ -359,6 +366,16 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
         int published = 0;              // slabs whose completion was published
         bool ok = true;
         int local_tile = 0;
+        // B chunks this thread fills in every slab: idx = tid + 256 i over [chunk][c_out]
+        const int tasks = (p.c_out * 8 + kProducerThreads - 1) / kProducerThreads;
+        int task_co[kMaxTasks];
+        int task_chunk[kMaxTasks];
+#pragma unroll
+        for (int i = 0; i < kMaxTasks; ++i) {
+            int idx = tid + kProducerThreads * i;
+            task_co[i] = idx % p.c_out;
+            task_chunk[i] = idx / p.c_out;  // >= 8 means no task
+        }
         for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++local_tile) {
             const int a = local_tile % p.acc_stages;
             const uint32_t acc_parity = ((local_tile / p.acc_stages) & 1) ^ 1;
@@ -379,7 +396,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
                 producer_sync();
                 continue;
             }
-            // ---- neighbour table of this tile ----
+            // ---- neighbour table of this tile: one row per producer thread ----
             int position = tile * kTileRows + tid;
             int row = -1;
             if (position < p.out_capacity) {
@@ -389,10 +406,9 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
                     row = -1;
                 }
             }
-            ctl.tile_rows[a][tid] = row;
-            int* my_nbr = ctl.nbr + tid * kNbrStride;
-#pragma unroll 8
-            for (int k = 0; k < kMaxKernel; ++k) {
+            tile_rows[a * kTileRows + tid] = row;
+            int* my_nbr = nbr + tid * p.nbr_stride;
+            for (int k = 0; k < p.n_kernels; ++k) {
                 my_nbr[k] = -1;
             }
             uint32_t mask = 0;
@@ -448,18 +464,25 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
                 uint8_t* stage_b = stage_a + kSlabBytesA;
                 const uint32_t a_addr = smem_u32(stage_a);
                 const uint32_t b_addr = smem_u32(stage_b);
-                // A: thread -> chunk (tid % 8) of rows tid/8 + 16 j
+                // unit (k, h) of each half of the slab
+                int unit_k[2], unit_h[2];
+                bool unit_valid[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int unit = 2 * s + u;
+                    unit_valid[u] = unit < units;
+                    unit_k[u] = unit_valid[u] ? ctl.klist[unit / units_per_offset] : 0;
+                    unit_h[u] = unit_valid[u] ? unit % units_per_offset : 0;
+                }
+                // A: thread -> chunk (tid % 8) of rows tid/8 + 32 j
                 {
                     const int chunk = tid & 7;
-                    const int unit = 2 * s + (chunk >> 2);
-                    const bool unit_valid = unit < units;
-                    const int k = unit_valid ? ctl.klist[unit / units_per_offset] : 0;
-                    const int h = unit_valid ? unit % units_per_offset : 0;
-                    const int col = h * 32 + (chunk & 3) * 8;
+                    const int u = chunk >> 2;
+                    const int col = unit_h[u] * 32 + (chunk & 3) * 8;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        const int r = (tid >> 3) + 16 * j;
-                        const int in_row = unit_valid ? ctl.nbr[r * kNbrStride + k] : -1;
+                        const int r = (tid >> 3) + 32 * j;
+                        const int in_row = unit_valid[u] ? nbr[r * p.nbr_stride + unit_k[u]] : -1;
                         const bool valid = in_row >= 0;
                         const __half* src =
                             p.feats + (valid ? static_cast<size_t>(in_row) * p.feat_stride + col : 0);
@@ -469,44 +492,61 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
                 // B: [c_out rows][64 channels of the slab]
                 if (kBits == 0) {
                     const int chunk = tid & 7;
-                    const int unit = 2 * s + (chunk >> 2);
-                    const bool unit_valid = unit < units;
-                    const int k = unit_valid ? ctl.klist[unit / units_per_offset] : 0;
-                    const int h = unit_valid ? unit % units_per_offset : 0;
-                    const __half* base =
-                        p.weights + static_cast<size_t>(k) * p.w_stride_k + h * 32 + (chunk & 3) * 8;
-                    for (int co = tid >> 3; co < p.c_out; co += 16) {
+                    const int u = chunk >> 2;
+                    const __half* base = p.weights + static_cast<size_t>(unit_k[u]) * p.w_stride_k +
+                                         unit_h[u] * 32 + (chunk & 3) * 8;
+                    for (int co = tid >> 3; co < p.c_out; co += 32) {
                         cp_async_16(b_addr + co * 128 + ((chunk ^ (co & 7)) << 4),
-                                    base + static_cast<size_t>(co) * p.w_stride_co, unit_valid);
+                                    base + static_cast<size_t>(co) * p.w_stride_co, unit_valid[u]);
                     }
                 } else {
-                    const int total = p.c_out * 8;
-                    for (int idx = tid; idx < total; idx += kProducerThreads) {
-                        const int co = idx % p.c_out;
-                        const int chunk = idx / p.c_out;
-                        const int unit = 2 * s + (chunk >> 2);
-                        uint4 value = make_uint4(0, 0, 0, 0);
-                        if (unit < units) {
-                            const int k = ctl.klist[unit / units_per_offset];
-                            const int h = unit % units_per_offset;
-                            const int ci = h * 32 + (chunk & 3) * 8;
-                            const size_t q =
-                                (static_cast<size_t>(k) * p.groups + ci / p.group_size) * p.c_out + co;
-                            const __half2 scale = __half2half2(__ldg(p.scales + q));
-                            const __half2 qbias = __half2half2(__ldg(p.qbiases + q));
-                            if (kBits == 4) {
-                                const uint32_t word = __ldg(
-                                    p.packed + (static_cast<size_t>(k) * p.words + (ci >> 3)) * p.c_out + co);
-                                value = dequant_int4(word, scale, qbias);
-                            } else {
-                                const size_t w0 =
-                                    (static_cast<size_t>(k) * p.words + (ci >> 2)) * p.c_out + co;
-                                uint2 lo = dequant_int8(__ldg(p.packed + w0), scale, qbias);
-                                uint2 hi = dequant_int8(__ldg(p.packed + w0 + p.c_out), scale, qbias);
-                                value = make_uint4(lo.x, lo.y, hi.x, hi.y);
+                    // issue every load of the slab first, convert afterwards
+                    uint32_t w0[kMaxTasks], w1[kMaxTasks];
+                    __half sc[kMaxTasks], qb[kMaxTasks];
+#pragma unroll
+                    for (int i = 0; i < kMaxTasks; ++i) {
+                        w0[i] = 0u;
+                        w1[i] = 0u;
+                        sc[i] = __ushort_as_half(0);
+                        qb[i] = __ushort_as_half(0);
+                        if (i < tasks && task_chunk[i] < 8) {
+                            const int u = task_chunk[i] >> 2;
+                            if (unit_valid[u]) {
+                                const int ci = unit_h[u] * 32 + (task_chunk[i] & 3) * 8;
+                                const int co = task_co[i];
+                                const size_t q = (static_cast<size_t>(unit_k[u]) * p.groups +
+                                                  ci / p.group_size) * p.c_out + co;
+                                sc[i] = __ldg(p.scales + q);
+                                qb[i] = __ldg(p.qbiases + q);
+                                if (kBits == 4) {
+                                    w0[i] = __ldg(p.packed + (static_cast<size_t>(unit_k[u]) * p.words +
+                                                              (ci >> 3)) * p.c_out + co);
+                                } else {
+                                    const size_t w = (static_cast<size_t>(unit_k[u]) * p.words +
+                                                      (ci >> 2)) * p.c_out + co;
+                                    w0[i] = __ldg(p.packed + w);
+                                    w1[i] = __ldg(p.packed + w + p.c_out);
+                                }
                             }
                         }
-                        *reinterpret_cast<uint4*>(stage_b + co * 128 + ((chunk ^ (co & 7)) << 4)) = value;
+                    }
+#pragma unroll
+                    for (int i = 0; i < kMaxTasks; ++i) {
+                        if (i < tasks && task_chunk[i] < 8) {
+                            const __half2 scale = __half2half2(sc[i]);
+                            const __half2 qbias = __half2half2(qb[i]);
+                            uint4 value;
+                            if (kBits == 4) {
+                                value = dequant_int4(w0[i], scale, qbias);
+                            } else {
+                                uint2 lo = dequant_int8(w0[i], scale, qbias);
+                                uint2 hi = dequant_int8(w1[i], scale, qbias);
+                                value = make_uint4(lo.x, lo.y, hi.x, hi.y);
+                            }
+                            const int co = task_co[i];
+                            *reinterpret_cast<uint4*>(
+                                stage_b + co * 128 + ((task_chunk[i] ^ (co & 7)) << 4)) = value;
+                        }
                     }
                 }
                 cp_async_commit();
@@ -526,10 +566,12 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
             mbar_arrive(&ctl.full[published % p.stages]);
             ++published;
         }
-    } else if (warp < 8) {
+    } else if (warp < 16) {
         // ======================= epilogue =======================
-        const int ew = warp - 4;          // TMEM lanes 32*ew .. 32*ew + 31
-        const int tile_row = ew * 32 + lane;
+        const int ew = warp - 8;
+        const int quarter = ew & 3;       // TMEM lanes 32*quarter .. +31 (warp index % 4)
+        const int half_tile = ew >> 2;    // which 128-row half of the tile
+        const int tile_row = half_tile * 128 + quarter * 32 + lane;
         bool ok = true;
         int local_tile = 0;
         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++local_tile) {
@@ -542,10 +584,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
             }
             tc_fence_after();
             const int slabs = ctl.tile_slabs[a];
-            const int row = ctl.tile_rows[a][tile_row];
+            const int row = tile_rows[a * kTileRows + tile_row];
             __half* out_row = row >= 0 ? p.out + static_cast<size_t>(row) * p.c_out : nullptr;
-            const uint32_t taddr =
-                tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(a * p.acc_cols);
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   static_cast<uint32_t>((2 * a + half_tile) * p.acc_cols);
             for (int c0 = 0; c0 < p.c_out; c0 += 32) {
                 uint32_t v[32];
                 const int width = min(32, p.c_out - c0);  // 32 or 16
@@ -569,10 +611,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
                             __half2 h[4];
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
-                                float x = __uint_as_float(v[i + 2 * j]);
-                                float y = __uint_as_float(v[i + 2 * j + 1]);
-                                __half hx = __float2half_rn(x);
-                                __half hy = __float2half_rn(y);
+                                __half hx = __float2half_rn(__uint_as_float(v[i + 2 * j]));
+                                __half hy = __float2half_rn(__uint_as_float(v[i + 2 * j + 1]));
                                 if (p.bias != nullptr) {
                                     hx = __float2half_rn(__half2float(hx) +
                                                          __half2float(__ldg(p.bias + c0 + i + 2 * j)));
@@ -591,7 +631,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
         }
     } else if (lane == 0) {
         // ======================= MMA issuer =======================
-        const uint32_t idesc = make_instr_desc(kTileRows, p.c_out);
+        const uint32_t idesc = make_instr_desc(128, p.c_out);
         bool ok = true;
         int consumed = 0;
         int local_tile = 0;
@@ -605,7 +645,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
             }
             tc_fence_after();
             const int slabs = ctl.tile_slabs[a];
-            const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(a * p.acc_cols);
+            const uint32_t tmem_d0 = tmem_base + static_cast<uint32_t>(2 * a * p.acc_cols);
+            const uint32_t tmem_d1 = tmem_d0 + static_cast<uint32_t>(p.acc_cols);
             for (int s = 0; s < slabs; ++s, ++consumed) {
                 const int stage = consumed % p.stages;
                 if (!mbar_wait(&ctl.full[stage], (consumed / p.stages) & 1, abort_flag, p.status)) {
@@ -614,12 +655,15 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
                 }
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(smem + stage * p.stage_bytes);
-                const uint64_t desc_a = make_smem_desc(a_addr);
+                const uint64_t desc_a0 = make_smem_desc(a_addr);
+                const uint64_t desc_a1 = make_smem_desc(a_addr + 128 * 128);
                 const uint64_t desc_b = make_smem_desc(a_addr + kSlabBytesA);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
                     // 16 fp16 = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
-                    umma_f16(tmem_d, desc_a + 2 * kk, desc_b + 2 * kk, idesc, (s | kk) != 0 ? 1u : 0u);
+                    const uint32_t acc = (s | kk) != 0 ? 1u : 0u;
+                    umma_f16(tmem_d0, desc_a0 + 2 * kk, desc_b + 2 * kk, idesc, acc);
+                    umma_f16(tmem_d1, desc_a1 + 2 * kk, desc_b + 2 * kk, idesc, acc);
                 }
                 umma_commit(&ctl.empty[stage]);
             }
@@ -637,7 +681,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 8) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                      "r"(static_cast<uint32_t>(p.tmem_cols))
                      : "memory");
@@ -758,14 +802,17 @@ int run_tc_conv(
     p.out = static_cast<__half*>(out);
     p.status = status;
     p.stage_bytes = kSlabBytesA + out_channels * 128;
-    const int smem_budget = 227 * 1024 - 1024 /*alignment slack*/ -
-                            static_cast<int>(sizeof(SharedControl)) - 256;
-    p.stages = std::max(3, std::min(kMaxStages, smem_budget / p.stage_bytes));
     p.acc_cols = pow2_at_least(out_channels, 32);
-    p.acc_stages = std::min(kMaxAccStages, 512 / p.acc_cols);
-    p.tmem_cols = p.acc_stages * p.acc_cols;
+    p.acc_stages = std::min(kMaxAccStages, 512 / (2 * p.acc_cols));
+    p.tmem_cols = p.acc_stages * 2 * p.acc_cols;
+    p.nbr_stride = n_kernels | 1;
+    p.ctl_bytes = static_cast<int>(align_up(
+        sizeof(SharedControl) + sizeof(int) * kTileRows * (p.acc_stages + p.nbr_stride), 16));
+    const int smem_budget = 227 * 1024 - 1024 /*alignment slack*/ - p.ctl_bytes;
+    p.stages = std::max(2, std::min(kMaxStages, smem_budget / p.stage_bytes));
     p.num_tiles = (out_capacity + kTileRows - 1) / kTileRows;
-    size_t smem_bytes = 1024 + static_cast<size_t>(p.stages) * p.stage_bytes + sizeof(SharedControl);
+    size_t smem_bytes = 1024 + static_cast<size_t>(p.stages) * p.stage_bytes + p.ctl_bytes;
+    LAT_REQUIRE(smem_bytes <= 227 * 1024, "internal: shared-memory plan exceeds the SM.");
 
     int device = 0;
     LAT_CUDA_CHECK(cudaGetDevice(&device));

@@ -622,7 +622,8 @@ __global__ void target_transposed_fill_kernel(
     const int32_t* target, const int32_t* target_active_ptr, int target_rows,
     int sx, int sy, int sz, int lox, int loy, int loz,
     const int32_t* hit_rows, const int32_t* block_offsets, const int32_t* counts,
-    int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets
+    int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
+    int32_t* row_masks
 ) {
     int active = clamp_count(target_active_ptr, target_rows);
     int row = blockIdx.x * blockDim.x + threadIdx.x;
@@ -640,12 +641,21 @@ __global__ void target_transposed_fill_kernel(
             int ox = t.x - lox - floor_div(t.x - lox, sx) * sx;
             int oy = t.y - loy - floor_div(t.y - loy, sy) * sy;
             int oz = t.z - loz - floor_div(t.z - loz, sz) * sz;
+            int k = (ox * sy + oy) * sz + oz;
             in_rows[pos] = in_row;
             out_rows[pos] = row;
-            kernel_ids[pos] = (ox * sy + oy) * sz + oz;
+            kernel_ids[pos] = k;
+            if (row_masks != nullptr) {
+                row_masks[row] = static_cast<int>(1u << (k & 31));
+            }
+        } else if (row_masks != nullptr) {
+            row_masks[row] = 0;
         }
     } else if (row <= target_rows) {
         row_offsets[row] = edges;
+        if (row_masks != nullptr && row < target_rows) {
+            row_masks[row] = 0;
+        }
     }
 }
 
@@ -1419,10 +1429,13 @@ int lat_build_target_transposed_relation(
     const int32_t* target_coords, int32_t target_rows, const int32_t* target_active_rows,
     lat_triple stride,
     int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
-    int32_t* counts,
+    int32_t* counts, int32_t* row_masks,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream_ptr
 ) {
     int rc = validate_relation_args(coords, rows, active_rows, stride, stride, {0, 0, 0}, {1, 1, 1});
+    if (rc == LAT_OK && row_masks != nullptr && 1LL * stride.x * stride.y * stride.z > 32) {
+        rc = fail(LAT_INVALID_ARGUMENT, "row masks need a kernel volume of at most 32.");
+    }
     if (rc != LAT_OK) {
         return rc;
     }
@@ -1459,7 +1472,7 @@ int lat_build_target_transposed_relation(
     LAT_LAUNCH_CHECK();
     target_transposed_fill_kernel<<<nblocks, kBlockThreads, 0, stream>>>(
         target_coords, target_active_rows, target_rows, stride.x, stride.y, stride.z, lox, loy,
-        loz, hit_rows, sums, counts, in_rows, out_rows, kernel_ids, row_offsets);
+        loz, hit_rows, sums, counts, in_rows, out_rows, kernel_ids, row_offsets, row_masks);
     LAT_LAUNCH_CHECK();
     return LAT_OK;
 }

@@ -12,8 +12,6 @@ from mlx_lattice_b200.core.relations import KernelRelation
 def _row_order(relation: KernelRelation, uses_tensor_cores: bool):
     if not uses_tensor_cores:
         return None
-    if relation.contract.kind not in ('forward', 'target', 'submanifold'):
-        return None
     return relation.require_row_order()
 
 

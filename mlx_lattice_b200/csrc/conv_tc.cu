@@ -75,8 +75,9 @@ struct TcParams {
     const int32_t* row_order;
     __half* out;
     int32_t* status;
-    int stages;
-    int stage_bytes;
+    int a_stages;        // ring of gathered A slabs (32 KB each)
+    int b_stages;        // ring of B slabs (c_out * 128 bytes each)
+    int b_stage_bytes;
     int tmem_cols;       // allocated columns (power of two >= 32)
     int acc_cols;        // columns per accumulator stage
     int acc_stages;      // accumulator stages in TMEM (power of two)
@@ -300,7 +301,8 @@ __device__ __forceinline__ uint2 dequant_int8(uint32_t word, __half2 scale, __ha
 // [256][nbr_stride] follow it in shared memory.
 struct SharedControl {
     uint64_t full[kMaxStages];
-    uint64_t empty[kMaxStages];
+    uint64_t a_empty[kMaxStages];
+    uint64_t b_empty[kMaxStages];
     uint64_t info_full[kMaxAccStages];
     uint64_t acc_full[kMaxAccStages];
     uint64_t acc_empty[kMaxAccStages];
@@ -311,13 +313,14 @@ struct SharedControl {
     int klist[kMaxKernel];
 };
 
-template <int kBits>
+template <int kBits, bool kUniform>
 __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // stage buffers first (1024-byte aligned for the swizzle atoms), control block after
     uint8_t* smem = reinterpret_cast<uint8_t*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint8_t* ctl_base = smem + p.stages * p.stage_bytes;
+    uint8_t* smem_b = smem + p.a_stages * kSlabBytesA;   // B ring after the A ring
+    uint8_t* ctl_base = smem_b + p.b_stages * p.b_stage_bytes;
     SharedControl& ctl = *reinterpret_cast<SharedControl*>(ctl_base);
     int* tile_rows = reinterpret_cast<int*>(ctl_base + sizeof(SharedControl));  // [acc][256]
     int* nbr = tile_rows + p.acc_stages * kTileRows;                            // [256][stride]
@@ -329,9 +332,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
     const int units_per_offset = p.c_in / 32;
 
     if (tid == 0) {
-        for (int s = 0; s < p.stages; ++s) {
+        for (int s = 0; s < kMaxStages; ++s) {
             mbar_init(&ctl.full[s], kProducerThreads);
-            mbar_init(&ctl.empty[s], 1);
+            mbar_init(&ctl.a_empty[s], 1);
+            mbar_init(&ctl.b_empty[s], 1);
         }
         for (int a = 0; a < p.acc_stages; ++a) {
             mbar_init(&ctl.info_full[a], kProducerThreads);
@@ -361,9 +365,12 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
         // ======================= producers =======================
         // Once a wait gives up (ok == false) a producer keeps walking the tile loop so
         // that the three named-barrier syncs per tile stay matched, but does no work.
-        const int lag = p.stages - 2;   // stages whose copies may still be in flight
-        int issued = 0;                 // slabs issued by this thread (all tiles)
-        int published = 0;              // slabs whose completion was published
+        const int ahead_a = p.a_stages - 1;
+        const int ahead_b = kBits == 0 ? p.b_stages - 1 : 0;
+        const int lookahead = ahead_a > ahead_b ? ahead_a : ahead_b;
+        // copies younger than this many steps may still be in flight when a slab is published
+        const int pending = kBits == 0 ? (ahead_a < ahead_b ? ahead_a : ahead_b) : ahead_a;
+        long long slab_base = 0;        // slabs of all earlier tiles of this CTA
         bool ok = true;
         int local_tile = 0;
         // B chunks this thread fills in every slab: idx = tid + 256 i over [chunk][c_out]
@@ -376,19 +383,91 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
             task_co[i] = idx % p.c_out;
             task_chunk[i] = idx / p.c_out;  // >= 8 means no task
         }
+        // per-thread constants of the A gather: rows tid/8 + 32 j, chunk tid % 8
+        const int a_chunk = tid & 7;
+        const int a_half = a_chunk >> 2;
+        uint32_t a_dst[8];
+        int a_nbr[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int r = (tid >> 3) + 32 * j;
+            a_dst[j] = static_cast<uint32_t>(r * 128 + ((a_chunk ^ (r & 7)) << 4));
+            a_nbr[j] = r * p.nbr_stride;
+        }
+        // per-task constants of the B fill
+        uint32_t b_dst[kMaxTasks];
+        int b_src[kMaxTasks];   // (chunk & 3) * words-per-chunk * c_out + co
+#pragma unroll
+        for (int i = 0; i < kMaxTasks; ++i) {
+            b_dst[i] = static_cast<uint32_t>(task_co[i] * 128 + (((task_chunk[i] & 7) ^ (task_co[i] & 7)) << 4));
+            b_src[i] = (task_chunk[i] & 3) * (kBits == 8 ? 2 : 1) * p.c_out + task_co[i];
+        }
+        const int group_shift = p.group_size >= 128 ? 7 : (p.group_size >= 64 ? 6 : 5);
+        // Packed codes of one slab for this thread's B chunks. With kUniform (C_out
+        // divides 256) every chunk of a thread has the same output channel, so two
+        // (scale | bias << 16) words -- one per slab half -- suffice.
+        uint32_t nw0[kMaxTasks], nw1[kMaxTasks], nsb[2], nsbt[kUniform ? 1 : kMaxTasks];
+        int cur_units = 0;
+        auto load_b = [&](int slab) {
+            const uint32_t* wb[2];
+            const __half* sp[2];
+            const __half* bp[2];
+            bool uv[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int unit = 2 * slab + u;
+                uv[u] = unit < cur_units;
+                const int k = uv[u] ? ctl.klist[unit / units_per_offset] : 0;
+                const int ci0 = uv[u] ? (unit % units_per_offset) * 32 : 0;
+                const size_t q = (static_cast<size_t>(k) * p.groups + (ci0 >> group_shift)) * p.c_out;
+                sp[u] = p.scales + q;
+                bp[u] = p.qbiases + q;
+                wb[u] = p.packed + (static_cast<size_t>(k) * p.words +
+                                    (kBits == 4 ? (ci0 >> 3) : (ci0 >> 2))) * p.c_out;
+            }
+            if (kUniform) {
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    nsb[u] = 0u;
+                    if (uv[u]) {
+                        nsb[u] = static_cast<uint32_t>(__half_as_ushort(__ldg(sp[u] + task_co[0]))) |
+                                 (static_cast<uint32_t>(__half_as_ushort(__ldg(bp[u] + task_co[0]))) << 16);
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kMaxTasks; ++i) {
+                nw0[i] = 0u;
+                nw1[i] = 0u;
+                if (!kUniform) {
+                    nsbt[i] = 0u;
+                }
+                if (i < tasks && task_chunk[i] < 8) {
+                    const bool second = (task_chunk[i] & 4) != 0;
+                    if (second ? uv[1] : uv[0]) {
+                        const uint32_t* base = second ? wb[1] : wb[0];
+                        nw0[i] = __ldg(base + b_src[i]);
+                        if (kBits == 8) {
+                            nw1[i] = __ldg(base + b_src[i] + p.c_out);
+                        }
+                        if (!kUniform) {
+                            nsbt[i] =
+                                static_cast<uint32_t>(__half_as_ushort(
+                                    __ldg((second ? sp[1] : sp[0]) + task_co[i]))) |
+                                (static_cast<uint32_t>(__half_as_ushort(
+                                     __ldg((second ? bp[1] : bp[0]) + task_co[i]))) << 16);
+                        }
+                    }
+                }
+            }
+        };
         for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++local_tile) {
             const int a = local_tile % p.acc_stages;
             const uint32_t acc_parity = ((local_tile / p.acc_stages) & 1) ^ 1;
             producer_sync();  // everyone is done with the previous tile's tables
-            if (ok && !mbar_try_wait(&ctl.acc_empty[a], acc_parity)) {
-                // The accumulator stage frees up only after earlier tiles ran, and those
-                // need every slab issued so far: publish them before blocking.
-                cp_async_wait<0>();
-                fence_proxy_async();
-                while (published < issued) {
-                    mbar_arrive(&ctl.full[published % p.stages]);
-                    ++published;
-                }
+            if (ok) {
+                // every slab of the earlier tiles is already published, so this cannot
+                // wait on work that only this thread could release
                 ok = mbar_wait(&ctl.acc_empty[a], acc_parity, abort_flag, p.status);
             }
             if (!ok) {
@@ -451,121 +530,123 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
                 ctl.tile_mask = 0;  // for the next tile (ordered by the sync at its top)
             }
             mbar_arrive(&ctl.info_full[a]);
+            cur_units = units;
+            if (kBits != 0 && kUniform && slabs > 0) {
+                load_b(0);
+            }
 
             // ---- slabs ----
-            for (int s = 0; s < slabs && ok; ++s, ++issued) {
-                const int stage = issued % p.stages;
-                if (!mbar_wait(&ctl.empty[stage], ((issued / p.stages) & 1) ^ 1, abort_flag,
-                               p.status)) {
-                    ok = false;
-                    break;  // `issued` is not advanced for a slab that was never filled
-                }
-                uint8_t* stage_a = smem + stage * p.stage_bytes;
-                uint8_t* stage_b = stage_a + kSlabBytesA;
-                const uint32_t a_addr = smem_u32(stage_a);
-                const uint32_t b_addr = smem_u32(stage_b);
-                // unit (k, h) of each half of the slab
-                int unit_k[2], unit_h[2];
-                bool unit_valid[2];
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int unit = 2 * s + u;
-                    unit_valid[u] = unit < units;
-                    unit_k[u] = unit_valid[u] ? ctl.klist[unit / units_per_offset] : 0;
-                    unit_h[u] = unit_valid[u] ? unit % units_per_offset : 0;
-                }
-                // A: thread -> chunk (tid % 8) of rows tid/8 + 32 j
-                {
-                    const int chunk = tid & 7;
-                    const int u = chunk >> 2;
-                    const int col = unit_h[u] * 32 + (chunk & 3) * 8;
+            // A rows are gathered `ahead_a` slabs before their MMA (the gather latency is
+            // the long one); fp16 B tiles are copied `ahead_b` slabs ahead, quantized B
+            // tiles are converted in the step of their own slab from codes that were
+            // loaded into registers one step earlier. One cp.async group per step.
+            for (int s = -lookahead; s < slabs && ok; ++s) {
+                const int sa = s + ahead_a;
+                if (sa >= 0 && sa < slabs) {
+                    const long long g = slab_base + sa;
+                    const int stage = static_cast<int>(g % p.a_stages);
+                    if (!mbar_wait(&ctl.a_empty[stage], ((g / p.a_stages) & 1) ^ 1, abort_flag,
+                                   p.status)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_addr = smem_u32(smem + stage * kSlabBytesA);
+                    const int unit = 2 * sa + a_half;
+                    const bool uv = unit < units;
+                    const int uk = uv ? ctl.klist[unit / units_per_offset] : 0;
+                    const int uh = uv ? unit % units_per_offset : 0;
+                    const __half* col_base = p.feats + uh * 32 + (a_chunk & 3) * 8;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        const int r = (tid >> 3) + 32 * j;
-                        const int in_row = unit_valid[u] ? nbr[r * p.nbr_stride + unit_k[u]] : -1;
+                        const int in_row = uv ? nbr[a_nbr[j] + uk] : -1;
                         const bool valid = in_row >= 0;
                         const __half* src =
-                            p.feats + (valid ? static_cast<size_t>(in_row) * p.feat_stride + col : 0);
-                        cp_async_16(a_addr + r * 128 + ((chunk ^ (r & 7)) << 4), src, valid);
+                            valid ? col_base + static_cast<size_t>(in_row) * p.feat_stride : p.feats;
+                        cp_async_16(a_addr + a_dst[j], src, valid);
                     }
                 }
-                // B: [c_out rows][64 channels of the slab]
                 if (kBits == 0) {
-                    const int chunk = tid & 7;
-                    const int u = chunk >> 2;
-                    const __half* base = p.weights + static_cast<size_t>(unit_k[u]) * p.w_stride_k +
-                                         unit_h[u] * 32 + (chunk & 3) * 8;
-                    for (int co = tid >> 3; co < p.c_out; co += 32) {
-                        cp_async_16(b_addr + co * 128 + ((chunk ^ (co & 7)) << 4),
-                                    base + static_cast<size_t>(co) * p.w_stride_co, unit_valid[u]);
-                    }
-                } else {
-                    // issue every load of the slab first, convert afterwards
-                    uint32_t w0[kMaxTasks], w1[kMaxTasks];
-                    __half sc[kMaxTasks], qb[kMaxTasks];
-#pragma unroll
-                    for (int i = 0; i < kMaxTasks; ++i) {
-                        w0[i] = 0u;
-                        w1[i] = 0u;
-                        sc[i] = __ushort_as_half(0);
-                        qb[i] = __ushort_as_half(0);
-                        if (i < tasks && task_chunk[i] < 8) {
-                            const int u = task_chunk[i] >> 2;
-                            if (unit_valid[u]) {
-                                const int ci = unit_h[u] * 32 + (task_chunk[i] & 3) * 8;
-                                const int co = task_co[i];
-                                const size_t q = (static_cast<size_t>(unit_k[u]) * p.groups +
-                                                  ci / p.group_size) * p.c_out + co;
-                                sc[i] = __ldg(p.scales + q);
-                                qb[i] = __ldg(p.qbiases + q);
-                                if (kBits == 4) {
-                                    w0[i] = __ldg(p.packed + (static_cast<size_t>(unit_k[u]) * p.words +
-                                                              (ci >> 3)) * p.c_out + co);
-                                } else {
-                                    const size_t w = (static_cast<size_t>(unit_k[u]) * p.words +
-                                                      (ci >> 2)) * p.c_out + co;
-                                    w0[i] = __ldg(p.packed + w);
-                                    w1[i] = __ldg(p.packed + w + p.c_out);
-                                }
-                            }
+                    const int sb = s + ahead_b;
+                    if (sb >= 0 && sb < slabs) {
+                        const long long g = slab_base + sb;
+                        const int stage = static_cast<int>(g % p.b_stages);
+                        if (!mbar_wait(&ctl.b_empty[stage], ((g / p.b_stages) & 1) ^ 1, abort_flag,
+                                       p.status)) {
+                            ok = false;
+                            break;
                         }
-                    }
-#pragma unroll
-                    for (int i = 0; i < kMaxTasks; ++i) {
-                        if (i < tasks && task_chunk[i] < 8) {
-                            const __half2 scale = __half2half2(sc[i]);
-                            const __half2 qbias = __half2half2(qb[i]);
-                            uint4 value;
-                            if (kBits == 4) {
-                                value = dequant_int4(w0[i], scale, qbias);
-                            } else {
-                                uint2 lo = dequant_int8(w0[i], scale, qbias);
-                                uint2 hi = dequant_int8(w1[i], scale, qbias);
-                                value = make_uint4(lo.x, lo.y, hi.x, hi.y);
-                            }
-                            const int co = task_co[i];
-                            *reinterpret_cast<uint4*>(
-                                stage_b + co * 128 + ((task_chunk[i] ^ (co & 7)) << 4)) = value;
+                        const uint32_t b_addr = smem_u32(smem_b + stage * p.b_stage_bytes);
+                        const int unit = 2 * sb + a_half;
+                        const bool uv = unit < units;
+                        const int uk = uv ? ctl.klist[unit / units_per_offset] : 0;
+                        const int uh = uv ? unit % units_per_offset : 0;
+                        const __half* base = p.weights + static_cast<size_t>(uk) * p.w_stride_k +
+                                             uh * 32 + (a_chunk & 3) * 8;
+                        for (int co = tid >> 3; co < p.c_out; co += 32) {
+                            cp_async_16(b_addr + co * 128 + ((a_chunk ^ (co & 7)) << 4),
+                                        base + static_cast<size_t>(co) * p.w_stride_co, uv);
                         }
                     }
                 }
                 cp_async_commit();
-                // publish the slab issued `lag` iterations ago
-                if (issued - published >= lag) {
-                    cp_async_wait_dynamic(lag);
-                    fence_proxy_async();
-                    mbar_arrive(&ctl.full[published % p.stages]);
-                    ++published;
+                if (s < 0) {
+                    continue;
                 }
+                const long long g = slab_base + s;
+                if (kBits != 0) {
+                    const int stage = static_cast<int>(g % p.b_stages);
+                    if (!mbar_wait(&ctl.b_empty[stage], ((g / p.b_stages) & 1) ^ 1, abort_flag,
+                                   p.status)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* stage_b = smem_b + stage * p.b_stage_bytes;
+                    if (!kUniform) {
+                        load_b(s);
+                    }
+                    uint32_t c0[kMaxTasks], c1[kMaxTasks], csb[kUniform ? 2 : kMaxTasks];
+#pragma unroll
+                    for (int i = 0; i < kMaxTasks; ++i) {
+                        c0[i] = nw0[i];
+                        c1[i] = nw1[i];
+                        if (!kUniform) {
+                            csb[i] = nsbt[i];
+                        }
+                    }
+                    if (kUniform) {
+                        csb[0] = nsb[0];
+                        csb[1] = nsb[1];
+                        if (s + 1 < slabs) {
+                            load_b(s + 1);  // in flight while this slab is converted
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < kMaxTasks; ++i) {
+                        if (i < tasks && task_chunk[i] < 8) {
+                            const uint32_t sb =
+                                kUniform ? ((task_chunk[i] & 4) ? csb[1] : csb[0]) : csb[kUniform ? 0 : i];
+                            const __half2 scale = __half2half2(__ushort_as_half(sb & 0xFFFFu));
+                            const __half2 qbias = __half2half2(__ushort_as_half(sb >> 16));
+                            uint4 value;
+                            if (kBits == 4) {
+                                value = dequant_int4(c0[i], scale, qbias);
+                            } else {
+                                uint2 lo = dequant_int8(c0[i], scale, qbias);
+                                uint2 hi = dequant_int8(c1[i], scale, qbias);
+                                value = make_uint4(lo.x, lo.y, hi.x, hi.y);
+                            }
+                            *reinterpret_cast<uint4*>(stage_b + b_dst[i]) = value;
+                        }
+                    }
+                }
+                // slab s is complete once the copies issued up to `pending` steps ago landed
+                cp_async_wait_dynamic(pending);
+                fence_proxy_async();
+                mbar_arrive(&ctl.full[g % kMaxStages]);
             }
+            slab_base += slabs;
         }
-        // drain: publish everything still pending (also on abort, so counts stay sane)
         cp_async_wait<0>();
-        fence_proxy_async();
-        while (published < issued) {
-            mbar_arrive(&ctl.full[published % p.stages]);
-            ++published;
-        }
     } else if (warp < 16) {
         // ======================= epilogue =======================
         const int ew = warp - 8;
@@ -633,7 +714,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
         // ======================= MMA issuer =======================
         const uint32_t idesc = make_instr_desc(128, p.c_out);
         bool ok = true;
-        int consumed = 0;
+        long long consumed = 0;
         int local_tile = 0;
         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++local_tile) {
             const int a = local_tile % p.acc_stages;
@@ -648,16 +729,18 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
             const uint32_t tmem_d0 = tmem_base + static_cast<uint32_t>(2 * a * p.acc_cols);
             const uint32_t tmem_d1 = tmem_d0 + static_cast<uint32_t>(p.acc_cols);
             for (int s = 0; s < slabs; ++s, ++consumed) {
-                const int stage = consumed % p.stages;
-                if (!mbar_wait(&ctl.full[stage], (consumed / p.stages) & 1, abort_flag, p.status)) {
+                if (!mbar_wait(&ctl.full[consumed % kMaxStages], (consumed / kMaxStages) & 1,
+                               abort_flag, p.status)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + stage * p.stage_bytes);
+                const int stage_a = static_cast<int>(consumed % p.a_stages);
+                const int stage_b = static_cast<int>(consumed % p.b_stages);
+                const uint32_t a_addr = smem_u32(smem + stage_a * kSlabBytesA);
                 const uint64_t desc_a0 = make_smem_desc(a_addr);
                 const uint64_t desc_a1 = make_smem_desc(a_addr + 128 * 128);
-                const uint64_t desc_b = make_smem_desc(a_addr + kSlabBytesA);
+                const uint64_t desc_b = make_smem_desc(smem_u32(smem_b + stage_b * p.b_stage_bytes));
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
                     // 16 fp16 = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
@@ -665,7 +748,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
                     umma_f16(tmem_d0, desc_a0 + 2 * kk, desc_b + 2 * kk, idesc, acc);
                     umma_f16(tmem_d1, desc_a1 + 2 * kk, desc_b + 2 * kk, idesc, acc);
                 }
-                umma_commit(&ctl.empty[stage]);
+                umma_commit(&ctl.a_empty[stage_a]);
+                umma_commit(&ctl.b_empty[stage_b]);
             }
             if (!ok) {
                 break;
@@ -801,17 +885,29 @@ int run_tc_conv(
     p.row_order = row_order;
     p.out = static_cast<__half*>(out);
     p.status = status;
-    p.stage_bytes = kSlabBytesA + out_channels * 128;
+    p.b_stage_bytes = out_channels * 128;
     p.acc_cols = pow2_at_least(out_channels, 32);
     p.acc_stages = std::min(kMaxAccStages, 512 / (2 * p.acc_cols));
     p.tmem_cols = p.acc_stages * 2 * p.acc_cols;
     p.nbr_stride = n_kernels | 1;
     p.ctl_bytes = static_cast<int>(align_up(
         sizeof(SharedControl) + sizeof(int) * kTileRows * (p.acc_stages + p.nbr_stride), 16));
+    // keep every B stage on a 1024-byte boundary (the swizzle pattern repeats every
+    // eight 128-byte rows)
+    p.b_stage_bytes = static_cast<int>(align_up(p.b_stage_bytes, 1024));
     const int smem_budget = 227 * 1024 - 1024 /*alignment slack*/ - p.ctl_bytes;
-    p.stages = std::max(2, std::min(kMaxStages, smem_budget / p.stage_bytes));
+    // fp16 B tiles are copied asynchronously and want depth; quantized B tiles are
+    // converted in the step that publishes them and need two stages only
+    p.b_stages = bits == 0 ? 3 : 2;
+    p.a_stages = std::min(6, (smem_budget - p.b_stages * p.b_stage_bytes) / kSlabBytesA);
+    if (p.a_stages < 2) {
+        p.b_stages = 2;
+        p.a_stages = (smem_budget - p.b_stages * p.b_stage_bytes) / kSlabBytesA;
+    }
+    LAT_REQUIRE(p.a_stages >= 2, "internal: shared-memory plan leaves no room for the A ring.");
     p.num_tiles = (out_capacity + kTileRows - 1) / kTileRows;
-    size_t smem_bytes = 1024 + static_cast<size_t>(p.stages) * p.stage_bytes + p.ctl_bytes;
+    size_t smem_bytes = 1024 + static_cast<size_t>(p.a_stages) * kSlabBytesA +
+                        static_cast<size_t>(p.b_stages) * p.b_stage_bytes + p.ctl_bytes;
     LAT_REQUIRE(smem_bytes <= 227 * 1024, "internal: shared-memory plan exceeds the SM.");
 
     int device = 0;
@@ -819,7 +915,10 @@ int run_tc_conv(
     int sm_count = 0;
     LAT_CUDA_CHECK(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
     int grid = std::max(1, std::min(p.num_tiles, sm_count));
-    auto kernel = bits == 4 ? tc_conv_kernel<4> : (bits == 8 ? tc_conv_kernel<8> : tc_conv_kernel<0>);
+    const bool uniform = bits != 0 && kProducerThreads % out_channels == 0;
+    auto kernel = bits == 4 ? (uniform ? tc_conv_kernel<4, true> : tc_conv_kernel<4, false>)
+                : bits == 8 ? (uniform ? tc_conv_kernel<8, true> : tc_conv_kernel<8, false>)
+                            : tc_conv_kernel<0, false>;
     LAT_CUDA_CHECK(cudaFuncSetAttribute(
         kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes)));
     kernel<<<grid, kThreads, smem_bytes, stream>>>(p);

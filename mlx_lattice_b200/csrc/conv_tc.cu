@@ -28,6 +28,7 @@
 // epilogue of a tile overlaps the MMAs of the following ones. Every mbarrier wait is bounded by a clock budget; on expiry the
 // kernel records LAT_STATUS_WAIT_TIMEOUT, all roles drain and the CTA frees its TMEM.
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -82,6 +83,7 @@ struct TcParams {
     int acc_cols;        // columns per accumulator stage
     int acc_stages;      // accumulator stages in TMEM (power of two)
     int num_tiles;
+    int debug_skip;      // experiment switches (0 in normal use)
     int nbr_stride;      // odd stride (in ints) of the neighbour table rows
     int ctl_bytes;
 };
@@ -251,6 +253,20 @@ __device__ __forceinline__ void tmem_load_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Loads whose issue point must stay where it is written (a prefetch one pipeline step
+// ahead of its use): volatile asm is not moved across the surrounding memory operations.
+__device__ __forceinline__ uint32_t ldg_u32_pinned(const uint32_t* ptr) {
+    uint32_t v;
+    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ uint32_t ldg_u16_pinned(const __half* ptr) {
+    uint16_t v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(ptr) : "memory");
+    return v;
+}
+
 // ---- in-register dequantisation --------------------------------------------------
 
 // eight int4 codes of one word (channel i in nibble i) -> eight fp16 values
@@ -296,6 +312,35 @@ __device__ __forceinline__ uint2 dequant_int8(uint32_t word, __half2 scale, __ha
 }
 
 // ---- the kernel ---------------------------------------------------------------
+
+// Ring position kept incrementally: runtime divisions are far too slow for the
+// per-slab loops (they run on the special-function pipe).
+struct Ring {
+    int index;
+    uint32_t phase;
+    __device__ __forceinline__ void advance(int size) {
+        if (++index == size) {
+            index = 0;
+            phase ^= 1u;
+        }
+    }
+};
+
+// Position in the unit list of a tile: unit = (klist[offset], slice) with `per_offset`
+// 32-channel slices per kernel offset.
+struct UnitCursor {
+    int unit;
+    int offset;
+    int slice;
+    __device__ __forceinline__ void advance(int n, int per_offset) {
+        unit += n;
+        slice += n;
+        while (slice >= per_offset) {
+            slice -= per_offset;
+            ++offset;
+        }
+    }
+};
 
 // Fixed part of the control block; tile_rows[acc_stages][256] and the neighbour table
 // [256][nbr_stride] follow it in shared memory.
@@ -365,12 +410,15 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
         // ======================= producers =======================
         // Once a wait gives up (ok == false) a producer keeps walking the tile loop so
         // that the three named-barrier syncs per tile stay matched, but does no work.
-        const int ahead_a = p.a_stages - 1;
-        const int ahead_b = kBits == 0 ? p.b_stages - 1 : 0;
-        const int lookahead = ahead_a > ahead_b ? ahead_a : ahead_b;
-        // copies younger than this many steps may still be in flight when a slab is published
+        // Step s of a tile first publishes slab s and then issues the copies of slab
+        // s + 1 + ahead; the stage those copies overwrite was read by the MMA of slab
+        // s + 1 + ahead - stages = s - 1, i.e. not by the MMA that was just released.
+        const int ahead_a = p.a_stages - 2;
+        const int ahead_b = kBits == 0 ? p.b_stages - 2 : 0;
+        const int lookahead = 1 + (ahead_a > ahead_b ? ahead_a : ahead_b);
+        // groups committed after the copies of slab s and before its publication
         const int pending = kBits == 0 ? (ahead_a < ahead_b ? ahead_a : ahead_b) : ahead_a;
-        long long slab_base = 0;        // slabs of all earlier tiles of this CTA
+        Ring ring_a{0, 0u}, ring_b{0, 0u}, ring_full{0, 0u};   // persist across tiles
         bool ok = true;
         int local_tile = 0;
         // B chunks this thread fills in every slab: idx = tid + 256 i over [chunk][c_out]
@@ -408,30 +456,30 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
         // (scale | bias << 16) words -- one per slab half -- suffice.
         uint32_t nw0[kMaxTasks], nw1[kMaxTasks], nsb[2], nsbt[kUniform ? 1 : kMaxTasks];
         int cur_units = 0;
-        auto load_b = [&](int slab) {
+        auto load_b = [&](UnitCursor cursor) {
             const uint32_t* wb[2];
             const __half* sp[2];
             const __half* bp[2];
             bool uv[2];
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
-                const int unit = 2 * slab + u;
-                uv[u] = unit < cur_units;
-                const int k = uv[u] ? ctl.klist[unit / units_per_offset] : 0;
-                const int ci0 = uv[u] ? (unit % units_per_offset) * 32 : 0;
+                uv[u] = cursor.unit < cur_units;
+                const int k = uv[u] ? ctl.klist[cursor.offset] : 0;
+                const int ci0 = uv[u] ? cursor.slice * 32 : 0;
                 const size_t q = (static_cast<size_t>(k) * p.groups + (ci0 >> group_shift)) * p.c_out;
                 sp[u] = p.scales + q;
                 bp[u] = p.qbiases + q;
                 wb[u] = p.packed + (static_cast<size_t>(k) * p.words +
                                     (kBits == 4 ? (ci0 >> 3) : (ci0 >> 2))) * p.c_out;
+                cursor.advance(1, units_per_offset);
             }
             if (kUniform) {
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
                     nsb[u] = 0u;
                     if (uv[u]) {
-                        nsb[u] = static_cast<uint32_t>(__half_as_ushort(__ldg(sp[u] + task_co[0]))) |
-                                 (static_cast<uint32_t>(__half_as_ushort(__ldg(bp[u] + task_co[0]))) << 16);
+                        nsb[u] = ldg_u16_pinned(sp[u] + task_co[0]) |
+                                 (ldg_u16_pinned(bp[u] + task_co[0]) << 16);
                     }
                 }
             }
@@ -446,16 +494,13 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
                     const bool second = (task_chunk[i] & 4) != 0;
                     if (second ? uv[1] : uv[0]) {
                         const uint32_t* base = second ? wb[1] : wb[0];
-                        nw0[i] = __ldg(base + b_src[i]);
+                        nw0[i] = ldg_u32_pinned(base + b_src[i]);
                         if (kBits == 8) {
-                            nw1[i] = __ldg(base + b_src[i] + p.c_out);
+                            nw1[i] = ldg_u32_pinned(base + b_src[i] + p.c_out);
                         }
                         if (!kUniform) {
-                            nsbt[i] =
-                                static_cast<uint32_t>(__half_as_ushort(
-                                    __ldg((second ? sp[1] : sp[0]) + task_co[i]))) |
-                                (static_cast<uint32_t>(__half_as_ushort(
-                                     __ldg((second ? bp[1] : bp[0]) + task_co[i]))) << 16);
+                            nsbt[i] = ldg_u16_pinned((second ? sp[1] : sp[0]) + task_co[i]) |
+                                      (ldg_u16_pinned((second ? bp[1] : bp[0]) + task_co[i]) << 16);
                         }
                     }
                 }
@@ -531,8 +576,13 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
             }
             mbar_arrive(&ctl.info_full[a]);
             cur_units = units;
+            UnitCursor cur_a{a_half, 0, a_half};     // this thread's half of the A slab to gather
+            cur_a.advance(0, units_per_offset);
+            UnitCursor cur_bf = cur_a;               // fp16 B copies (same half mapping)
+            UnitCursor cur_q{0, 0, 0};               // quantized B: first unit of the slab
             if (kBits != 0 && kUniform && slabs > 0) {
-                load_b(0);
+                load_b(cur_q);
+                cur_q.advance(2, units_per_offset);
             }
 
             // ---- slabs ----
@@ -541,47 +591,108 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
             // tiles are converted in the step of their own slab from codes that were
             // loaded into registers one step earlier. One cp.async group per step.
             for (int s = -lookahead; s < slabs && ok; ++s) {
-                const int sa = s + ahead_a;
-                if (sa >= 0 && sa < slabs) {
-                    const long long g = slab_base + sa;
-                    const int stage = static_cast<int>(g % p.a_stages);
-                    if (!mbar_wait(&ctl.a_empty[stage], ((g / p.a_stages) & 1) ^ 1, abort_flag,
-                                   p.status)) {
-                        ok = false;
-                        break;
-                    }
-                    const uint32_t a_addr = smem_u32(smem + stage * kSlabBytesA);
-                    const int unit = 2 * sa + a_half;
-                    const bool uv = unit < units;
-                    const int uk = uv ? ctl.klist[unit / units_per_offset] : 0;
-                    const int uh = uv ? unit % units_per_offset : 0;
-                    const __half* col_base = p.feats + uh * 32 + (a_chunk & 3) * 8;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int in_row = uv ? nbr[a_nbr[j] + uk] : -1;
-                        const bool valid = in_row >= 0;
-                        const __half* src =
-                            valid ? col_base + static_cast<size_t>(in_row) * p.feat_stride : p.feats;
-                        cp_async_16(a_addr + a_dst[j], src, valid);
-                    }
-                }
-                if (kBits == 0) {
-                    const int sb = s + ahead_b;
-                    if (sb >= 0 && sb < slabs) {
-                        const long long g = slab_base + sb;
-                        const int stage = static_cast<int>(g % p.b_stages);
-                        if (!mbar_wait(&ctl.b_empty[stage], ((g / p.b_stages) & 1) ^ 1, abort_flag,
+                // (1) finish slab s: convert its B tile (quantized weights), make sure its
+                // gathered rows landed, publish it -- before touching any stage that the
+                // MMA of the previous slab may still be reading
+                if (s >= 0) {
+                    if (kBits != 0) {
+                        if (!mbar_wait(&ctl.b_empty[ring_b.index], ring_b.phase ^ 1u, abort_flag,
                                        p.status)) {
                             ok = false;
                             break;
                         }
-                        const uint32_t b_addr = smem_u32(smem_b + stage * p.b_stage_bytes);
-                        const int unit = 2 * sb + a_half;
-                        const bool uv = unit < units;
-                        const int uk = uv ? ctl.klist[unit / units_per_offset] : 0;
-                        const int uh = uv ? unit % units_per_offset : 0;
+                        uint8_t* stage_b = smem_b + ring_b.index * p.b_stage_bytes;
+                        ring_b.advance(p.b_stages);
+                        if (!kUniform) {
+                            load_b(cur_q);
+                            cur_q.advance(2, units_per_offset);
+                        }
+                        if (!(p.debug_skip & 2)) {
+                            uint32_t c0[kMaxTasks], c1[kMaxTasks], csb[kUniform ? 2 : kMaxTasks];
+#pragma unroll
+                            for (int i = 0; i < kMaxTasks; ++i) {
+                                c0[i] = nw0[i];
+                                c1[i] = nw1[i];
+                                if (!kUniform) {
+                                    csb[i] = nsbt[i];
+                                }
+                            }
+                            if (kUniform) {
+                                csb[0] = nsb[0];
+                                csb[1] = nsb[1];
+                                if (s + 1 < slabs) {
+                                    load_b(cur_q);  // in flight while this slab is converted
+                                    cur_q.advance(2, units_per_offset);
+                                }
+                            }
+#pragma unroll
+                            for (int i = 0; i < kMaxTasks; ++i) {
+                                if (i < tasks && task_chunk[i] < 8) {
+                                    const uint32_t sb = kUniform
+                                                            ? ((task_chunk[i] & 4) ? csb[1] : csb[0])
+                                                            : csb[kUniform ? 0 : i];
+                                    const __half2 scale = __half2half2(__ushort_as_half(sb & 0xFFFFu));
+                                    const __half2 qbias = __half2half2(__ushort_as_half(sb >> 16));
+                                    uint4 value;
+                                    if (kBits == 4) {
+                                        value = dequant_int4(c0[i], scale, qbias);
+                                    } else {
+                                        uint2 lo = dequant_int8(c0[i], scale, qbias);
+                                        uint2 hi = dequant_int8(c1[i], scale, qbias);
+                                        value = make_uint4(lo.x, lo.y, hi.x, hi.y);
+                                    }
+                                    *reinterpret_cast<uint4*>(stage_b + b_dst[i]) = value;
+                                }
+                            }
+                        }
+                    }
+                    // the copies of slab s were committed `pending` groups ago
+                    cp_async_wait_dynamic(pending);
+                    fence_proxy_async();
+                    mbar_arrive(&ctl.full[ring_full.index]);
+                    ring_full.advance(kMaxStages);
+                }
+                // (2) run ahead: gather the A rows of slab s + ahead_a (and copy the fp16 B
+                // tile of slab s + ahead_b)
+                const int sa = s + 1 + ahead_a;
+                if (sa >= 0 && sa < slabs) {
+                    if (!mbar_wait(&ctl.a_empty[ring_a.index], ring_a.phase ^ 1u, abort_flag,
+                                   p.status)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_addr = smem_u32(smem + ring_a.index * kSlabBytesA);
+                    ring_a.advance(p.a_stages);
+                    const bool uv = cur_a.unit < units;
+                    const int uk = uv ? ctl.klist[cur_a.offset] : 0;
+                    const __half* col_base = p.feats + (uv ? cur_a.slice : 0) * 32 + (a_chunk & 3) * 8;
+                    cur_a.advance(2, units_per_offset);
+                    if (!(p.debug_skip & 1)) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const int in_row = uv ? nbr[a_nbr[j] + uk] : -1;
+                            const bool valid = in_row >= 0;
+                            const __half* src =
+                                valid ? col_base + static_cast<size_t>(in_row) * p.feat_stride : p.feats;
+                            cp_async_16(a_addr + a_dst[j], src, valid);
+                        }
+                    }
+                }
+                if (kBits == 0) {
+                    const int sb = s + 1 + ahead_b;
+                    if (sb >= 0 && sb < slabs) {
+                        if (!mbar_wait(&ctl.b_empty[ring_b.index], ring_b.phase ^ 1u, abort_flag,
+                                       p.status)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t b_addr = smem_u32(smem_b + ring_b.index * p.b_stage_bytes);
+                        ring_b.advance(p.b_stages);
+                        const bool uv = cur_bf.unit < units;
+                        const int uk = uv ? ctl.klist[cur_bf.offset] : 0;
                         const __half* base = p.weights + static_cast<size_t>(uk) * p.w_stride_k +
-                                             uh * 32 + (a_chunk & 3) * 8;
+                                             (uv ? cur_bf.slice : 0) * 32 + (a_chunk & 3) * 8;
+                        cur_bf.advance(2, units_per_offset);
                         for (int co = tid >> 3; co < p.c_out; co += 32) {
                             cp_async_16(b_addr + co * 128 + ((a_chunk ^ (co & 7)) << 4),
                                         base + static_cast<size_t>(co) * p.w_stride_co, uv);
@@ -589,62 +700,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
                     }
                 }
                 cp_async_commit();
-                if (s < 0) {
-                    continue;
-                }
-                const long long g = slab_base + s;
-                if (kBits != 0) {
-                    const int stage = static_cast<int>(g % p.b_stages);
-                    if (!mbar_wait(&ctl.b_empty[stage], ((g / p.b_stages) & 1) ^ 1, abort_flag,
-                                   p.status)) {
-                        ok = false;
-                        break;
-                    }
-                    uint8_t* stage_b = smem_b + stage * p.b_stage_bytes;
-                    if (!kUniform) {
-                        load_b(s);
-                    }
-                    uint32_t c0[kMaxTasks], c1[kMaxTasks], csb[kUniform ? 2 : kMaxTasks];
-#pragma unroll
-                    for (int i = 0; i < kMaxTasks; ++i) {
-                        c0[i] = nw0[i];
-                        c1[i] = nw1[i];
-                        if (!kUniform) {
-                            csb[i] = nsbt[i];
-                        }
-                    }
-                    if (kUniform) {
-                        csb[0] = nsb[0];
-                        csb[1] = nsb[1];
-                        if (s + 1 < slabs) {
-                            load_b(s + 1);  // in flight while this slab is converted
-                        }
-                    }
-#pragma unroll
-                    for (int i = 0; i < kMaxTasks; ++i) {
-                        if (i < tasks && task_chunk[i] < 8) {
-                            const uint32_t sb =
-                                kUniform ? ((task_chunk[i] & 4) ? csb[1] : csb[0]) : csb[kUniform ? 0 : i];
-                            const __half2 scale = __half2half2(__ushort_as_half(sb & 0xFFFFu));
-                            const __half2 qbias = __half2half2(__ushort_as_half(sb >> 16));
-                            uint4 value;
-                            if (kBits == 4) {
-                                value = dequant_int4(c0[i], scale, qbias);
-                            } else {
-                                uint2 lo = dequant_int8(c0[i], scale, qbias);
-                                uint2 hi = dequant_int8(c1[i], scale, qbias);
-                                value = make_uint4(lo.x, lo.y, hi.x, hi.y);
-                            }
-                            *reinterpret_cast<uint4*>(stage_b + b_dst[i]) = value;
-                        }
-                    }
-                }
-                // slab s is complete once the copies issued up to `pending` steps ago landed
-                cp_async_wait_dynamic(pending);
-                fence_proxy_async();
-                mbar_arrive(&ctl.full[g % kMaxStages]);
             }
-            slab_base += slabs;
         }
         cp_async_wait<0>();
     } else if (warp < 16) {
@@ -714,7 +770,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
         // ======================= MMA issuer =======================
         const uint32_t idesc = make_instr_desc(128, p.c_out);
         bool ok = true;
-        long long consumed = 0;
+        Ring ring_a{0, 0u}, ring_b{0, 0u}, ring_full{0, 0u};
         int local_tile = 0;
         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++local_tile) {
             const int a = local_tile % p.acc_stages;
@@ -728,15 +784,17 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
             const int slabs = ctl.tile_slabs[a];
             const uint32_t tmem_d0 = tmem_base + static_cast<uint32_t>(2 * a * p.acc_cols);
             const uint32_t tmem_d1 = tmem_d0 + static_cast<uint32_t>(p.acc_cols);
-            for (int s = 0; s < slabs; ++s, ++consumed) {
-                if (!mbar_wait(&ctl.full[consumed % kMaxStages], (consumed / kMaxStages) & 1,
-                               abort_flag, p.status)) {
+            for (int s = 0; s < slabs; ++s) {
+                if (!mbar_wait(&ctl.full[ring_full.index], ring_full.phase, abort_flag, p.status)) {
                     ok = false;
                     break;
                 }
+                ring_full.advance(kMaxStages);
                 tc_fence_after();
-                const int stage_a = static_cast<int>(consumed % p.a_stages);
-                const int stage_b = static_cast<int>(consumed % p.b_stages);
+                const int stage_a = ring_a.index;
+                const int stage_b = ring_b.index;
+                ring_a.advance(p.a_stages);
+                ring_b.advance(p.b_stages);
                 const uint32_t a_addr = smem_u32(smem + stage_a * kSlabBytesA);
                 const uint64_t desc_a0 = make_smem_desc(a_addr);
                 const uint64_t desc_a1 = make_smem_desc(a_addr + 128 * 128);
@@ -745,6 +803,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
                 for (int kk = 0; kk < 4; ++kk) {
                     // 16 fp16 = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
                     const uint32_t acc = (s | kk) != 0 ? 1u : 0u;
+                    if (p.debug_skip & 4) continue;
                     umma_f16(tmem_d0, desc_a0 + 2 * kk, desc_b + 2 * kk, idesc, acc);
                     umma_f16(tmem_d1, desc_a1 + 2 * kk, desc_b + 2 * kk, idesc, acc);
                 }
@@ -890,6 +949,9 @@ int run_tc_conv(
     p.acc_stages = std::min(kMaxAccStages, 512 / (2 * p.acc_cols));
     p.tmem_cols = p.acc_stages * 2 * p.acc_cols;
     p.nbr_stride = n_kernels | 1;
+    if (const char* dbg = std::getenv("LAT_TC_DEBUG_SKIP")) {
+        p.debug_skip = std::atoi(dbg);
+    }
     p.ctl_bytes = static_cast<int>(align_up(
         sizeof(SharedControl) + sizeof(int) * kTileRows * (p.acc_stages + p.nbr_stride), 16));
     // keep every B stage on a 1024-byte boundary (the swizzle pattern repeats every
@@ -899,6 +961,9 @@ int run_tc_conv(
     // fp16 B tiles are copied asynchronously and want depth; quantized B tiles are
     // converted in the step that publishes them and need two stages only
     p.b_stages = bits == 0 ? 3 : 2;
+    if (const char* dbg = std::getenv("LAT_TC_B_STAGES")) {
+        p.b_stages = std::atoi(dbg);
+    }
     p.a_stages = std::min(6, (smem_budget - p.b_stages * p.b_stage_bytes) / kSlabBytesA);
     if (p.a_stages < 2) {
         p.b_stages = 2;

@@ -242,11 +242,11 @@ __global__ void compact_winners_kernel(
     }
 }
 
+// (ox, oy, oz) is the spatial offset of the lane's kernel id, computed once per pass
+// (the integer divisions in KernelGeometry::offset are too slow for the row loop)
 __device__ __forceinline__ bool candidate_of(
-    const MapParams& p, Coord out, int k, Coord& cand
+    const MapParams& p, Coord out, int ox, int oy, int oz, Coord& cand
 ) {
-    int ox, oy, oz;
-    p.geo.offset(k, ox, oy, oz);
     if (p.rule == static_cast<int>(MapRule::Forward)) {
         cand = {out.b, out.x * p.sx + ox - p.px, out.y * p.sy + oy - p.py,
                 out.z * p.sz + oz - p.pz};
@@ -280,6 +280,10 @@ __global__ void __launch_bounds__(kBlockThreads) map_count_kernel(MapParams p) {
     for (int pass = 0; pass < p.words; ++pass) {
         int k = pass * 32 + lane;
         int k_hits = 0;
+        int ox = 0, oy = 0, oz = 0;
+        if (k < K) {
+            p.geo.offset(k, ox, oy, oz);
+        }
         for (int j = 0; j < 32; ++j) {
             int row = row0 + j;
             if (row >= n_out) {
@@ -289,7 +293,7 @@ __global__ void __launch_bounds__(kBlockThreads) map_count_kernel(MapParams p) {
                       __shfl_sync(0xffffffffu, mine.y, j), __shfl_sync(0xffffffffu, mine.z, j)};
             bool hit = false;
             Coord cand;
-            if (k < K && candidate_of(p, out, k, cand)) {
+            if (k < K && candidate_of(p, out, ox, oy, oz, cand)) {
                 hit = table_find(p.table, p.table_mask, cand, key_of) >= 0;
             }
             unsigned m = __ballot_sync(0xffffffffu, hit);
@@ -417,6 +421,10 @@ __global__ void __launch_bounds__(kBlockThreads) map_fill_kernel(MapParams p) {
     for (int pass = 0; pass < p.words; ++pass) {
         int k = pass * 32 + lane;
         int k_cursor = (lists && k < K) ? warp_kbase[warp * K + k] : 0;
+        int ox = 0, oy = 0, oz = 0;
+        if (k < K) {
+            p.geo.offset(k, ox, oy, oz);
+        }
         for (int j = 0; j < 32; ++j) {
             int row = row0 + j;
             if (row >= n_out) {
@@ -441,7 +449,7 @@ __global__ void __launch_bounds__(kBlockThreads) map_fill_kernel(MapParams p) {
             if (hit) {
                 Coord out = load_coord(p.out_coords, row);
                 Coord cand;
-                candidate_of(p, out, k, cand);
+                candidate_of(p, out, ox, oy, oz, cand);
                 int in_row = table_find(p.table, p.table_mask, cand, key_of);
                 int pos = start + before + __popc(static_cast<unsigned>(m) & lanemask_lt());
                 if (pos < p.edge_capacity) {

@@ -79,6 +79,7 @@ struct TcParams {
     int a_stages;        // ring of gathered A slabs (32 KB each)
     int b_stages;        // ring of B slabs (c_out * 128 bytes each)
     int b_stage_bytes;
+    int a_stage_bytes;   // 32 KB, plus the B tile when A and B share a stage (fp16 weights)
     int tmem_cols;       // allocated columns (power of two >= 32)
     int acc_cols;        // columns per accumulator stage
     int acc_stages;      // accumulator stages in TMEM (power of two)
@@ -145,24 +146,14 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool 
                  : "memory");
 }
 
-__device__ __forceinline__ void cp_async_commit() {
-    asm volatile("cp.async.commit_group;" ::: "memory");
+// arrive on `bar` once every cp.async this thread has issued so far has landed
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
 }
 
 template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
-__device__ __forceinline__ void cp_async_wait_dynamic(int pending) {
-    switch (pending) {
-    case 0: cp_async_wait<0>(); break;
-    case 1: cp_async_wait<1>(); break;
-    case 2: cp_async_wait<2>(); break;
-    case 3: cp_async_wait<3>(); break;
-    case 4: cp_async_wait<4>(); break;
-    case 5: cp_async_wait<5>(); break;
-    default: cp_async_wait<6>(); break;
-    }
 }
 
 __device__ __forceinline__ void fence_proxy_async() {
@@ -345,7 +336,8 @@ struct UnitCursor {
 // Fixed part of the control block; tile_rows[acc_stages][256] and the neighbour table
 // [256][nbr_stride] follow it in shared memory.
 struct SharedControl {
-    uint64_t full[kMaxStages];
+    uint64_t full_a[kMaxStages];   // A rows (and the fp16 B tile) of a stage landed
+    uint64_t full_b[kMaxStages];   // converted B tile of a stage is written
     uint64_t a_empty[kMaxStages];
     uint64_t b_empty[kMaxStages];
     uint64_t info_full[kMaxAccStages];
@@ -364,7 +356,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
     // stage buffers first (1024-byte aligned for the swizzle atoms), control block after
     uint8_t* smem = reinterpret_cast<uint8_t*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint8_t* smem_b = smem + p.a_stages * kSlabBytesA;   // B ring after the A ring
+    uint8_t* smem_b = smem + p.a_stages * p.a_stage_bytes;   // B ring after the A ring
     uint8_t* ctl_base = smem_b + p.b_stages * p.b_stage_bytes;
     SharedControl& ctl = *reinterpret_cast<SharedControl*>(ctl_base);
     int* tile_rows = reinterpret_cast<int*>(ctl_base + sizeof(SharedControl));  // [acc][256]
@@ -378,7 +370,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
 
     if (tid == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
-            mbar_init(&ctl.full[s], kProducerThreads);
+            mbar_init(&ctl.full_a[s], kProducerThreads);
+            mbar_init(&ctl.full_b[s], kProducerThreads);
             mbar_init(&ctl.a_empty[s], 1);
             mbar_init(&ctl.b_empty[s], 1);
         }
@@ -410,15 +403,9 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
         // ======================= producers =======================
         // Once a wait gives up (ok == false) a producer keeps walking the tile loop so
         // that the three named-barrier syncs per tile stay matched, but does no work.
-        // Step s of a tile first publishes slab s and then issues the copies of slab
-        // s + 1 + ahead; the stage those copies overwrite was read by the MMA of slab
-        // s + 1 + ahead - stages = s - 1, i.e. not by the MMA that was just released.
+        // the stage an A gather overwrites was read two MMAs before the one just released
         const int ahead_a = p.a_stages - 2;
-        const int ahead_b = kBits == 0 ? p.b_stages - 2 : 0;
-        const int lookahead = 1 + (ahead_a > ahead_b ? ahead_a : ahead_b);
-        // groups committed after the copies of slab s and before its publication
-        const int pending = kBits == 0 ? (ahead_a < ahead_b ? ahead_a : ahead_b) : ahead_a;
-        Ring ring_a{0, 0u}, ring_b{0, 0u}, ring_full{0, 0u};   // persist across tiles
+        Ring ring_a{0, 0u}, ring_b{0, 0u};   // persist across tiles
         bool ok = true;
         int local_tile = 0;
         // B chunks this thread fills in every slab: idx = tid + 256 i over [chunk][c_out]
@@ -578,7 +565,6 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
             cur_units = units;
             UnitCursor cur_a{a_half, 0, a_half};     // this thread's half of the A slab to gather
             cur_a.advance(0, units_per_offset);
-            UnitCursor cur_bf = cur_a;               // fp16 B copies (same half mapping)
             UnitCursor cur_q{0, 0, 0};               // quantized B: first unit of the slab
             if (kBits != 0 && kUniform && slabs > 0) {
                 load_b(cur_q);
@@ -590,116 +576,124 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
             // the long one); fp16 B tiles are copied `ahead_b` slabs ahead, quantized B
             // tiles are converted in the step of their own slab from codes that were
             // loaded into registers one step earlier. One cp.async group per step.
-            for (int s = -lookahead; s < slabs && ok; ++s) {
-                // (1) finish slab s: convert its B tile (quantized weights), make sure its
-                // gathered rows landed, publish it -- before touching any stage that the
-                // MMA of the previous slab may still be reading
-                if (s >= 0) {
-                    if (kBits != 0) {
-                        if (!mbar_wait(&ctl.b_empty[ring_b.index], ring_b.phase ^ 1u, abort_flag,
-                                       p.status)) {
-                            ok = false;
-                            break;
-                        }
-                        uint8_t* stage_b = smem_b + ring_b.index * p.b_stage_bytes;
-                        ring_b.advance(p.b_stages);
-                        if (!kUniform) {
-                            load_b(cur_q);
-                            cur_q.advance(2, units_per_offset);
-                        }
-                        if (!(p.debug_skip & 2)) {
-                            uint32_t c0[kMaxTasks], c1[kMaxTasks], csb[kUniform ? 2 : kMaxTasks];
-#pragma unroll
-                            for (int i = 0; i < kMaxTasks; ++i) {
-                                c0[i] = nw0[i];
-                                c1[i] = nw1[i];
-                                if (!kUniform) {
-                                    csb[i] = nsbt[i];
-                                }
-                            }
-                            if (kUniform) {
-                                csb[0] = nsb[0];
-                                csb[1] = nsb[1];
-                                if (s + 1 < slabs) {
-                                    load_b(cur_q);  // in flight while this slab is converted
-                                    cur_q.advance(2, units_per_offset);
-                                }
-                            }
-#pragma unroll
-                            for (int i = 0; i < kMaxTasks; ++i) {
-                                if (i < tasks && task_chunk[i] < 8) {
-                                    const uint32_t sb = kUniform
-                                                            ? ((task_chunk[i] & 4) ? csb[1] : csb[0])
-                                                            : csb[kUniform ? 0 : i];
-                                    const __half2 scale = __half2half2(__ushort_as_half(sb & 0xFFFFu));
-                                    const __half2 qbias = __half2half2(__ushort_as_half(sb >> 16));
-                                    uint4 value;
-                                    if (kBits == 4) {
-                                        value = dequant_int4(c0[i], scale, qbias);
-                                    } else {
-                                        uint2 lo = dequant_int8(c0[i], scale, qbias);
-                                        uint2 hi = dequant_int8(c1[i], scale, qbias);
-                                        value = make_uint4(lo.x, lo.y, hi.x, hi.y);
-                                    }
-                                    *reinterpret_cast<uint4*>(stage_b + b_dst[i]) = value;
-                                }
-                            }
-                        }
-                    }
-                    // the copies of slab s were committed `pending` groups ago
-                    cp_async_wait_dynamic(pending);
-                    fence_proxy_async();
-                    mbar_arrive(&ctl.full[ring_full.index]);
-                    ring_full.advance(kMaxStages);
-                }
-                // (2) run ahead: gather the A rows of slab s + ahead_a (and copy the fp16 B
-                // tile of slab s + ahead_b)
-                const int sa = s + 1 + ahead_a;
-                if (sa >= 0 && sa < slabs) {
+            if (kBits == 0) {
+                // fp16 weights: A rows and the B tile of a slab share one stage; the copies
+                // are asynchronous and signal the stage's barrier themselves when they
+                // land, so this loop only blocks on free stages.
+                for (int s = 0; s < slabs && ok; ++s) {
                     if (!mbar_wait(&ctl.a_empty[ring_a.index], ring_a.phase ^ 1u, abort_flag,
                                    p.status)) {
                         ok = false;
                         break;
                     }
-                    const uint32_t a_addr = smem_u32(smem + ring_a.index * kSlabBytesA);
-                    ring_a.advance(p.a_stages);
+                    const uint32_t a_addr = smem_u32(smem + ring_a.index * p.a_stage_bytes);
+                    const uint32_t b_addr = a_addr + kSlabBytesA;
                     const bool uv = cur_a.unit < units;
                     const int uk = uv ? ctl.klist[cur_a.offset] : 0;
-                    const __half* col_base = p.feats + (uv ? cur_a.slice : 0) * 32 + (a_chunk & 3) * 8;
+                    const int col = (uv ? cur_a.slice : 0) * 32 + (a_chunk & 3) * 8;
                     cur_a.advance(2, units_per_offset);
-                    if (!(p.debug_skip & 1)) {
+                    const __half* col_base = p.feats + col;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const int in_row = uv ? nbr[a_nbr[j] + uk] : -1;
-                            const bool valid = in_row >= 0;
-                            const __half* src =
-                                valid ? col_base + static_cast<size_t>(in_row) * p.feat_stride : p.feats;
-                            cp_async_16(a_addr + a_dst[j], src, valid);
-                        }
+                    for (int j = 0; j < 8; ++j) {
+                        const int in_row = uv ? nbr[a_nbr[j] + uk] : -1;
+                        const bool valid = in_row >= 0;
+                        const __half* src =
+                            valid ? col_base + static_cast<size_t>(in_row) * p.feat_stride : p.feats;
+                        cp_async_16(a_addr + a_dst[j], src, valid);
                     }
+                    const __half* base = p.weights + static_cast<size_t>(uk) * p.w_stride_k + col;
+                    for (int co = tid >> 3; co < p.c_out; co += 32) {
+                        cp_async_16(b_addr + co * 128 + ((a_chunk ^ (co & 7)) << 4),
+                                    base + static_cast<size_t>(co) * p.w_stride_co, uv);
+                    }
+                    cp_async_arrive_noinc(&ctl.full_a[ring_a.index]);
+                    ring_a.advance(p.a_stages);
                 }
-                if (kBits == 0) {
-                    const int sb = s + 1 + ahead_b;
-                    if (sb >= 0 && sb < slabs) {
-                        if (!mbar_wait(&ctl.b_empty[ring_b.index], ring_b.phase ^ 1u, abort_flag,
+            } else {
+                // packed weights: the A gather runs `ahead_a` slabs ahead of the B
+                // conversion, each on its own ring
+                for (int s = -ahead_a; s < slabs && ok; ++s) {
+                    const int sa = s + ahead_a;
+                    if (sa < slabs) {
+                        if (!mbar_wait(&ctl.a_empty[ring_a.index], ring_a.phase ^ 1u, abort_flag,
                                        p.status)) {
                             ok = false;
                             break;
                         }
-                        const uint32_t b_addr = smem_u32(smem_b + ring_b.index * p.b_stage_bytes);
-                        ring_b.advance(p.b_stages);
-                        const bool uv = cur_bf.unit < units;
-                        const int uk = uv ? ctl.klist[cur_bf.offset] : 0;
-                        const __half* base = p.weights + static_cast<size_t>(uk) * p.w_stride_k +
-                                             (uv ? cur_bf.slice : 0) * 32 + (a_chunk & 3) * 8;
-                        cur_bf.advance(2, units_per_offset);
-                        for (int co = tid >> 3; co < p.c_out; co += 32) {
-                            cp_async_16(b_addr + co * 128 + ((a_chunk ^ (co & 7)) << 4),
-                                        base + static_cast<size_t>(co) * p.w_stride_co, uv);
+                        const uint32_t a_addr = smem_u32(smem + ring_a.index * p.a_stage_bytes);
+                        const bool uv = cur_a.unit < units;
+                        const int uk = uv ? ctl.klist[cur_a.offset] : 0;
+                        const __half* col_base =
+                            p.feats + (uv ? cur_a.slice : 0) * 32 + (a_chunk & 3) * 8;
+                        cur_a.advance(2, units_per_offset);
+                        if (!(p.debug_skip & 1)) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const int in_row = uv ? nbr[a_nbr[j] + uk] : -1;
+                                const bool valid = in_row >= 0;
+                                const __half* src = valid ? col_base + static_cast<size_t>(in_row) *
+                                                                           p.feat_stride
+                                                          : p.feats;
+                                cp_async_16(a_addr + a_dst[j], src, valid);
+                            }
+                        }
+                        cp_async_arrive_noinc(&ctl.full_a[ring_a.index]);
+                        ring_a.advance(p.a_stages);
+                    }
+                    if (s < 0) {
+                        continue;
+                    }
+                    if (!mbar_wait(&ctl.b_empty[ring_b.index], ring_b.phase ^ 1u, abort_flag,
+                                   p.status)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* stage_b = smem_b + ring_b.index * p.b_stage_bytes;
+                    if (!kUniform) {
+                        load_b(cur_q);
+                        cur_q.advance(2, units_per_offset);
+                    }
+                    if (!(p.debug_skip & 2)) {
+                        uint32_t c0[kMaxTasks], c1[kMaxTasks], csb[kUniform ? 2 : kMaxTasks];
+#pragma unroll
+                        for (int i = 0; i < kMaxTasks; ++i) {
+                            c0[i] = nw0[i];
+                            c1[i] = nw1[i];
+                            if (!kUniform) {
+                                csb[i] = nsbt[i];
+                            }
+                        }
+                        if (kUniform) {
+                            csb[0] = nsb[0];
+                            csb[1] = nsb[1];
+                            if (s + 1 < slabs) {
+                                load_b(cur_q);  // in flight while this slab is converted
+                                cur_q.advance(2, units_per_offset);
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < kMaxTasks; ++i) {
+                            if (i < tasks && task_chunk[i] < 8) {
+                                const uint32_t sb = kUniform ? ((task_chunk[i] & 4) ? csb[1] : csb[0])
+                                                             : csb[kUniform ? 0 : i];
+                                const __half2 scale = __half2half2(__ushort_as_half(sb & 0xFFFFu));
+                                const __half2 qbias = __half2half2(__ushort_as_half(sb >> 16));
+                                uint4 value;
+                                if (kBits == 4) {
+                                    value = dequant_int4(c0[i], scale, qbias);
+                                } else {
+                                    uint2 lo = dequant_int8(c0[i], scale, qbias);
+                                    uint2 hi = dequant_int8(c1[i], scale, qbias);
+                                    value = make_uint4(lo.x, lo.y, hi.x, hi.y);
+                                }
+                                *reinterpret_cast<uint4*>(stage_b + b_dst[i]) = value;
+                            }
                         }
                     }
+                    fence_proxy_async();  // generic-proxy stores -> visible to the MMA
+                    mbar_arrive(&ctl.full_b[ring_b.index]);
+                    ring_b.advance(p.b_stages);
                 }
-                cp_async_commit();
             }
         }
         cp_async_wait<0>();
@@ -770,7 +764,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
         // ======================= MMA issuer =======================
         const uint32_t idesc = make_instr_desc(128, p.c_out);
         bool ok = true;
-        Ring ring_a{0, 0u}, ring_b{0, 0u}, ring_full{0, 0u};
+        Ring ring_a{0, 0u}, ring_b{0, 0u};
         int local_tile = 0;
         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++local_tile) {
             const int a = local_tile % p.acc_stages;
@@ -785,20 +779,22 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
             const uint32_t tmem_d0 = tmem_base + static_cast<uint32_t>(2 * a * p.acc_cols);
             const uint32_t tmem_d1 = tmem_d0 + static_cast<uint32_t>(p.acc_cols);
             for (int s = 0; s < slabs; ++s) {
-                if (!mbar_wait(&ctl.full[ring_full.index], ring_full.phase, abort_flag, p.status)) {
+                if (!mbar_wait(&ctl.full_a[ring_a.index], ring_a.phase, abort_flag, p.status) ||
+                    (kBits != 0 &&
+                     !mbar_wait(&ctl.full_b[ring_b.index], ring_b.phase, abort_flag, p.status))) {
                     ok = false;
                     break;
                 }
-                ring_full.advance(kMaxStages);
                 tc_fence_after();
                 const int stage_a = ring_a.index;
                 const int stage_b = ring_b.index;
                 ring_a.advance(p.a_stages);
                 ring_b.advance(p.b_stages);
-                const uint32_t a_addr = smem_u32(smem + stage_a * kSlabBytesA);
+                const uint32_t a_addr = smem_u32(smem + stage_a * p.a_stage_bytes);
                 const uint64_t desc_a0 = make_smem_desc(a_addr);
                 const uint64_t desc_a1 = make_smem_desc(a_addr + 128 * 128);
-                const uint64_t desc_b = make_smem_desc(smem_u32(smem_b + stage_b * p.b_stage_bytes));
+                const uint64_t desc_b = make_smem_desc(
+                    kBits == 0 ? a_addr + kSlabBytesA : smem_u32(smem_b + stage_b * p.b_stage_bytes));
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
                     // 16 fp16 = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
@@ -808,7 +804,9 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
                     umma_f16(tmem_d1, desc_a1 + 2 * kk, desc_b + 2 * kk, idesc, acc);
                 }
                 umma_commit(&ctl.a_empty[stage_a]);
-                umma_commit(&ctl.b_empty[stage_b]);
+                if (kBits != 0) {
+                    umma_commit(&ctl.b_empty[stage_b]);
+                }
             }
             if (!ok) {
                 break;
@@ -845,6 +843,31 @@ __global__ void transpose_weights_kernel(const __half* in, int K, int c_in, int 
     out[i] = in[(static_cast<size_t>(k) * c_in + ci) * c_out + co];
 }
 
+// packed int4/int8 (K, S*bits/32, C_out) + scales/biases (K, S/group, C_out) ->
+// fp16 (K, C_out, C_in) = code*scale + bias evaluated in float32 and rounded once
+__global__ void stage_quantized_weights_kernel(
+    const uint32_t* packed, const __half* scales, const __half* biases, int K, int c_in, int c_out,
+    int words, int groups, int group_size, int bits, __half* out
+) {
+    size_t total = static_cast<size_t>(K) * c_in * c_out;
+    size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (i >= total) {
+        return;
+    }
+    // consecutive threads -> consecutive co (coalesced reads); writes are strided
+    int co = static_cast<int>(i % c_out);
+    size_t rest = i / c_out;
+    int ci = static_cast<int>(rest % c_in);
+    int k = static_cast<int>(rest / c_in);
+    int bit = ci * bits;
+    uint32_t word = __ldg(packed + (static_cast<size_t>(k) * words + (bit >> 5)) * c_out + co);
+    uint32_t code = (word >> (bit & 31)) & ((1u << bits) - 1u);
+    size_t q = (static_cast<size_t>(k) * groups + ci / group_size) * c_out + co;
+    float w = fmaf(static_cast<float>(code), __half2float(__ldg(scales + q)),
+                   __half2float(__ldg(biases + q)));
+    out[(static_cast<size_t>(k) * c_out + co) * c_in + ci] = __float2half_rn(w);
+}
+
 int pow2_at_least(int value, int floor_value) {
     int out = floor_value;
     while (out < value) {
@@ -854,6 +877,13 @@ int pow2_at_least(int value, int floor_value) {
 }
 
 } // namespace
+
+// Packed weights reach the B tiles either converted in registers inside the kernel or
+// staged once per call as fp16 (default; LAT_TC_DEQUANT=register selects the former).
+static bool dequant_in_registers() {
+    const char* mode = std::getenv("LAT_TC_DEQUANT");
+    return mode != nullptr && mode[0] == 'r';
+}
 
 bool tc_conv_supported(int dtype, int n_kernels, int in_channels, int out_channels,
                        int quantized_bits, int group_size) {
@@ -926,6 +956,25 @@ int run_tc_conv(
             p.w_stride_k = static_cast<long long>(out_channels) * in_channels;
             p.w_stride_co = in_channels;
         }
+    } else if (!dequant_in_registers()) {
+        // staged route: the whole weight is dequantised to fp16 once per call (a few MB,
+        // L2-resident) and the B tiles are then plain asynchronous copies
+        Workspace ws(workspace, workspace_bytes);
+        size_t total = static_cast<size_t>(n_kernels) * in_channels * out_channels;
+        __half* wt = ws.take<__half>(total);
+        if (!ws.ok) {
+            return fail(LAT_WORKSPACE_TOO_SMALL, "workspace is too small for the convolution.");
+        }
+        stage_quantized_weights_kernel<<<static_cast<int>((total + 255) / 256), 256, 0, stream>>>(
+            packed, static_cast<const __half*>(scales), static_cast<const __half*>(biases),
+            n_kernels, in_channels, out_channels, storage_in_channels * bits / 32,
+            storage_in_channels / group_size, group_size, bits, wt);
+        LAT_LAUNCH_CHECK();
+        p.weights = wt;
+        p.w_stride_k = static_cast<long long>(out_channels) * in_channels;
+        p.w_stride_co = in_channels;
+        packed = nullptr;
+        bits = 0;
     } else {
         p.packed = packed;
         p.scales = static_cast<const __half*>(scales);
@@ -958,20 +1007,22 @@ int run_tc_conv(
     // eight 128-byte rows)
     p.b_stage_bytes = static_cast<int>(align_up(p.b_stage_bytes, 1024));
     const int smem_budget = 227 * 1024 - 1024 /*alignment slack*/ - p.ctl_bytes;
-    // fp16 B tiles are copied asynchronously and want depth; quantized B tiles are
-    // converted in the step that publishes them and need two stages only
-    p.b_stages = bits == 0 ? 3 : 2;
-    if (const char* dbg = std::getenv("LAT_TC_B_STAGES")) {
-        p.b_stages = std::atoi(dbg);
-    }
-    p.a_stages = std::min(6, (smem_budget - p.b_stages * p.b_stage_bytes) / kSlabBytesA);
-    if (p.a_stages < 2) {
+    if (packed == nullptr) {
+        // fp16 weights: one ring, a stage holds the A rows and the B tile
+        p.a_stage_bytes = kSlabBytesA + p.b_stage_bytes;
+        p.b_stages = 0;
+        p.a_stages = std::min(kMaxStages, smem_budget / p.a_stage_bytes);
+    } else {
+        p.a_stage_bytes = kSlabBytesA;
         p.b_stages = 2;
-        p.a_stages = (smem_budget - p.b_stages * p.b_stage_bytes) / kSlabBytesA;
+        if (const char* dbg = std::getenv("LAT_TC_B_STAGES")) {
+            p.b_stages = std::atoi(dbg);
+        }
+        p.a_stages = std::min(kMaxStages, (smem_budget - p.b_stages * p.b_stage_bytes) / kSlabBytesA);
     }
-    LAT_REQUIRE(p.a_stages >= 2, "internal: shared-memory plan leaves no room for the A ring.");
+    LAT_REQUIRE(p.a_stages >= 2, "internal: shared-memory plan leaves no room for the stage ring.");
     p.num_tiles = (out_capacity + kTileRows - 1) / kTileRows;
-    size_t smem_bytes = 1024 + static_cast<size_t>(p.a_stages) * kSlabBytesA +
+    size_t smem_bytes = 1024 + static_cast<size_t>(p.a_stages) * p.a_stage_bytes +
                         static_cast<size_t>(p.b_stages) * p.b_stage_bytes + p.ctl_bytes;
     LAT_REQUIRE(smem_bytes <= 227 * 1024, "internal: shared-memory plan exceeds the SM.");
 

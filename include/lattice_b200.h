@@ -257,10 +257,12 @@ int lat_conv_uses_tensor_cores(int32_t dtype, int32_t n_kernels, int32_t in_chan
 
 /* Row permutation that groups output rows with equal offset masks (the idea of
  * the sorted view, mlx_lattice/core/relations/views.py:467-510, as a native
- * product). row_masks [rows, 1] (K <= 32). row_order [rows]. */
+ * product). row_masks [rows, 1] with bits [0, kernel_count) (K <= 32); rows at or
+ * beyond counts[1] come last. row_order [rows]. */
 size_t lat_mask_order_workspace_bytes(int32_t rows);
 int lat_build_mask_row_order(
-    const int32_t* row_masks, int32_t rows, const int32_t* counts, int32_t* row_order,
+    const int32_t* row_masks, int32_t rows, int32_t kernel_count, const int32_t* counts,
+    int32_t* row_order,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
 /* ---- pooling and pointwise feature ops ---------------------------------- */

@@ -634,7 +634,7 @@ def conv_uses_tensor_cores(dtype, n_kernels, in_channels, out_channels, bits=0, 
         _dtype_code(dtype), n_kernels, in_channels, out_channels, bits, group_size))
 
 
-def build_mask_row_order(row_masks, counts):
+def build_mask_row_order(row_masks, counts, kernel_count: int = 32):
     """Row permutation grouping output rows by equal offset mask (K <= 32)."""
     row_masks = _i32(row_masks, 'row_masks')
     if row_masks.ndim != 2 or row_masks.shape[1] != 1:
@@ -646,7 +646,7 @@ def build_mask_row_order(row_masks, counts):
     ws = _workspace(lib.lat_mask_order_workspace_bytes(rows), device)
     with torch.cuda.device(device):
         check(lib.lat_build_mask_row_order(
-            _ptr(row_masks), rows, _ptr(_i32(counts, 'counts')), _ptr(order), _ptr(ws),
+            _ptr(row_masks), rows, int(kernel_count), _ptr(_i32(counts, 'counts')), _ptr(order), _ptr(ws),
             ws.numel(), _ptr(status_word(device)), _stream(),
         ))
     return order

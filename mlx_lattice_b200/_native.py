@@ -75,7 +75,7 @@ SIGNATURES = {
             c_size_t, P, P]),
     'lat_conv_uses_tensor_cores': (I, [I, I, I, I, I, I]),
     'lat_mask_order_workspace_bytes': (c_size_t, [I]),
-    'lat_build_mask_row_order': (I, [P, I, P, P, P, c_size_t, P, P]),
+    'lat_build_mask_row_order': (I, [P, I, I, P, P, P, c_size_t, P, P]),
     'lat_sparse_pool_features': (
         I, [P, I, I, c_int64, P, P, P, I, P, P, I, I, I, I, P, P, P]),
     'lat_global_pool': (I, [P, I, I, P, I, I, P, P]),

@@ -287,5 +287,7 @@ class KernelRelation:
         if self._row_order is None and self.row_masks is not None and self.row_masks.shape[1] == 1:
             from mlx_lattice_b200 import _ext
 
-            self._row_order = _ext.build_mask_row_order(self.row_masks, self.counts)
+            self._row_order = _ext.build_mask_row_order(
+                self.row_masks, self.counts, int(self.n_kernels or 32)
+            )
         return self._row_order

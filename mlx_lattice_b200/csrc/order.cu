@@ -5,7 +5,8 @@
 // 1024-row chunk histograms, per-digit column scans over the chunks, then a stable
 // scatter that ranks equal digits inside a chunk with warp match/ballot -- integer
 // atomics only on shared counters whose final values do not depend on ordering.
-// Rows at or beyond counts[1] get the key 0xFFFFFFFF and therefore sort last.
+// Rows at or beyond counts[1] get a key above every mask and therefore sort last. Only
+// the digits that can differ are sorted: ceil((K + 1) / 8) passes for K kernel offsets.
 #include <algorithm>
 
 #include "common.cuh"
@@ -19,12 +20,13 @@ constexpr int kBuckets = 256;
 constexpr int kWarps = 8;
 
 __global__ void order_init_kernel(
-    const int32_t* row_masks, int rows, const int32_t* counts, uint32_t* keys, int32_t* perm
+    const int32_t* row_masks, int rows, const int32_t* counts, uint32_t inactive_key,
+    uint32_t* keys, int32_t* perm
 ) {
     int n_out = clamp_count(counts + 1, rows);
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < rows) {
-        keys[i] = i < n_out ? static_cast<uint32_t>(row_masks[i]) : 0xFFFFFFFFu;
+        keys[i] = i < n_out ? static_cast<uint32_t>(row_masks[i]) : inactive_key;
         perm[i] = i;
     }
 }
@@ -149,7 +151,8 @@ size_t lat_mask_order_workspace_bytes(int32_t rows) {
 }
 
 int lat_build_mask_row_order(
-    const int32_t* row_masks, int32_t rows, const int32_t* counts, int32_t* row_order,
+    const int32_t* row_masks, int32_t rows, int32_t kernel_count, const int32_t* counts,
+    int32_t* row_order,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream_ptr
 ) {
     (void)status;
@@ -171,13 +174,18 @@ int lat_build_mask_row_order(
     if (!ws.ok) {
         return fail(LAT_WORKSPACE_TOO_SMALL, "workspace is too small for the row order.");
     }
-    order_init_kernel<<<(rows + 255) / 256, 256, 0, stream>>>(row_masks, rows, counts, keys_a, perm_a);
+    LAT_REQUIRE(kernel_count >= 1 && kernel_count <= 32, "row masks need 1 <= K <= 32.");
+    // masks use bits [0, K); inactive rows get bit K (or all ones when K == 32)
+    const uint32_t inactive_key = kernel_count >= 32 ? 0xFFFFFFFFu : (1u << kernel_count);
+    const int passes = kernel_count >= 32 ? 4 : (kernel_count + 1 + 7) / 8;
+    order_init_kernel<<<(rows + 255) / 256, 256, 0, stream>>>(
+        row_masks, rows, counts, inactive_key, keys_a, perm_a);
     LAT_LAUNCH_CHECK();
-    for (int pass = 0; pass < 4; ++pass) {
+    for (int pass = 0; pass < passes; ++pass) {
         const uint32_t* kin = (pass & 1) ? keys_b : keys_a;
         const int32_t* pin = (pass & 1) ? perm_b : perm_a;
         uint32_t* kout = (pass & 1) ? keys_a : keys_b;
-        int32_t* pout = pass == 3 ? row_order : ((pass & 1) ? perm_a : perm_b);
+        int32_t* pout = pass == passes - 1 ? row_order : ((pass & 1) ? perm_a : perm_b);
         order_hist_kernel<<<blocks, kWarps * 32, 0, stream>>>(kin, rows, pass * 8, hist);
         LAT_LAUNCH_CHECK();
         order_scan_kernel<<<kBuckets, 256, 0, stream>>>(hist, chunks, totals);

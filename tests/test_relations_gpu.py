@@ -239,7 +239,7 @@ def test_row_masks_and_mask_order(cuda, oracle):
     offs = np.asarray(_ext.kernel_offsets(3), np.int32)
     _, want_masks = oracle.implicit_gemm_view(coords, n - 100, coords, n - 100, offs)
     assert np.array_equal(masks.cpu().numpy(), want_masks)
-    order = _ext.build_mask_row_order(masks, base[5]).cpu().numpy()
+    order = _ext.build_mask_row_order(masks, base[5], 27).cpu().numpy()
     assert np.array_equal(np.sort(order), np.arange(n))
     keys = np.where(np.arange(n) < n - 100, want_masks[:, 0].astype(np.uint32), np.uint32(0xFFFFFFFF))
     assert np.array_equal(order, np.argsort(keys, kind='stable'))

@@ -196,6 +196,19 @@ int lat_lookup_coords(
     int32_t* out_rows,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
+/* No counterpart in the reference. The same lookup as lat_lookup_coords for callers
+ * that must not allocate and have no workspace to lend (a host that freezes its device
+ * memory after start-up, a latency-critical loop): the hash table lives in a fixed
+ * 2 MiB __device__ array inside the library instead. At most
+ * lat_lookup_coords_static_max_rows() (262144) source rows; more is an
+ * LAT_INVALID_ARGUMENT. The array is shared by all calls: calls that overlap on the
+ * GPU race, so serialise them. The first call on a device looks up the array's address;
+ * make it before any stream capture. */
+int32_t lat_lookup_coords_static_max_rows(void);
+int lat_lookup_coords_static(
+    const int32_t* coords, int32_t rows, const int32_t* queries, int32_t query_rows,
+    int32_t* out_rows, int32_t* status, void* stream);
+
 /* native/bindings/coords.cpp:191-222 (`build_sparse_alignment`) ->
  * native/features/coordinates/lookup.cpp:111-146; algorithm
  * cpu/set_neighbors_detail.h:59-136. Output capacity: lhs_rows (inner, left),

@@ -476,6 +476,30 @@ def lookup_coords(coords, queries):
     return out
 
 
+def lookup_coords_static(coords, queries, out: torch.Tensor | None = None):
+    """``lookup_coords`` without any scratch allocation: the hash table is a fixed
+    array inside the library (at most ``lookup_coords_static_max_rows()`` source rows).
+    For callers that may not allocate; pass ``out`` (int32, one entry per query) to
+    avoid even the result allocation. Calls share the table, so do not overlap them."""
+    coords = _coords_arg(coords)
+    queries = _coords_arg(queries, 'queries')
+    device = coords.device
+    if out is None:
+        out = torch.empty(queries.shape[0], dtype=torch.int32, device=device)
+    elif out.dtype != torch.int32 or out.numel() != queries.shape[0] or not out.is_contiguous():
+        raise ValueError('out must be a contiguous int32 tensor with one entry per query.')
+    with torch.cuda.device(device):
+        check(_lib().lat_lookup_coords_static(
+            _ptr(coords), int(coords.shape[0]), _ptr(queries), int(queries.shape[0]), _ptr(out),
+            _ptr(status_word(device)), _stream(),
+        ))
+    return out
+
+
+def lookup_coords_static_max_rows() -> int:
+    return int(_lib().lat_lookup_coords_static_max_rows())
+
+
 def build_sparse_alignment(lhs_coords, lhs_active_rows, rhs_coords, rhs_active_rows, join):
     """Returns (coords, active_rows [1], lhs_rows, rhs_rows)
     (``coords.cpp:191-222``)."""

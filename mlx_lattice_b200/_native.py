@@ -64,6 +64,8 @@ SIGNATURES = {
     'lat_coord_set_workspace_bytes': (c_size_t, [I]),
     'lat_downsample_coords': (I, [P, I, Triple, P, P, P, c_size_t, P, P]),
     'lat_lookup_coords': (I, [P, I, P, I, P, P, c_size_t, P, P]),
+    'lat_lookup_coords_static_max_rows': (I, []),
+    'lat_lookup_coords_static': (I, [P, I, P, I, P, P, P]),
     'lat_sparse_alignment_workspace_bytes': (c_size_t, [I, I]),
     'lat_build_sparse_alignment': (I, [P, I, P, P, I, P, I, P, P, P, P, P, c_size_t, P, P]),
     'lat_sparse_conv_workspace_bytes': (c_size_t, [I, I, I]),

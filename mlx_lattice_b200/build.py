@@ -20,6 +20,7 @@ SOURCES = (
     'conv_direct.cu',
     'conv_tc.cu',
     'order.cu',
+    'static_scratch.cu',
     'pool.cu',
     'feature.cu',
     'capi.cu',

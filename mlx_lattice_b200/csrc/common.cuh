@@ -163,7 +163,83 @@ __device__ __forceinline__ int warp_exclusive_scan(int v, int& total) {
     return inc - v;
 }
 
-// ---- open-addressing table of row ids -------------------------------------------
+// ---- open-addressing table: 8-byte slots (tag << 32 | row) ---------------------------
+//
+// slots[capacity] (capacity a power of two) hold (tag << 32) | row or kEmptySlot. The
+// tag is the upper half of a 64-bit hash of the key, the slot index its lower bits; a
+// probe compares tags first and loads the stored row's coordinate only on a tag match,
+// so a miss costs slot reads only. Equal keys keep the smallest row id (first row
+// wins, like the reference's first_row_map, coordinates/cpu/quantization_detail.h:
+// 394-402): equal keys have equal tags, so a 64-bit atomicMin on the slot is a min
+// over the row ids. Linear probing: consecutive slots share 32-byte sectors.
+using Slot = unsigned long long;
+constexpr Slot kEmptySlot = ~0ull;
+
+__device__ __forceinline__ unsigned long long hash_coord64(Coord c) {
+    unsigned long long k0 =
+        (static_cast<unsigned long long>(static_cast<uint32_t>(c.b)) << 32) | static_cast<uint32_t>(c.x);
+    unsigned long long k1 =
+        (static_cast<unsigned long long>(static_cast<uint32_t>(c.y)) << 32) | static_cast<uint32_t>(c.z);
+    unsigned long long h = k0 * 0x9E3779B97F4A7C15ull;
+    h ^= h >> 32;
+    h = (h ^ k1) * 0xC2B2AE3D27D4EB4Full;
+    h ^= h >> 29;
+    h *= 0x165667B19E3779F9ull;
+    h ^= h >> 32;
+    return h;
+}
+
+template <typename KeyOf>
+__device__ __forceinline__ bool
+table_insert(Slot* slots, uint32_t mask, int row, Coord key, KeyOf key_of, bool* met_duplicate) {
+    const unsigned long long h = hash_coord64(key);
+    const Slot tag = h & 0xFFFFFFFF00000000ull;
+    const Slot want = tag | static_cast<uint32_t>(row);
+    uint32_t slot = static_cast<uint32_t>(h) & mask;
+    for (uint32_t probe = 0; probe <= mask; ++probe) {
+        Slot cur = *reinterpret_cast<volatile Slot*>(slots + slot);
+        if (cur == kEmptySlot) {
+            Slot old = atomicCAS(slots + slot, kEmptySlot, want);
+            if (old == kEmptySlot) {
+                return true;
+            }
+            cur = old;
+        }
+        if ((cur & 0xFFFFFFFF00000000ull) == tag && key_of(static_cast<int>(cur & 0xFFFFFFFFu)) == key) {
+            atomicMin(slots + slot, want);
+            if (met_duplicate != nullptr) {
+                *met_duplicate = true;
+            }
+            return true;
+        }
+        slot = (slot + 1) & mask;
+    }
+    return false;
+}
+
+template <typename KeyOf>
+__device__ __forceinline__ int
+table_find(const Slot* slots, uint32_t mask, Coord key, KeyOf key_of) {
+    const unsigned long long h = hash_coord64(key);
+    const Slot tag = h & 0xFFFFFFFF00000000ull;
+    uint32_t slot = static_cast<uint32_t>(h) & mask;
+    for (uint32_t probe = 0; probe <= mask; ++probe) {
+        Slot cur = __ldg(slots + slot);
+        if (cur == kEmptySlot) {
+            return -1;
+        }
+        if ((cur & 0xFFFFFFFF00000000ull) == tag) {
+            int row = static_cast<int>(cur & 0xFFFFFFFFu);
+            if (key_of(row) == key) {
+                return row;
+            }
+        }
+        slot = (slot + 1) & mask;
+    }
+    return -1;
+}
+
+// ---- 4-byte-slot variant (row ids only) -------------------------------------------
 //
 // slots[capacity] (capacity a power of two) hold a row id or -1. The key of a slot
 // is whatever `key_of(row)` says for the stored row, so the table itself stays
@@ -172,7 +248,7 @@ __device__ __forceinline__ int warp_exclusive_scan(int v, int& total) {
 
 template <typename KeyOf>
 __device__ __forceinline__ bool
-table_insert(int32_t* slots, uint32_t mask, int row, Coord key, KeyOf key_of, bool* met_duplicate) {
+table32_insert(int32_t* slots, uint32_t mask, int row, Coord key, KeyOf key_of, bool* met_duplicate) {
     uint32_t slot = hash_coord(key) & mask;
     for (uint32_t probe = 0; probe <= mask; ++probe) {
         int cur = *reinterpret_cast<volatile int32_t*>(slots + slot);
@@ -197,7 +273,7 @@ table_insert(int32_t* slots, uint32_t mask, int row, Coord key, KeyOf key_of, bo
 
 template <typename KeyOf>
 __device__ __forceinline__ int
-table_find(const int32_t* slots, uint32_t mask, Coord key, KeyOf key_of) {
+table32_find(const int32_t* slots, uint32_t mask, Coord key, KeyOf key_of) {
     uint32_t slot = hash_coord(key) & mask;
     for (uint32_t probe = 0; probe <= mask; ++probe) {
         int cur = __ldg(slots + slot);

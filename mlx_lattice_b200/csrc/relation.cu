@@ -34,7 +34,7 @@ enum class MapRule : int {
 
 struct MapParams {
     const int32_t* coords;        // source coords
-    const int32_t* table;         // source table
+    const Slot* table;            // source table
     uint32_t table_mask;
     const int32_t* out_coords;    // coordinates of the output rows
     const int32_t* out_count_ptr; // device count of output rows (already clamped source)
@@ -71,7 +71,7 @@ __global__ void fill_i32_kernel(int32_t* data, size_t count, int value) {
 
 // insert rows [0, active) keyed by their own coordinate
 __global__ void insert_rows_kernel(
-    const int32_t* coords, const int32_t* active_ptr, int rows, int32_t* table,
+    const int32_t* coords, const int32_t* active_ptr, int rows, Slot* table,
     uint32_t mask, int32_t* status, int flag_duplicates
 ) {
     int active = clamp_count(active_ptr, rows);
@@ -91,7 +91,7 @@ __global__ void insert_rows_kernel(
 
 // insert all rows [0, rows) regardless of an active count
 __global__ void insert_all_rows_kernel(
-    const int32_t* coords, int rows, int32_t* table, uint32_t mask, int32_t* status
+    const int32_t* coords, int rows, Slot* table, uint32_t mask, int32_t* status
 ) {
     int row = blockIdx.x * blockDim.x + threadIdx.x;
     if (row >= rows) {
@@ -105,7 +105,7 @@ __global__ void insert_all_rows_kernel(
 
 __global__ void insert_downsampled_kernel(
     const int32_t* coords, const int32_t* active_ptr, int rows, int sx, int sy, int sz,
-    int32_t* table, uint32_t mask, int32_t* status
+    Slot* table, uint32_t mask, int32_t* status
 ) {
     int active = active_ptr ? clamp_count(active_ptr, rows) : rows;
     int row = blockIdx.x * blockDim.x + threadIdx.x;
@@ -151,7 +151,7 @@ __device__ __forceinline__ int block_exclusive_scan(int value, int& block_total)
 // winners of the downsampled table -> per-block counts
 __global__ void mark_winners_kernel(
     const int32_t* coords, const int32_t* active_ptr, int rows, int sx, int sy, int sz,
-    const int32_t* table, uint32_t mask, int32_t* block_sums
+    const Slot* table, uint32_t mask, int32_t* block_sums
 ) {
     int active = active_ptr ? clamp_count(active_ptr, rows) : rows;
     int row = blockIdx.x * blockDim.x + threadIdx.x;
@@ -219,7 +219,7 @@ __global__ void scan_blocks_kernel(
 // stable compaction of the winners: out_coords in first-seen order
 __global__ void compact_winners_kernel(
     const int32_t* coords, const int32_t* active_ptr, int rows, int sx, int sy, int sz,
-    const int32_t* table, uint32_t mask, const int32_t* block_offsets, int32_t* out_coords,
+    const Slot* table, uint32_t mask, const int32_t* block_offsets, int32_t* out_coords,
     int out_capacity, int32_t* status
 ) {
     int active = active_ptr ? clamp_count(active_ptr, rows) : rows;
@@ -468,6 +468,189 @@ __global__ void __launch_bounds__(kBlockThreads) map_fill_kernel(MapParams p) {
     }
 }
 
+// ---- single-pass kernel map (K <= 32) --------------------------------------------------
+//
+// One block per 256 output rows (tiles taken in ticket order), one warp per 32 rows, lane =
+// kernel offset. Each candidate is probed once; the hit rows wait in shared memory while
+// the block learns where its edges start from a decoupled look-back over the tiles
+// before it (a tile first publishes its own edge count, then sums its predecessors'
+// counts until it meets one that already knows its prefix). Edges are then written in
+// (output row asc, kernel id asc) order. Four rows are probed per step so that four
+// independent slot loads are in flight per lane.
+constexpr unsigned long long kTileAggregate = 1ull << 62;
+constexpr unsigned long long kTilePrefix = 2ull << 62;
+constexpr unsigned long long kTileValueMask = (1ull << 62) - 1;
+constexpr long long kLookbackBudgetCycles = 4000000000LL;  // about two seconds
+
+__global__ void __launch_bounds__(kBlockThreads) map_single_pass_kernel(
+    MapParams p, unsigned long long* tile_status, int* ticket, int num_tiles
+) {
+    extern __shared__ int s_hits[];  // [256][K]
+    __shared__ int s_tile;
+    __shared__ int s_base;
+    __shared__ int s_failed;
+    __shared__ int warp_total[kWarpsPerBlock];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int K = p.geo.volume;
+    if (threadIdx.x == 0) {
+        s_tile = atomicAdd(ticket, 1);
+        s_failed = 0;
+    }
+    __syncthreads();
+    const int tile = s_tile;
+    if (tile >= num_tiles) {
+        return;
+    }
+    const int n_out = clamp_count(p.out_count_ptr, p.out_count_cap);
+    const int row0 = tile * kRowsPerBlock + warp * 32;
+    const int my_row = row0 + lane;
+    PlainKey key_of{p.coords};
+
+    Coord mine{0, 0, 0, 0};
+    if (my_row < n_out) {
+        mine = load_coord(p.out_coords, my_row);
+    }
+    int ox = 0, oy = 0, oz = 0;
+    if (lane < K) {
+        p.geo.offset(lane, ox, oy, oz);
+    }
+    unsigned my_mask = 0;
+    int* warp_hits = s_hits + warp * 32 * K;
+    for (int j = 0; j < 32; j += 4) {
+        if (row0 + j >= n_out) {
+            break;
+        }
+        Coord cand[4];
+        bool live[4];
+        unsigned long long tag[4];
+        uint32_t slot[4];
+        Slot cur[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            Coord out{__shfl_sync(0xffffffffu, mine.b, j + u), __shfl_sync(0xffffffffu, mine.x, j + u),
+                      __shfl_sync(0xffffffffu, mine.y, j + u), __shfl_sync(0xffffffffu, mine.z, j + u)};
+            live[u] = lane < K && row0 + j + u < n_out && candidate_of(p, out, ox, oy, oz, cand[u]);
+            cur[u] = kEmptySlot;
+            tag[u] = 0;
+            slot[u] = 0;
+            if (live[u]) {
+                const unsigned long long h = hash_coord64(cand[u]);
+                tag[u] = h & 0xFFFFFFFF00000000ull;
+                slot[u] = static_cast<uint32_t>(h) & p.table_mask;
+                cur[u] = __ldg(p.table + slot[u]);  // four independent loads in flight
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            int found = -1;
+            if (live[u]) {
+                for (uint32_t probe = 0; probe <= p.table_mask; ++probe) {
+                    if (cur[u] == kEmptySlot) {
+                        break;
+                    }
+                    if ((cur[u] & 0xFFFFFFFF00000000ull) == tag[u]) {
+                        int row = static_cast<int>(cur[u] & 0xFFFFFFFFu);
+                        if (key_of(row) == cand[u]) {
+                            found = row;
+                            break;
+                        }
+                    }
+                    slot[u] = (slot[u] + 1) & p.table_mask;
+                    cur[u] = __ldg(p.table + slot[u]);
+                }
+            }
+            const unsigned m = __ballot_sync(0xffffffffu, found >= 0);
+            if (lane == j + u) {
+                my_mask = m;
+            }
+            if (lane < K) {
+                warp_hits[(j + u) * K + lane] = found;
+            }
+        }
+    }
+    if (p.masks != nullptr && my_row < p.out_capacity) {
+        p.masks[my_row] = static_cast<int>(my_mask);
+    }
+    int wtotal;
+    int my_start = warp_exclusive_scan(__popc(my_mask), wtotal);
+    if (lane == 0) {
+        warp_total[warp] = wtotal;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int total = 0;
+        for (int w = 0; w < kWarpsPerBlock; ++w) {
+            int t = warp_total[w];
+            warp_total[w] = total;
+            total += t;
+        }
+        // publish this tile's count, then look back for the prefix
+        volatile unsigned long long* status = tile_status;
+        long long exclusive = 0;
+        if (tile == 0) {
+            status[0] = kTilePrefix | static_cast<unsigned long long>(total);
+        } else {
+            status[tile] = kTileAggregate | static_cast<unsigned long long>(total);
+            long long start = clock64();
+            int t = tile - 1;
+            while (t >= 0) {
+                unsigned long long v = status[t];
+                if (v == 0) {
+                    if (clock64() - start > kLookbackBudgetCycles) {
+                        s_failed = 1;
+                        raise_status(p.status, LAT_STATUS_WAIT_TIMEOUT);
+                        break;
+                    }
+                    continue;
+                }
+                exclusive += static_cast<long long>(v & kTileValueMask);
+                if (v & kTilePrefix) {
+                    break;
+                }
+                --t;
+            }
+            status[tile] = kTilePrefix | static_cast<unsigned long long>(exclusive + total);
+        }
+        s_base = static_cast<int>(exclusive);
+        if (tile == num_tiles - 1 && !s_failed) {
+            p.counts[0] = static_cast<int>(exclusive + total);
+            p.counts[1] = n_out;
+        }
+    }
+    __syncthreads();
+    if (s_failed) {
+        return;
+    }
+    my_start += s_base + warp_total[warp];
+    const int total_after = my_start + __popc(my_mask);  // == E for rows at and beyond n_out
+    if (my_row < n_out) {
+        p.row_offsets[my_row] = my_start;
+    } else if (my_row <= p.out_capacity) {
+        if (my_row == n_out || p.tail_is_total) {
+            p.row_offsets[my_row] = total_after;
+        }
+    }
+    for (int j = 0; j < 32; ++j) {
+        const int row = row0 + j;
+        if (row >= n_out) {
+            break;
+        }
+        const unsigned m = __shfl_sync(0xffffffffu, my_mask, j);
+        const int start = __shfl_sync(0xffffffffu, my_start, j);
+        if ((m >> lane) & 1u) {
+            const int pos = start + __popc(m & lanemask_lt());
+            if (pos < p.edge_capacity) {
+                p.in_rows[pos] = warp_hits[j * K + lane];
+                p.out_rows[pos] = row;
+                p.kernel_ids[pos] = lane;
+            } else {
+                raise_status(p.status, LAT_STATUS_EDGE_OVERFLOW);
+            }
+        }
+    }
+}
+
 // rows of the identity output support: a copy of the active input rows, zero after
 __global__ void copy_active_coords_kernel(
     const int32_t* coords, const int32_t* active_ptr, int rows, int32_t* out_coords
@@ -548,7 +731,7 @@ struct TransposedCandidateKey {
 };
 
 __global__ void insert_candidates_kernel(
-    TransposedCandidateKey key_of, const int32_t* active_ptr, int rows, int32_t* table,
+    TransposedCandidateKey key_of, const int32_t* active_ptr, int rows, Slot* table,
     uint32_t mask, int32_t* status
 ) {
     int active = clamp_count(active_ptr, rows);
@@ -564,7 +747,7 @@ __global__ void insert_candidates_kernel(
 }
 
 __global__ void mark_candidate_winners_kernel(
-    TransposedCandidateKey key_of, const int32_t* active_ptr, int rows, const int32_t* table,
+    TransposedCandidateKey key_of, const int32_t* active_ptr, int rows, const Slot* table,
     uint32_t mask, int32_t* block_sums
 ) {
     int active = clamp_count(active_ptr, rows);
@@ -583,7 +766,7 @@ __global__ void mark_candidate_winners_kernel(
 }
 
 __global__ void compact_candidates_kernel(
-    TransposedCandidateKey key_of, const int32_t* active_ptr, int rows, const int32_t* table,
+    TransposedCandidateKey key_of, const int32_t* active_ptr, int rows, const Slot* table,
     uint32_t mask, const int32_t* block_offsets, int32_t* out_coords, int out_capacity
 ) {
     int active = clamp_count(active_ptr, rows);
@@ -604,7 +787,7 @@ __global__ void compact_candidates_kernel(
 
 // target-restricted transposed map of a kernel_size == stride conv
 __global__ void target_transposed_count_kernel(
-    const int32_t* coords, const int32_t* table, uint32_t mask, const int32_t* target,
+    const int32_t* coords, const Slot* table, uint32_t mask, const int32_t* target,
     const int32_t* target_active_ptr, int target_rows, int sx, int sy, int sz,
     int lox, int loy, int loz, int32_t* hit_rows, int32_t* block_sums
 ) {
@@ -831,7 +1014,7 @@ __global__ void grouped_sort_kernel(const int32_t* row_offsets, int groups, int3
 // ---- implicit-GEMM view, lookup, alignment ----------------------------------------
 
 __global__ void __launch_bounds__(kBlockThreads) igemm_view_kernel(
-    const int32_t* source_coords, const int32_t* table, uint32_t mask,
+    const int32_t* source_coords, const Slot* table, uint32_t mask,
     const int32_t* source_active_ptr, int source_rows, const int32_t* output_coords,
     const int32_t* output_active_ptr, int output_rows, const int32_t* offsets, int K,
     int words, int sx, int sy, int sz, int px, int py, int pz, int32_t* out_in_map,
@@ -869,7 +1052,7 @@ __global__ void __launch_bounds__(kBlockThreads) igemm_view_kernel(
 }
 
 __global__ void lookup_kernel(
-    const int32_t* coords, const int32_t* table, uint32_t mask, const int32_t* queries,
+    const int32_t* coords, const Slot* table, uint32_t mask, const int32_t* queries,
     int query_rows, const int32_t* query_active_ptr, int32_t* out_rows
 ) {
     int row = blockIdx.x * blockDim.x + threadIdx.x;
@@ -887,7 +1070,7 @@ __global__ void lookup_kernel(
 // alignment pass over lhs rows: keep flag (+ matching rhs row) and block counts
 __global__ void align_lhs_count_kernel(
     const int32_t* lhs, const int32_t* lhs_active_ptr, int lhs_rows, const int32_t* rhs,
-    const int32_t* rhs_table, uint32_t rhs_mask, int inner, int32_t* match, int32_t* block_sums
+    const Slot* rhs_table, uint32_t rhs_mask, int inner, int32_t* match, int32_t* block_sums
 ) {
     int active = clamp_count(lhs_active_ptr, lhs_rows);
     int row = blockIdx.x * blockDim.x + threadIdx.x;
@@ -928,7 +1111,7 @@ __global__ void align_lhs_fill_kernel(
 // outer join tail: rhs rows absent from lhs, appended after `base` rows
 __global__ void align_rhs_count_kernel(
     const int32_t* rhs, const int32_t* rhs_active_ptr, int rhs_rows, const int32_t* lhs,
-    const int32_t* lhs_table, uint32_t lhs_mask, int32_t* absent, int32_t* block_sums
+    const Slot* lhs_table, uint32_t lhs_mask, int32_t* absent, int32_t* block_sums
 ) {
     int active = clamp_count(rhs_active_ptr, rhs_rows);
     int row = blockIdx.x * blockDim.x + threadIdx.x;
@@ -968,7 +1151,7 @@ __global__ void align_rhs_fill_kernel(
 // right join: one output row per active rhs row
 __global__ void align_right_kernel(
     const int32_t* rhs, const int32_t* rhs_active_ptr, int rhs_rows, const int32_t* lhs,
-    const int32_t* lhs_table, uint32_t lhs_mask, int32_t* out_coords, int32_t* out_lhs,
+    const Slot* lhs_table, uint32_t lhs_mask, int32_t* out_coords, int32_t* out_lhs,
     int32_t* out_rhs, int32_t* out_count
 ) {
     int active = clamp_count(rhs_active_ptr, rhs_rows);
@@ -1011,8 +1194,12 @@ cudaError_t fill_i32(int32_t* data, size_t count, int value, cudaStream_t stream
     return cudaGetLastError();
 }
 
+cudaError_t clear_table(Slot* slots, size_t capacity, cudaStream_t stream) {
+    return cudaMemsetAsync(slots, 0xFF, capacity * sizeof(Slot), stream);
+}
+
 struct SourceTable {
-    int32_t* slots;
+    Slot* slots;
     uint32_t mask;
 };
 
@@ -1022,12 +1209,12 @@ int build_source_table(
     int32_t* status, bool flag_duplicates, cudaStream_t stream, SourceTable& table
 ) {
     int capacity = next_pow2(std::max(2LL * rows, 1LL));
-    table.slots = ws.take<int32_t>(capacity);
+    table.slots = ws.take<Slot>(capacity);
     table.mask = static_cast<uint32_t>(capacity - 1);
     if (!ws.ok) {
         return fail(LAT_WORKSPACE_TOO_SMALL, "workspace is too small for the coordinate table.");
     }
-    LAT_CUDA_CHECK(fill_i32(table.slots, capacity, -1, stream));
+    LAT_CUDA_CHECK(clear_table(table.slots, capacity, stream));
     if (rows > 0) {
         insert_rows_kernel<<<blocks_for(rows), kBlockThreads, 0, stream>>>(
             coords, active_rows, rows, table.slots, table.mask, status, flag_duplicates ? 1 : 0);
@@ -1112,6 +1299,21 @@ int run_map(
     p.edge_capacity = static_cast<int>(std::min<size_t>(edge_capacity, 0x7fffffff));
     p.status = status;
 
+    if (!lists && K <= 32) {
+        // single pass: probe once, look back for the tile prefix, write
+        unsigned long long* tile_status = ws.take<unsigned long long>(nblocks);
+        int* ticket = ws.take<int>(1);
+        if (!ws.ok) {
+            return fail(LAT_WORKSPACE_TOO_SMALL, "workspace is too small for the kernel map.");
+        }
+        LAT_CUDA_CHECK(cudaMemsetAsync(tile_status, 0, sizeof(unsigned long long) * nblocks, stream));
+        LAT_CUDA_CHECK(cudaMemsetAsync(ticket, 0, sizeof(int), stream));
+        p.masks = o.row_masks;  // optional output; no scratch copy needed
+        size_t smem = sizeof(int) * kRowsPerBlock * K;
+        map_single_pass_kernel<<<nblocks, kBlockThreads, smem, stream>>>(p, tile_status, ticket, nblocks);
+        LAT_LAUNCH_CHECK();
+        return LAT_OK;
+    }
     size_t count_smem = lists ? sizeof(int) * kWarpsPerBlock * K : 0;
     map_count_kernel<<<nblocks, kBlockThreads, count_smem, stream>>>(p);
     LAT_LAUNCH_CHECK();
@@ -1139,13 +1341,14 @@ size_t lat_relation_workspace_bytes(int32_t rows, int32_t out_rows, int32_t kern
     size_t r = static_cast<size_t>(std::max(rows, 1));
     size_t o = static_cast<size_t>(std::max(out_rows, 1));
     size_t total = 0;
-    total += align_up(sizeof(int32_t) * next_pow2(2 * r));           // source table
-    total += align_up(sizeof(int32_t) * next_pow2(2 * std::max(r, o)));  // second table
+    total += align_up(sizeof(Slot) * next_pow2(2 * r));              // source table
+    total += align_up(sizeof(Slot) * next_pow2(2 * std::max(r, o)));     // second table
     total += align_up(sizeof(int32_t) * o * words);                  // masks
     size_t nblocks = (std::max(o, r * 1) + kRowsPerBlock) / kRowsPerBlock + 2;
     total += 3 * align_up(sizeof(int32_t) * nblocks);                // block sums
     total += align_up(sizeof(int32_t) * nblocks * K);                // per-block offset hist
     total += align_up(sizeof(int32_t) * K) + 4 * 256;
+    total += align_up(sizeof(unsigned long long) * nblocks) + 256;      // tile status + ticket
     total += align_up(sizeof(int32_t) * o);                          // hit rows / flags
     return total;
 }
@@ -1214,14 +1417,14 @@ int lat_build_kernel_relation(
         LAT_LAUNCH_CHECK();
     } else {
         int capacity = next_pow2(std::max(2LL * rows, 1LL));
-        int32_t* table2 = ws.take<int32_t>(capacity);
+        Slot* table2 = ws.take<Slot>(capacity);
         int nblocks = blocks_for(rows);
         int32_t* sums = ws.take<int32_t>(nblocks);
         if (!ws.ok) {
             return fail(LAT_WORKSPACE_TOO_SMALL, "workspace is too small for the kernel map.");
         }
         uint32_t mask2 = static_cast<uint32_t>(capacity - 1);
-        LAT_CUDA_CHECK(fill_i32(table2, capacity, -1, stream));
+        LAT_CUDA_CHECK(clear_table(table2, capacity, stream));
         LAT_CUDA_CHECK(fill_i32(out_coords, static_cast<size_t>(rows) * 4, 0, stream));
         insert_downsampled_kernel<<<nblocks, kBlockThreads, 0, stream>>>(
             coords, active_rows, rows, stride.x, stride.y, stride.z, table2, mask2, status);
@@ -1333,7 +1536,7 @@ int lat_build_transposed_kernel_relation(
         return rc;
     }
     int cap2 = next_pow2(std::max(2LL * capacity, 1LL));
-    int32_t* table2 = ws.take<int32_t>(cap2);
+    Slot* table2 = ws.take<Slot>(cap2);
     int nblocks = std::max(1, blocks_for(capacity));
     int32_t* sums = ws.take<int32_t>(nblocks);
     int32_t* out_count = ws.take<int32_t>(1);
@@ -1343,7 +1546,7 @@ int lat_build_transposed_kernel_relation(
     uint32_t mask2 = static_cast<uint32_t>(cap2 - 1);
     TransposedCandidateKey key_of{coords, geo, stride.x, stride.y, stride.z,
                                   padding.x, padding.y, padding.z};
-    LAT_CUDA_CHECK(fill_i32(table2, cap2, -1, stream));
+    LAT_CUDA_CHECK(clear_table(table2, cap2, stream));
     LAT_CUDA_CHECK(fill_i32(out_coords, static_cast<size_t>(capacity) * 4, 0, stream));
     insert_candidates_kernel<<<nblocks, kBlockThreads, 0, stream>>>(
         key_of, active_rows, rows, table2, mask2, status);
@@ -1564,7 +1767,7 @@ int lat_build_relation_grouped_view(
 }
 
 size_t lat_implicit_gemm_view_workspace_bytes(int32_t source_rows) {
-    return align_up(sizeof(int32_t) * next_pow2(2LL * std::max(source_rows, 1))) + 1024;
+    return align_up(sizeof(Slot) * next_pow2(2LL * std::max(source_rows, 1))) + 1024;
 }
 
 int lat_build_relation_implicit_gemm_view(
@@ -1585,12 +1788,12 @@ int lat_build_relation_implicit_gemm_view(
     }
     Workspace ws(workspace, workspace_bytes);
     int capacity = next_pow2(std::max(2LL * source_rows, 1LL));
-    int32_t* table = ws.take<int32_t>(capacity);
+    Slot* table = ws.take<Slot>(capacity);
     if (!ws.ok) {
         return fail(LAT_WORKSPACE_TOO_SMALL, "workspace is too small for the implicit GEMM view.");
     }
     uint32_t mask = static_cast<uint32_t>(capacity - 1);
-    LAT_CUDA_CHECK(fill_i32(table, capacity, -1, stream));
+    LAT_CUDA_CHECK(clear_table(table, capacity, stream));
     if (source_rows > 0) {
         // the reference hashes every source row and filters hits by the active count
         // afterwards (coordinates/cpu/relation_views_detail.h:122-169)
@@ -1608,7 +1811,7 @@ int lat_build_relation_implicit_gemm_view(
 
 size_t lat_coord_set_workspace_bytes(int32_t rows) {
     size_t r = static_cast<size_t>(std::max(rows, 1));
-    return align_up(sizeof(int32_t) * next_pow2(2 * r)) +
+    return align_up(sizeof(Slot) * next_pow2(2 * r)) +
            align_up(sizeof(int32_t) * ((r + kBlockThreads) / kBlockThreads + 1)) + 1024;
 }
 
@@ -1626,14 +1829,14 @@ int lat_downsample_coords(
     }
     Workspace ws(workspace, workspace_bytes);
     int capacity = next_pow2(2LL * rows);
-    int32_t* table = ws.take<int32_t>(capacity);
+    Slot* table = ws.take<Slot>(capacity);
     int nblocks = blocks_for(rows);
     int32_t* sums = ws.take<int32_t>(nblocks);
     if (!ws.ok) {
         return fail(LAT_WORKSPACE_TOO_SMALL, "workspace is too small for the coordinate set.");
     }
     uint32_t mask = static_cast<uint32_t>(capacity - 1);
-    LAT_CUDA_CHECK(fill_i32(table, capacity, -1, stream));
+    LAT_CUDA_CHECK(clear_table(table, capacity, stream));
     LAT_CUDA_CHECK(fill_i32(out_coords, static_cast<size_t>(rows) * 4, 0, stream));
     insert_downsampled_kernel<<<nblocks, kBlockThreads, 0, stream>>>(
         coords, nullptr, rows, stride.x, stride.y, stride.z, table, mask, status);
@@ -1663,12 +1866,12 @@ int lat_lookup_coords(
     }
     Workspace ws(workspace, workspace_bytes);
     int capacity = next_pow2(std::max(2LL * rows, 1LL));
-    int32_t* table = ws.take<int32_t>(capacity);
+    Slot* table = ws.take<Slot>(capacity);
     if (!ws.ok) {
         return fail(LAT_WORKSPACE_TOO_SMALL, "workspace is too small for the coordinate set.");
     }
     uint32_t mask = static_cast<uint32_t>(capacity - 1);
-    LAT_CUDA_CHECK(fill_i32(table, capacity, -1, stream));
+    LAT_CUDA_CHECK(clear_table(table, capacity, stream));
     if (rows > 0) {
         insert_all_rows_kernel<<<blocks_for(rows), kBlockThreads, 0, stream>>>(
             coords, rows, table, mask, status);
@@ -1683,8 +1886,8 @@ int lat_lookup_coords(
 size_t lat_sparse_alignment_workspace_bytes(int32_t lhs_rows, int32_t rhs_rows) {
     size_t l = static_cast<size_t>(std::max(lhs_rows, 1));
     size_t r = static_cast<size_t>(std::max(rhs_rows, 1));
-    return align_up(sizeof(int32_t) * next_pow2(2 * l)) +
-           align_up(sizeof(int32_t) * next_pow2(2 * r)) + align_up(sizeof(int32_t) * l) +
+    return align_up(sizeof(Slot) * next_pow2(2 * l)) +
+           align_up(sizeof(Slot) * next_pow2(2 * r)) + align_up(sizeof(int32_t) * l) +
            align_up(sizeof(int32_t) * r) +
            2 * align_up(sizeof(int32_t) * ((std::max(l, r) + kBlockThreads) / kBlockThreads + 1)) +
            2048;

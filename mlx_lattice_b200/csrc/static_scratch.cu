@@ -63,7 +63,7 @@ __global__ void static_insert_kernel(
         return;
     }
     PlainKey key_of{coords};
-    if (!table_insert(table, mask, row, key_of(row), key_of, nullptr)) {
+    if (!table32_insert(table, mask, row, key_of(row), key_of, nullptr)) {
         raise_status(status, LAT_STATUS_HASH_FULL);
     }
 }
@@ -74,7 +74,7 @@ __global__ void static_lookup_kernel(
 ) {
     int row = blockIdx.x * blockDim.x + threadIdx.x;
     if (row < query_rows) {
-        out_rows[row] = table_find(table, mask, load_coord(queries, row), PlainKey{coords});
+        out_rows[row] = table32_find(table, mask, load_coord(queries, row), PlainKey{coords});
     }
 }
 

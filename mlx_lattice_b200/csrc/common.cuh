@@ -48,8 +48,9 @@ inline size_t align_up(size_t value, size_t alignment = 256) {
     return (value + alignment - 1) / alignment * alignment;
 }
 
+// smallest power of two >= value, never below 4 (one hash bucket)
 inline int next_pow2(long long value) {
-    long long out = 1;
+    long long out = 4;
     while (out < value) {
         out <<= 1;
     }
@@ -175,66 +176,133 @@ __device__ __forceinline__ int warp_exclusive_scan(int v, int& total) {
 using Slot = unsigned long long;
 constexpr Slot kEmptySlot = ~0ull;
 
-__device__ __forceinline__ unsigned long long hash_coord64(Coord c) {
-    unsigned long long k0 =
-        (static_cast<unsigned long long>(static_cast<uint32_t>(c.b)) << 32) | static_cast<uint32_t>(c.x);
-    unsigned long long k1 =
-        (static_cast<unsigned long long>(static_cast<uint32_t>(c.y)) << 32) | static_cast<uint32_t>(c.z);
-    unsigned long long h = k0 * 0x9E3779B97F4A7C15ull;
-    h ^= h >> 32;
-    h = (h ^ k1) * 0xC2B2AE3D27D4EB4Full;
-    h ^= h >> 29;
-    h *= 0x165667B19E3779F9ull;
-    h ^= h >> 32;
-    return h;
+// Two 32-bit hashes of a coordinate. Both start from a linear form of the four ints
+// (hash_linear), so the form of `base + offset` is the sum of the forms: a kernel map
+// computes the form of each output row once and adds a per-offset constant. `index`
+// pushes its form through an integer finaliser and picks the bucket; `tag` is the
+// second form as it is and only has to differ between keys that share a bucket.
+__device__ __forceinline__ void hash_linear(Coord c, uint32_t& u, uint32_t& t) {
+    const uint32_t b = static_cast<uint32_t>(c.b), x = static_cast<uint32_t>(c.x);
+    const uint32_t y = static_cast<uint32_t>(c.y), z = static_cast<uint32_t>(c.z);
+    u = x * 0x9E3779B1u + y * 0x85EBCA77u + z * 0xC2B2AE3Du + b * 0x27D4EB2Fu;
+    t = x * 0x165667B1u + y * 0xD3A2646Du + z * 0xFD7046C5u + b * 0xB55A4F09u;
 }
+
+__device__ __forceinline__ uint32_t hash_finalize(uint32_t u) {
+    u ^= u >> 16;
+    u *= 0x7FEB352Du;
+    u ^= u >> 15;
+    u *= 0x846CA68Bu;
+    u ^= u >> 16;
+    return u;
+}
+
+__device__ __forceinline__ void hash_coord(Coord c, uint32_t& index, uint32_t& tag) {
+    uint32_t u;
+    hash_linear(c, u, tag);
+    index = hash_finalize(u);
+}
+
+// Buckets of four consecutive slots (one 32-byte sector). Inserts take the first empty
+// slot of a bucket in slot order, so a bucket fills from the front and a lookup that
+// meets an empty slot knows the key is absent; one sector read decides most probes.
+constexpr uint32_t kBucketSlots = 4;
 
 template <typename KeyOf>
 __device__ __forceinline__ bool
 table_insert(Slot* slots, uint32_t mask, int row, Coord key, KeyOf key_of, bool* met_duplicate) {
-    const unsigned long long h = hash_coord64(key);
-    const Slot tag = h & 0xFFFFFFFF00000000ull;
-    const Slot want = tag | static_cast<uint32_t>(row);
-    uint32_t slot = static_cast<uint32_t>(h) & mask;
-    for (uint32_t probe = 0; probe <= mask; ++probe) {
-        Slot cur = *reinterpret_cast<volatile Slot*>(slots + slot);
-        if (cur == kEmptySlot) {
-            Slot old = atomicCAS(slots + slot, kEmptySlot, want);
-            if (old == kEmptySlot) {
+    uint32_t index, tag;
+    hash_coord(key, index, tag);
+    const Slot want = (static_cast<Slot>(tag) << 32) | static_cast<uint32_t>(row);
+    uint32_t base = index & mask & ~(kBucketSlots - 1);
+    for (uint32_t probe = 0; probe <= mask; probe += kBucketSlots) {
+#pragma unroll
+        for (uint32_t i = 0; i < kBucketSlots; ++i) {
+            Slot* ptr = slots + base + i;
+            Slot cur = *reinterpret_cast<volatile Slot*>(ptr);
+            if (cur == kEmptySlot) {
+                Slot old = atomicCAS(ptr, kEmptySlot, want);
+                if (old == kEmptySlot) {
+                    return true;
+                }
+                cur = old;
+            }
+            if (static_cast<uint32_t>(cur >> 32) == tag &&
+                key_of(static_cast<int>(cur & 0xFFFFFFFFu)) == key) {
+                atomicMin(ptr, want);
+                if (met_duplicate != nullptr) {
+                    *met_duplicate = true;
+                }
                 return true;
             }
-            cur = old;
         }
-        if ((cur & 0xFFFFFFFF00000000ull) == tag && key_of(static_cast<int>(cur & 0xFFFFFFFFu)) == key) {
-            atomicMin(slots + slot, want);
-            if (met_duplicate != nullptr) {
-                *met_duplicate = true;
-            }
-            return true;
-        }
-        slot = (slot + 1) & mask;
+        base = (base + kBucketSlots) & mask;
     }
     return false;
+}
+
+// The four slots of a bucket as 32-bit words: rows in lo.x lo.z hi.x hi.z, tags in
+// lo.y lo.w hi.y hi.w (a slot's low word is its row).
+struct Bucket {
+    uint4 lo, hi;
+};
+
+__device__ __forceinline__ Bucket load_bucket(const Slot* slots, uint32_t base) {
+    Bucket b;
+    b.lo = __ldg(reinterpret_cast<const uint4*>(slots + base));
+    b.hi = __ldg(reinterpret_cast<const uint4*>(slots + base + 2));
+    return b;
+}
+
+// Scan one loaded bucket without data-dependent branches except the rare verification
+// of a tag match: returns the row (>= 0), -1 when the key is absent for sure, -2 when
+// the bucket is full without a match (continue with the next bucket). A row word of all
+// ones marks an empty slot (row ids are non-negative).
+template <typename KeyOf>
+__device__ __forceinline__ int
+scan_bucket(const Bucket& b, uint32_t tag, Coord key, KeyOf key_of) {
+    const unsigned empty = (b.lo.x == 0xFFFFFFFFu ? 1u : 0u) | (b.lo.z == 0xFFFFFFFFu ? 2u : 0u) |
+                           (b.hi.x == 0xFFFFFFFFu ? 4u : 0u) | (b.hi.z == 0xFFFFFFFFu ? 8u : 0u);
+    unsigned match = (b.lo.y == tag ? 1u : 0u) | (b.lo.w == tag ? 2u : 0u) |
+                     (b.hi.y == tag ? 4u : 0u) | (b.hi.w == tag ? 8u : 0u);
+    match &= ((empty & (0u - empty)) - 1u) & 0xFu;  // only slots before the first empty one
+    while (match != 0) {
+        const int i = __ffs(match) - 1;
+        match &= match - 1;
+        const uint32_t row = i == 0 ? b.lo.x : i == 1 ? b.lo.z : i == 2 ? b.hi.x : b.hi.z;
+        if (key_of(static_cast<int>(row)) == key) {
+            return static_cast<int>(row);
+        }
+    }
+    return empty != 0 ? -1 : -2;
+}
+
+// Tag-only scan without branches: the row of the first slot before the first empty one
+// whose tag matches (the caller still has to compare coordinates), -1 when the key is
+// absent for sure, -2 when the bucket is full without a tag match.
+__device__ __forceinline__ int scan_bucket_tags(const Bucket& b, uint32_t tag) {
+    const unsigned empty = (b.lo.x == 0xFFFFFFFFu ? 1u : 0u) | (b.lo.z == 0xFFFFFFFFu ? 2u : 0u) |
+                           (b.hi.x == 0xFFFFFFFFu ? 4u : 0u) | (b.hi.z == 0xFFFFFFFFu ? 8u : 0u);
+    unsigned match = (b.lo.y == tag ? 1u : 0u) | (b.lo.w == tag ? 2u : 0u) |
+                     (b.hi.y == tag ? 4u : 0u) | (b.hi.w == tag ? 8u : 0u);
+    match &= ((empty & (0u - empty)) - 1u) & 0xFu;
+    const uint32_t row = (match & 1u) ? b.lo.x : (match & 2u) ? b.lo.z : (match & 4u) ? b.hi.x : b.hi.z;
+    return match != 0 ? static_cast<int>(row) : (empty != 0 ? -1 : -2);
 }
 
 template <typename KeyOf>
 __device__ __forceinline__ int
 table_find(const Slot* slots, uint32_t mask, Coord key, KeyOf key_of) {
-    const unsigned long long h = hash_coord64(key);
-    const Slot tag = h & 0xFFFFFFFF00000000ull;
-    uint32_t slot = static_cast<uint32_t>(h) & mask;
-    for (uint32_t probe = 0; probe <= mask; ++probe) {
-        Slot cur = __ldg(slots + slot);
-        if (cur == kEmptySlot) {
-            return -1;
+    uint32_t index, tag;
+    hash_coord(key, index, tag);
+    uint32_t base = index & mask & ~(kBucketSlots - 1);
+    for (uint32_t probe = 0; probe <= mask; probe += kBucketSlots) {
+        const Bucket b = load_bucket(slots, base);
+        int found = scan_bucket(b, tag, key, key_of);
+        if (found != -2) {
+            return found;
         }
-        if ((cur & 0xFFFFFFFF00000000ull) == tag) {
-            int row = static_cast<int>(cur & 0xFFFFFFFFu);
-            if (key_of(row) == key) {
-                return row;
-            }
-        }
-        slot = (slot + 1) & mask;
+        base = (base + kBucketSlots) & mask;
     }
     return -1;
 }

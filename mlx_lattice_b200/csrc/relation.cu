@@ -15,6 +15,7 @@
 // The order of the emitted edges is the reference's (out row ascending, kernel id
 // ascending; coordinates/cpu/relation_build_detail.h:19-34).
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -470,22 +471,29 @@ __global__ void __launch_bounds__(kBlockThreads) map_fill_kernel(MapParams p) {
 
 // ---- single-pass kernel map (K <= 32) --------------------------------------------------
 //
-// One block per 256 output rows (tiles taken in ticket order), one warp per 32 rows, lane =
-// kernel offset. Each candidate is probed once; the hit rows wait in shared memory while
-// the block learns where its edges start from a decoupled look-back over the tiles
-// before it (a tile first publishes its own edge count, then sums its predecessors'
-// counts until it meets one that already knows its prefix). Edges are then written in
-// (output row asc, kernel id asc) order. Four rows are probed per step so that four
-// independent slot loads are in flight per lane.
+// One block per 256 output rows (tiles taken in ticket order), one warp per 32 rows.
+//  1. probe, lane = kernel offset: every candidate's bucket is read once and scanned by
+//     tag only; the hit rows wait in shared memory. For the forward rule the candidate is
+//     `row base + offset`, so its two linear hash forms are the row's forms (computed once
+//     per row) plus a per-lane constant.
+//  2. verify, lane = output row: each tag hit is compared with the coordinate it stands
+//     for; a false tag match (one in 2^32) falls back to the exact table lookup.
+//  3. the block learns where its edges start from a decoupled look-back over the tiles
+//     before it: it publishes its own edge count, then one warp sums its predecessors'
+//     counts 32 tiles at a time until it meets one that already knows its prefix.
+//  4. write, lane = output row: edges in (output row asc, kernel id asc) order.
 constexpr unsigned long long kTileAggregate = 1ull << 62;
 constexpr unsigned long long kTilePrefix = 2ull << 62;
 constexpr unsigned long long kTileValueMask = (1ull << 62) - 1;
 constexpr long long kLookbackBudgetCycles = 4000000000LL;  // about two seconds
 
-__global__ void __launch_bounds__(kBlockThreads) map_single_pass_kernel(
+template <int kProbeRows, int kMinBlocks>
+__global__ void __launch_bounds__(kBlockThreads, kMinBlocks) map_single_pass_kernel(
     MapParams p, unsigned long long* tile_status, int* ticket, int num_tiles
 ) {
-    extern __shared__ int s_hits[];  // [256][K]
+    extern __shared__ int s_hits[];            // [256][K]
+    __shared__ int4 s_row[kRowsPerBlock];      // forward rule: (u, t, -, -) of the row base; else the row's coords
+    __shared__ int4 s_offset[32];              // kernel offsets by id
     __shared__ int s_tile;
     __shared__ int s_base;
     __shared__ int s_failed;
@@ -497,6 +505,13 @@ __global__ void __launch_bounds__(kBlockThreads) map_single_pass_kernel(
         s_tile = atomicAdd(ticket, 1);
         s_failed = 0;
     }
+    int ox = 0, oy = 0, oz = 0;
+    if (lane < K) {
+        p.geo.offset(lane, ox, oy, oz);
+    }
+    if (warp == 0) {
+        s_offset[lane] = make_int4(ox, oy, oz, 0);
+    }
     __syncthreads();
     const int tile = s_tile;
     if (tile >= num_tiles) {
@@ -505,59 +520,65 @@ __global__ void __launch_bounds__(kBlockThreads) map_single_pass_kernel(
     const int n_out = clamp_count(p.out_count_ptr, p.out_count_cap);
     const int row0 = tile * kRowsPerBlock + warp * 32;
     const int my_row = row0 + lane;
+    const bool forward = p.rule == static_cast<int>(MapRule::Forward);
     PlainKey key_of{p.coords};
 
     Coord mine{0, 0, 0, 0};
     if (my_row < n_out) {
         mine = load_coord(p.out_coords, my_row);
     }
-    int ox = 0, oy = 0, oz = 0;
-    if (lane < K) {
-        p.geo.offset(lane, ox, oy, oz);
+    uint32_t u_lane = 0, t_lane = 0;  // linear hash forms of this lane's offset
+    if (forward) {
+        hash_linear(Coord{0, ox, oy, oz}, u_lane, t_lane);
+        uint32_t u_row, t_row;
+        hash_linear(Coord{mine.b, mine.x * p.sx - p.px, mine.y * p.sy - p.py, mine.z * p.sz - p.pz},
+                    u_row, t_row);
+        s_row[warp * 32 + lane] = make_int4(static_cast<int>(u_row), static_cast<int>(t_row), 0, 0);
+    } else {
+        s_row[warp * 32 + lane] = make_int4(mine.b, mine.x, mine.y, mine.z);
     }
+    __syncwarp();
+
+    // 1. probe
     unsigned my_mask = 0;
     int* warp_hits = s_hits + warp * 32 * K;
-    for (int j = 0; j < 32; j += 4) {
+    for (int j = 0; j < 32; j += kProbeRows) {
         if (row0 + j >= n_out) {
             break;
         }
-        Coord cand[4];
-        bool live[4];
-        unsigned long long tag[4];
-        uint32_t slot[4];
-        Slot cur[4];
+        bool live[kProbeRows];
+        uint32_t tag[kProbeRows];
+        uint32_t base[kProbeRows];
+        Bucket bucket[kProbeRows];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            Coord out{__shfl_sync(0xffffffffu, mine.b, j + u), __shfl_sync(0xffffffffu, mine.x, j + u),
-                      __shfl_sync(0xffffffffu, mine.y, j + u), __shfl_sync(0xffffffffu, mine.z, j + u)};
-            live[u] = lane < K && row0 + j + u < n_out && candidate_of(p, out, ox, oy, oz, cand[u]);
-            cur[u] = kEmptySlot;
+        for (int u = 0; u < kProbeRows; ++u) {
+            const int4 r = s_row[warp * 32 + j + u];
+            live[u] = lane < K && row0 + j + u < n_out;
+            uint32_t index = 0;
             tag[u] = 0;
-            slot[u] = 0;
+            if (forward) {
+                index = hash_finalize(static_cast<uint32_t>(r.x) + u_lane);
+                tag[u] = static_cast<uint32_t>(r.y) + t_lane;
+            } else if (live[u]) {
+                Coord cand;
+                live[u] = candidate_of(p, Coord{r.x, r.y, r.z, r.w}, ox, oy, oz, cand);
+                hash_coord(cand, index, tag[u]);
+            }
+            base[u] = index & p.table_mask & ~(kBucketSlots - 1);
             if (live[u]) {
-                const unsigned long long h = hash_coord64(cand[u]);
-                tag[u] = h & 0xFFFFFFFF00000000ull;
-                slot[u] = static_cast<uint32_t>(h) & p.table_mask;
-                cur[u] = __ldg(p.table + slot[u]);  // four independent loads in flight
+                bucket[u] = load_bucket(p.table, base[u]);
             }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kProbeRows; ++u) {
             int found = -1;
             if (live[u]) {
-                for (uint32_t probe = 0; probe <= p.table_mask; ++probe) {
-                    if (cur[u] == kEmptySlot) {
-                        break;
-                    }
-                    if ((cur[u] & 0xFFFFFFFF00000000ull) == tag[u]) {
-                        int row = static_cast<int>(cur[u] & 0xFFFFFFFFu);
-                        if (key_of(row) == cand[u]) {
-                            found = row;
-                            break;
-                        }
-                    }
-                    slot[u] = (slot[u] + 1) & p.table_mask;
-                    cur[u] = __ldg(p.table + slot[u]);
+                found = scan_bucket_tags(bucket[u], tag[u]);
+                for (uint32_t probe = kBucketSlots; found == -2 && probe <= p.table_mask;
+                     probe += kBucketSlots) {
+                    base[u] = (base[u] + kBucketSlots) & p.table_mask;
+                    bucket[u] = load_bucket(p.table, base[u]);
+                    found = scan_bucket_tags(bucket[u], tag[u]);
                 }
             }
             const unsigned m = __ballot_sync(0xffffffffu, found >= 0);
@@ -569,59 +590,103 @@ __global__ void __launch_bounds__(kBlockThreads) map_single_pass_kernel(
             }
         }
     }
+    __syncwarp();
+
+    // 2. verify this lane's row
+    {
+        unsigned bits = my_mask;
+        while (bits != 0) {
+            const int k = __ffs(bits) - 1;
+            bits &= bits - 1;
+            const int4 off = s_offset[k];
+            Coord expect;
+            candidate_of(p, mine, off.x, off.y, off.z, expect);
+            const int hit = warp_hits[lane * K + k];
+            if (!(key_of(hit) == expect)) {
+                const int exact = table_find(p.table, p.table_mask, expect, key_of);
+                if (exact >= 0) {
+                    warp_hits[lane * K + k] = exact;
+                } else {
+                    my_mask &= ~(1u << k);
+                }
+            }
+        }
+    }
     if (p.masks != nullptr && my_row < p.out_capacity) {
         p.masks[my_row] = static_cast<int>(my_mask);
     }
+
+    // 3. where this tile's edges start
     int wtotal;
     int my_start = warp_exclusive_scan(__popc(my_mask), wtotal);
     if (lane == 0) {
         warp_total[warp] = wtotal;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int total = 0;
-        for (int w = 0; w < kWarpsPerBlock; ++w) {
-            int t = warp_total[w];
-            warp_total[w] = total;
-            total += t;
+    if (warp == 0) {
+        int block_total;
+        const int warp_start = warp_exclusive_scan(lane < kWarpsPerBlock ? warp_total[lane] : 0, block_total);
+        if (lane < kWarpsPerBlock) {
+            warp_total[lane] = warp_start;
         }
-        // publish this tile's count, then look back for the prefix
         volatile unsigned long long* status = tile_status;
         long long exclusive = 0;
-        if (tile == 0) {
-            status[0] = kTilePrefix | static_cast<unsigned long long>(total);
-        } else {
-            status[tile] = kTileAggregate | static_cast<unsigned long long>(total);
-            long long start = clock64();
-            int t = tile - 1;
-            while (t >= 0) {
-                unsigned long long v = status[t];
-                if (v == 0) {
+        bool failed = false;
+        if (tile > 0) {
+            if (lane == 0) {
+                status[tile] = kTileAggregate | static_cast<unsigned long long>(block_total);
+            }
+            const long long start = clock64();
+            int top = tile - 1;  // nearest predecessor not summed yet
+            while (true) {
+                const int t = top - lane;
+                unsigned long long v = 2ull << 62;  // before tile 0 stands a virtual tile with prefix 0
+                if (t >= 0) {
+                    v = status[t];
+                }
+                const unsigned ready = __ballot_sync(0xffffffffu, v != 0);
+                const unsigned prefix = __ballot_sync(0xffffffffu, (v >> 63) != 0);
+                const int nearest = prefix != 0 ? __ffs(prefix) - 1 : 31;
+                const unsigned need = nearest >= 31 ? 0xffffffffu : ((2u << nearest) - 1u);
+                if ((ready & need) != need) {
                     if (clock64() - start > kLookbackBudgetCycles) {
-                        s_failed = 1;
-                        raise_status(p.status, LAT_STATUS_WAIT_TIMEOUT);
+                        failed = true;
                         break;
                     }
                     continue;
                 }
-                exclusive += static_cast<long long>(v & kTileValueMask);
-                if (v & kTilePrefix) {
+                long long part = lane <= nearest ? static_cast<long long>(v & kTileValueMask) : 0;
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) {
+                    part += __shfl_xor_sync(0xffffffffu, part, d);
+                }
+                exclusive += part;
+                if (prefix != 0) {
                     break;
                 }
-                --t;
+                top -= 32;
             }
-            status[tile] = kTilePrefix | static_cast<unsigned long long>(exclusive + total);
         }
-        s_base = static_cast<int>(exclusive);
-        if (tile == num_tiles - 1 && !s_failed) {
-            p.counts[0] = static_cast<int>(exclusive + total);
-            p.counts[1] = n_out;
+        if (lane == 0) {
+            if (failed) {
+                s_failed = 1;
+                raise_status(p.status, LAT_STATUS_WAIT_TIMEOUT);
+            } else {
+                status[tile] = kTilePrefix | static_cast<unsigned long long>(exclusive + block_total);
+                if (tile == num_tiles - 1) {
+                    p.counts[0] = static_cast<int>(exclusive + block_total);
+                    p.counts[1] = n_out;
+                }
+            }
+            s_base = static_cast<int>(exclusive);
         }
     }
     __syncthreads();
     if (s_failed) {
         return;
     }
+
+    // 4. write this lane's row
     my_start += s_base + warp_total[warp];
     const int total_after = my_start + __popc(my_mask);  // == E for rows at and beyond n_out
     if (my_row < n_out) {
@@ -631,21 +696,37 @@ __global__ void __launch_bounds__(kBlockThreads) map_single_pass_kernel(
             p.row_offsets[my_row] = total_after;
         }
     }
-    for (int j = 0; j < 32; ++j) {
-        const int row = row0 + j;
-        if (row >= n_out) {
-            break;
+    if (total_after > p.edge_capacity) {
+        if (my_mask != 0) {
+            raise_status(p.status, LAT_STATUS_EDGE_OVERFLOW);
         }
-        const unsigned m = __shfl_sync(0xffffffffu, my_mask, j);
-        const int start = __shfl_sync(0xffffffffu, my_start, j);
-        if ((m >> lane) & 1u) {
-            const int pos = start + __popc(m & lanemask_lt());
+    }
+    if (wtotal <= 4 * 32) {
+        // few edges per row: each lane walks its own row's hits
+        unsigned bits = my_mask;
+        int pos = my_start;
+        while (bits != 0) {
+            const int k = __ffs(bits) - 1;
+            bits &= bits - 1;
             if (pos < p.edge_capacity) {
-                p.in_rows[pos] = warp_hits[j * K + lane];
-                p.out_rows[pos] = row;
-                p.kernel_ids[pos] = lane;
-            } else {
-                raise_status(p.status, LAT_STATUS_EDGE_OVERFLOW);
+                p.in_rows[pos] = warp_hits[lane * K + k];
+                p.out_rows[pos] = my_row;
+                p.kernel_ids[pos] = k;
+            }
+            ++pos;
+        }
+    } else {
+        // many edges per row: one row at a time, lane = kernel offset, contiguous stores
+        for (int j = 0; j < 32; ++j) {
+            const unsigned m = __shfl_sync(0xffffffffu, my_mask, j);
+            const int start = __shfl_sync(0xffffffffu, my_start, j);
+            if ((m >> lane) & 1u) {
+                const int pos = start + __popc(m & lanemask_lt());
+                if (pos < p.edge_capacity) {
+                    p.in_rows[pos] = warp_hits[j * K + lane];
+                    p.out_rows[pos] = row0 + j;
+                    p.kernel_ids[pos] = lane;
+                }
             }
         }
     }
@@ -1310,7 +1391,7 @@ int run_map(
         LAT_CUDA_CHECK(cudaMemsetAsync(ticket, 0, sizeof(int), stream));
         p.masks = o.row_masks;  // optional output; no scratch copy needed
         size_t smem = sizeof(int) * kRowsPerBlock * K;
-        map_single_pass_kernel<<<nblocks, kBlockThreads, smem, stream>>>(p, tile_status, ticket, nblocks);
+        map_single_pass_kernel<1, 5><<<nblocks, kBlockThreads, smem, stream>>>(p, tile_status, ticket, nblocks);
         LAT_LAUNCH_CHECK();
         return LAT_OK;
     }

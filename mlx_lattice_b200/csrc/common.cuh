@@ -57,6 +57,14 @@ inline int next_pow2(long long value) {
     return static_cast<int>(out);
 }
 
+// Slots of the hash table that holds `rows` keys: a power of two with a load factor in
+// (1/8, 1/4], so that a bucket of four slots is almost never full and a probe is one
+// sector read. Beyond 2^28 rows the factor halves to keep the slot count in an int.
+inline int table_slots(long long rows) {
+    rows = rows < 1 ? 1 : rows;
+    return next_pow2((rows > (1LL << 28) ? 2 : 4) * rows);
+}
+
 // Bump allocator over the caller's workspace.
 struct Workspace {
     char* base;

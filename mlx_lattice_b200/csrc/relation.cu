@@ -541,6 +541,7 @@ __global__ void __launch_bounds__(kBlockThreads, kMinBlocks) map_single_pass_ker
 
     // 1. probe
     unsigned my_mask = 0;
+    unsigned my_overflow = 0;  // offsets whose first bucket was full without a tag match
     int* warp_hits = s_hits + warp * 32 * K;
     for (int j = 0; j < 32; j += kProbeRows) {
         if (row0 + j >= n_out) {
@@ -548,7 +549,6 @@ __global__ void __launch_bounds__(kBlockThreads, kMinBlocks) map_single_pass_ker
         }
         bool live[kProbeRows];
         uint32_t tag[kProbeRows];
-        uint32_t base[kProbeRows];
         Bucket bucket[kProbeRows];
 #pragma unroll
         for (int u = 0; u < kProbeRows; ++u) {
@@ -564,9 +564,8 @@ __global__ void __launch_bounds__(kBlockThreads, kMinBlocks) map_single_pass_ker
                 live[u] = candidate_of(p, Coord{r.x, r.y, r.z, r.w}, ox, oy, oz, cand);
                 hash_coord(cand, index, tag[u]);
             }
-            base[u] = index & p.table_mask & ~(kBucketSlots - 1);
             if (live[u]) {
-                bucket[u] = load_bucket(p.table, base[u]);
+                bucket[u] = load_bucket(p.table, index & p.table_mask & ~(kBucketSlots - 1));
             }
         }
 #pragma unroll
@@ -574,16 +573,12 @@ __global__ void __launch_bounds__(kBlockThreads, kMinBlocks) map_single_pass_ker
             int found = -1;
             if (live[u]) {
                 found = scan_bucket_tags(bucket[u], tag[u]);
-                for (uint32_t probe = kBucketSlots; found == -2 && probe <= p.table_mask;
-                     probe += kBucketSlots) {
-                    base[u] = (base[u] + kBucketSlots) & p.table_mask;
-                    bucket[u] = load_bucket(p.table, base[u]);
-                    found = scan_bucket_tags(bucket[u], tag[u]);
-                }
             }
             const unsigned m = __ballot_sync(0xffffffffu, found >= 0);
+            const unsigned full = __ballot_sync(0xffffffffu, found == -2);
             if (lane == j + u) {
                 my_mask = m;
+                my_overflow = full;
             }
             if (lane < K) {
                 warp_hits[(j + u) * K + lane] = found;
@@ -610,6 +605,20 @@ __global__ void __launch_bounds__(kBlockThreads, kMinBlocks) map_single_pass_ker
                     my_mask &= ~(1u << k);
                 }
             }
+        }
+    }
+    // candidates that ran past their first bucket take the exact lookup (rare at this
+    // load factor), here rather than in the probe loop where one lane would hold up 32
+    while (my_overflow != 0) {
+        const int k = __ffs(my_overflow) - 1;
+        my_overflow &= my_overflow - 1;
+        const int4 off = s_offset[k];
+        Coord expect;
+        candidate_of(p, mine, off.x, off.y, off.z, expect);
+        const int exact = table_find(p.table, p.table_mask, expect, key_of);
+        if (exact >= 0) {
+            warp_hits[lane * K + k] = exact;
+            my_mask |= 1u << k;
         }
     }
     if (p.masks != nullptr && my_row < p.out_capacity) {
@@ -1289,7 +1298,7 @@ int build_source_table(
     Workspace& ws, const int32_t* coords, int rows, const int32_t* active_rows,
     int32_t* status, bool flag_duplicates, cudaStream_t stream, SourceTable& table
 ) {
-    int capacity = next_pow2(std::max(2LL * rows, 1LL));
+    int capacity = table_slots(rows);
     table.slots = ws.take<Slot>(capacity);
     table.mask = static_cast<uint32_t>(capacity - 1);
     if (!ws.ok) {
@@ -1422,8 +1431,8 @@ size_t lat_relation_workspace_bytes(int32_t rows, int32_t out_rows, int32_t kern
     size_t r = static_cast<size_t>(std::max(rows, 1));
     size_t o = static_cast<size_t>(std::max(out_rows, 1));
     size_t total = 0;
-    total += align_up(sizeof(Slot) * next_pow2(2 * r));              // source table
-    total += align_up(sizeof(Slot) * next_pow2(2 * std::max(r, o)));     // second table
+    total += align_up(sizeof(Slot) * table_slots(r));              // source table
+    total += align_up(sizeof(Slot) * table_slots(std::max(r, o)));     // second table
     total += align_up(sizeof(int32_t) * o * words);                  // masks
     size_t nblocks = (std::max(o, r * 1) + kRowsPerBlock) / kRowsPerBlock + 2;
     total += 3 * align_up(sizeof(int32_t) * nblocks);                // block sums
@@ -1497,7 +1506,7 @@ int lat_build_kernel_relation(
         store_clamped_kernel<<<1, 1, 0, stream>>>(active_rows, rows, out_count);
         LAT_LAUNCH_CHECK();
     } else {
-        int capacity = next_pow2(std::max(2LL * rows, 1LL));
+        int capacity = table_slots(rows);
         Slot* table2 = ws.take<Slot>(capacity);
         int nblocks = blocks_for(rows);
         int32_t* sums = ws.take<int32_t>(nblocks);
@@ -1616,7 +1625,7 @@ int lat_build_transposed_kernel_relation(
     if (rc != LAT_OK) {
         return rc;
     }
-    int cap2 = next_pow2(std::max(2LL * capacity, 1LL));
+    int cap2 = table_slots(capacity);
     Slot* table2 = ws.take<Slot>(cap2);
     int nblocks = std::max(1, blocks_for(capacity));
     int32_t* sums = ws.take<int32_t>(nblocks);
@@ -1848,7 +1857,7 @@ int lat_build_relation_grouped_view(
 }
 
 size_t lat_implicit_gemm_view_workspace_bytes(int32_t source_rows) {
-    return align_up(sizeof(Slot) * next_pow2(2LL * std::max(source_rows, 1))) + 1024;
+    return align_up(sizeof(Slot) * table_slots(source_rows)) + 1024;
 }
 
 int lat_build_relation_implicit_gemm_view(
@@ -1868,7 +1877,7 @@ int lat_build_relation_implicit_gemm_view(
         return LAT_OK;
     }
     Workspace ws(workspace, workspace_bytes);
-    int capacity = next_pow2(std::max(2LL * source_rows, 1LL));
+    int capacity = table_slots(source_rows);
     Slot* table = ws.take<Slot>(capacity);
     if (!ws.ok) {
         return fail(LAT_WORKSPACE_TOO_SMALL, "workspace is too small for the implicit GEMM view.");
@@ -1892,7 +1901,7 @@ int lat_build_relation_implicit_gemm_view(
 
 size_t lat_coord_set_workspace_bytes(int32_t rows) {
     size_t r = static_cast<size_t>(std::max(rows, 1));
-    return align_up(sizeof(Slot) * next_pow2(2 * r)) +
+    return align_up(sizeof(Slot) * table_slots(r)) +
            align_up(sizeof(int32_t) * ((r + kBlockThreads) / kBlockThreads + 1)) + 1024;
 }
 
@@ -1909,7 +1918,7 @@ int lat_downsample_coords(
         return LAT_OK;
     }
     Workspace ws(workspace, workspace_bytes);
-    int capacity = next_pow2(2LL * rows);
+    int capacity = table_slots(rows);
     Slot* table = ws.take<Slot>(capacity);
     int nblocks = blocks_for(rows);
     int32_t* sums = ws.take<int32_t>(nblocks);
@@ -1946,7 +1955,7 @@ int lat_lookup_coords(
         return LAT_OK;
     }
     Workspace ws(workspace, workspace_bytes);
-    int capacity = next_pow2(std::max(2LL * rows, 1LL));
+    int capacity = table_slots(rows);
     Slot* table = ws.take<Slot>(capacity);
     if (!ws.ok) {
         return fail(LAT_WORKSPACE_TOO_SMALL, "workspace is too small for the coordinate set.");
@@ -1967,8 +1976,8 @@ int lat_lookup_coords(
 size_t lat_sparse_alignment_workspace_bytes(int32_t lhs_rows, int32_t rhs_rows) {
     size_t l = static_cast<size_t>(std::max(lhs_rows, 1));
     size_t r = static_cast<size_t>(std::max(rhs_rows, 1));
-    return align_up(sizeof(Slot) * next_pow2(2 * l)) +
-           align_up(sizeof(Slot) * next_pow2(2 * r)) + align_up(sizeof(int32_t) * l) +
+    return align_up(sizeof(Slot) * table_slots(l)) +
+           align_up(sizeof(Slot) * table_slots(r)) + align_up(sizeof(int32_t) * l) +
            align_up(sizeof(int32_t) * r) +
            2 * align_up(sizeof(int32_t) * ((std::max(l, r) + kBlockThreads) / kBlockThreads + 1)) +
            2048;

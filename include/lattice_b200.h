@@ -234,7 +234,10 @@ int lat_build_sparse_alignment(
  * and are therefore not part of this signature. Optional `bias` [out_channels]
  * (feature dtype) is added after the final cast (mlx_lattice/ops/conv.py:460-469),
  * optional `row_order` [out_capacity] is a permutation of output rows that the
- * tensor-core route uses to form its 128-row tiles (any permutation is valid). */
+ * tensor-core route uses to form its 256-row tiles (any permutation is valid),
+ * optional `plan` is the gather plan built by lat_build_conv_plan over this relation
+ * and this `row_order` (the tensor-core route then reads it instead of the relation
+ * arrays; other routes ignore it). */
 size_t lat_sparse_conv_workspace_bytes(int32_t n_kernels, int32_t in_channels, int32_t out_channels);
 int lat_sparse_conv_features(
     int32_t dtype, const void* feats, int32_t in_capacity, int32_t in_channels,
@@ -243,7 +246,7 @@ int lat_sparse_conv_features(
     const int32_t* in_rows, const int32_t* out_rows, const int32_t* kernel_ids,
     int32_t edge_capacity, const int32_t* counts, const int32_t* row_offsets,
     int32_t out_capacity, int32_t n_kernels,
-    const void* bias, const int32_t* row_order, void* out,
+    const void* bias, const int32_t* row_order, const void* plan, void* out,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
 /* native/bindings/convolution.cpp:12-89 (`sparse_quantized_conv_features`) ->
@@ -260,8 +263,23 @@ int lat_sparse_quantized_conv_features(
     int32_t edge_capacity, const int32_t* counts, const int32_t* row_offsets,
     int32_t out_capacity, int32_t n_kernels, int32_t in_channels, int32_t out_channels,
     int32_t storage_in_channels, int32_t group_size, int32_t bits,
-    const void* bias, const int32_t* row_order, void* out,
+    const void* bias, const int32_t* row_order, const void* plan, void* out,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* Gather plan of the tensor-core route for one relation (no reference counterpart;
+ * it takes the place of the per-call walk over the relation that the reference's
+ * implicit-GEMM view, native/features/coordinates/cpu/relations.cpp, prepares on the
+ * host side). The output rows in `row_order` (natural order when NULL) are cut into
+ * 256-row tiles; per tile the plan holds the mask of kernel offsets its rows use and,
+ * per used offset, the input row of each tile row (-1 = none). Build it once per
+ * relation after `row_order`, then pass `plan` together with the same `row_order` to
+ * the convolutions over that relation. kernel_count <= 32. */
+size_t lat_conv_plan_bytes(int32_t out_capacity, int32_t kernel_count);
+int lat_build_conv_plan(
+    const int32_t* in_rows, const int32_t* kernel_ids, int32_t edge_capacity,
+    const int32_t* counts, const int32_t* row_offsets, int32_t in_capacity,
+    int32_t out_capacity, int32_t kernel_count, const int32_t* row_order,
+    void* plan, size_t plan_bytes, int32_t* status, void* stream);
 
 /* 1 when the tensor-core (tcgen05) route serves this shape, 0 when the CUDA-core
  * route does. Informational; both routes give results inside the tolerance. */

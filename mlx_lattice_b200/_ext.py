@@ -554,7 +554,7 @@ def _weight_geometry(weights: torch.Tensor, n_kernels: int, in_channels: int):
 def sparse_conv_features(
     feats, weights, in_rows, out_rows, kernel_ids, counts, row_offsets,
     in_row_offsets=None, in_edge_ids=None, kernel_row_offsets=None, kernel_edge_ids=None,
-    out_capacity=None, n_kernels=None, *, bias=None, row_order=None,
+    out_capacity=None, n_kernels=None, *, bias=None, row_order=None, plan=None,
 ):
     """``_ext.sparse_conv_features`` (``convolution.cpp:90-146``). The four grouped
     view arguments are accepted for signature compatibility; the forward pass does
@@ -587,8 +587,8 @@ def sparse_conv_features(
             dtype, _ptr(feats), int(feats.shape[0]), c_in, stride, _ptr(weights), layout, shape,
             c_out, _ptr(in_rows), _ptr(out_rows), _ptr(kernel_ids), int(in_rows.shape[0]),
             _ptr(counts), _ptr(row_offsets), out_capacity, n_kernels, _ptr(bias),
-            _ptr(row_order), _ptr(out), _ptr(ws), ws.numel(), _ptr(status_word(device)),
-            _stream(),
+            _ptr(row_order), _ptr(plan), _ptr(out), _ptr(ws), ws.numel(),
+            _ptr(status_word(device)), _stream(),
         )))
     return out
 
@@ -598,6 +598,7 @@ def sparse_quantized_conv_features(
     sorted_kv_out_in_map=None, reorder_rows=None, tile_masks=None,
     out_capacity=None, n_kernels=None, in_channels=None, out_channels=None,
     storage_in_channels=None, group_size=None, bits=None, *, bias=None, row_order=None,
+    plan=None,
 ):
     """``_ext.sparse_quantized_conv_features`` (``convolution.cpp:12-89``). The
     three sorted-plan arrays may be empty in the reference call; here a non-empty
@@ -648,7 +649,7 @@ def sparse_quantized_conv_features(
             _ptr(biases), _ptr(in_rows), _ptr(out_rows), _ptr(kernel_ids),
             int(in_rows.shape[0]), _ptr(counts), _ptr(row_offsets), out_capacity, n_kernels,
             in_channels, out_channels, storage, group_size, bits, _ptr(bias), _ptr(row_order),
-            _ptr(out), _ptr(ws), ws.numel(), _ptr(status_word(device)), _stream(),
+            _ptr(plan), _ptr(out), _ptr(ws), ws.numel(), _ptr(status_word(device)), _stream(),
         )))
     return out
 
@@ -656,6 +657,26 @@ def sparse_quantized_conv_features(
 def conv_uses_tensor_cores(dtype, n_kernels, in_channels, out_channels, bits=0, group_size=0) -> bool:
     return bool(_lib().lat_conv_uses_tensor_cores(
         _dtype_code(dtype), n_kernels, in_channels, out_channels, bits, group_size))
+
+
+def build_conv_plan(in_rows, kernel_ids, counts, row_offsets, in_capacity: int,
+                    out_capacity: int, kernel_count: int, row_order=None) -> torch.Tensor:
+    """Gather plan of the tensor-core convolution over one relation
+    (``lat_build_conv_plan``): per 256-row tile of ``row_order`` the mask of kernel
+    offsets in use and, per used offset, the input row of every tile row."""
+    in_rows, kernel_ids = _i32(in_rows, 'in_rows'), _i32(kernel_ids, 'kernel_ids')
+    counts, row_offsets = _i32(counts, 'counts'), _i32(row_offsets, 'row_offsets')
+    device = in_rows.device
+    lib = _lib()
+    plan = torch.empty(max(int(lib.lat_conv_plan_bytes(out_capacity, kernel_count)), 256),
+                       dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        check(lib.lat_build_conv_plan(
+            _ptr(in_rows), _ptr(kernel_ids), int(in_rows.shape[0]), _ptr(counts),
+            _ptr(row_offsets), int(in_capacity), int(out_capacity), int(kernel_count),
+            _ptr(row_order), _ptr(plan), plan.numel(), _ptr(status_word(device)), _stream(),
+        ))
+    return plan
 
 
 def build_mask_row_order(row_masks, counts, kernel_count: int = 32):

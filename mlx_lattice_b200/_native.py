@@ -70,11 +70,13 @@ SIGNATURES = {
     'lat_build_sparse_alignment': (I, [P, I, P, P, I, P, I, P, P, P, P, P, c_size_t, P, P]),
     'lat_sparse_conv_workspace_bytes': (c_size_t, [I, I, I]),
     'lat_sparse_conv_features': (
-        I, [I, P, I, I, c_int64, P, I, Triple, I, P, P, P, I, P, P, I, I, P, P, P, P,
+        I, [I, P, I, I, c_int64, P, I, Triple, I, P, P, P, I, P, P, I, I, P, P, P, P, P,
             c_size_t, P, P]),
     'lat_sparse_quantized_conv_features': (
-        I, [I, P, I, c_int64, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P, P, P, P,
+        I, [I, P, I, c_int64, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P, P, P, P, P,
             c_size_t, P, P]),
+    'lat_conv_plan_bytes': (c_size_t, [I, I]),
+    'lat_build_conv_plan': (I, [P, P, I, P, P, I, I, I, P, P, c_size_t, P, P]),
     'lat_conv_uses_tensor_cores': (I, [I, I, I, I, I, I]),
     'lat_mask_order_workspace_bytes': (c_size_t, [I]),
     'lat_build_mask_row_order': (I, [P, I, I, P, P, P, c_size_t, P, P]),

@@ -19,6 +19,8 @@ SOURCES = (
     'relation.cu',
     'conv_direct.cu',
     'conv_tc.cu',
+    'conv_tc_plan.cu',
+    'conv_plan.cu',
     'order.cu',
     'static_scratch.cu',
     'pool.cu',

@@ -159,6 +159,7 @@ class KernelRelation:
         self.implicit_gemm: RelationImplicitGemmView | None = None
         self.sorted_implicit_gemm: RelationSortedImplicitGemmView | None = None
         self._row_order: torch.Tensor | None = None
+        self._conv_plan: torch.Tensor | None = None
 
     # -- contract ------------------------------------------------------------
     @property
@@ -291,3 +292,21 @@ class KernelRelation:
                 self.row_masks, self.counts, int(self.n_kernels or 32)
             )
         return self._row_order
+
+    def require_conv_plan(self) -> torch.Tensor | None:
+        """Gather plan of the tensor-core convolution over this relation, built once
+        and shared by every convolution that consumes the relation; None when the
+        relation has more than 32 kernel offsets or no static capacities."""
+        if self._conv_plan is None:
+            if self.n_kernels is None or self.n_kernels > 32 or self.n_out_capacity is None:
+                return None
+            if self.n_in_capacity is None:
+                return None
+            from mlx_lattice_b200 import _ext
+
+            self._conv_plan = _ext.build_conv_plan(
+                self.edges.in_rows, self.edges.kernel_ids, self.counts,
+                self.output_csr.row_offsets, int(self.n_in_capacity), int(self.n_out_capacity),
+                int(self.n_kernels), self.require_row_order(),
+            )
+        return self._conv_plan

@@ -41,8 +41,8 @@ int run_tc_conv(
     const void* biases, int storage_in_channels, int group_size, int bits, int out_channels,
     const int32_t* in_rows, const int32_t* kernel_ids, int edge_capacity, const int32_t* counts,
     const int32_t* row_offsets, int out_capacity, int n_kernels, const void* bias,
-    const int32_t* row_order, void* out, void* workspace, size_t workspace_bytes,
-    int32_t* status, cudaStream_t stream);
+    const int32_t* row_order, const void* plan, void* out, void* workspace,
+    size_t workspace_bytes, int32_t* status, cudaStream_t stream);
 
 } // namespace lat
 
@@ -135,7 +135,7 @@ int lat_sparse_conv_features(
     const int32_t* in_rows, const int32_t* out_rows, const int32_t* kernel_ids,
     int32_t edge_capacity, const int32_t* counts, const int32_t* row_offsets,
     int32_t out_capacity, int32_t n_kernels,
-    const void* bias, const int32_t* row_order, void* out,
+    const void* bias, const int32_t* row_order, const void* plan, void* out,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream_ptr
 ) {
     (void)out_rows;
@@ -158,7 +158,7 @@ int lat_sparse_conv_features(
         return run_tc_conv(feats, in_capacity, in_channels, feat_row_stride, weights,
                            weight_layout, nullptr, nullptr, nullptr, in_channels, 0, 0,
                            out_channels, in_rows, kernel_ids, edge_capacity, counts, row_offsets,
-                           out_capacity, n_kernels, bias, row_order, out, workspace,
+                           out_capacity, n_kernels, bias, row_order, plan, out, workspace,
                            workspace_bytes, status, stream);
     }
     return run_direct_conv(dtype, feats, in_capacity, in_channels, feat_row_stride, weights,
@@ -175,7 +175,7 @@ int lat_sparse_quantized_conv_features(
     int32_t edge_capacity, const int32_t* counts, const int32_t* row_offsets,
     int32_t out_capacity, int32_t n_kernels, int32_t in_channels, int32_t out_channels,
     int32_t storage_in_channels, int32_t group_size, int32_t bits,
-    const void* bias, const int32_t* row_order, void* out,
+    const void* bias, const int32_t* row_order, const void* plan, void* out,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream_ptr
 ) {
     (void)out_rows;
@@ -198,7 +198,7 @@ int lat_sparse_quantized_conv_features(
         return run_tc_conv(feats, in_capacity, in_channels, feat_row_stride, nullptr, 0, packed,
                            scales, biases, storage_in_channels, group_size, bits, out_channels,
                            in_rows, kernel_ids, edge_capacity, counts, row_offsets, out_capacity,
-                           n_kernels, bias, row_order, out, workspace, workspace_bytes, status,
+                           n_kernels, bias, row_order, plan, out, workspace, workspace_bytes, status,
                            stream);
     }
     return run_direct_conv(dtype, feats, in_capacity, in_channels, feat_row_stride, nullptr, 0,

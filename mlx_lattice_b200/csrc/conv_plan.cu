@@ -1,0 +1,221 @@
+// Gather plan of the tensor-core convolution for one kernel relation.
+//
+// The output rows, taken through an optional permutation, are cut into 256-row tiles.
+// For every tile the plan holds
+//   tile_info[tile] = (mask, base): the kernel offsets any row of the tile uses, and the
+//                     index of the tile's first row vector;
+//   one row vector per used offset, in ascending offset order: the input row of each of
+//   the 256 tile rows at that offset, -1 where the row has no neighbour there.
+// The convolution kernel then streams these vectors instead of walking the CSR rows of
+// the relation tile by tile (three dependent loads per row before the first gather),
+// and a relation is usually consumed by several convolutions.
+//
+// A row vector is stored in the order the gather threads read it: tile row r sits at
+// (r % 32) * 8 + r / 32, so the eight rows q, q + 32, ... q + 224 of gather thread group
+// q are 32 contiguous bytes.
+#include <algorithm>
+
+#include "common.cuh"
+#include "conv_plan.cuh"
+
+namespace lat {
+
+namespace {
+
+struct PlanBuildParams {
+    const int32_t* in_rows;
+    const int32_t* kernel_ids;
+    const int32_t* row_offsets;
+    const int32_t* counts;
+    const int32_t* row_order;
+    int edge_capacity;
+    int in_capacity;
+    int out_capacity;
+    int kernel_count;
+    int num_tiles;
+    int2* tile_info;
+    int32_t* vectors;
+    int32_t* status;
+};
+
+// the output row a tile position stands for, -1 beyond the capacity or when invalid
+__device__ __forceinline__ int plan_row(const PlanBuildParams& p, int position) {
+    if (position >= p.out_capacity) {
+        return -1;
+    }
+    int row = p.row_order != nullptr ? __ldg(p.row_order + position) : position;
+    if (row < 0 || row >= p.out_capacity) {
+        raise_status(p.status, LAT_STATUS_BAD_INDEX);
+        return -1;
+    }
+    return row;
+}
+
+// pass 1: offset mask of every tile
+__global__ void __launch_bounds__(kPlanTileRows) plan_mask_kernel(PlanBuildParams p) {
+    __shared__ uint32_t tile_mask;
+    if (threadIdx.x == 0) {
+        tile_mask = 0;
+    }
+    __syncthreads();
+    const int n_out = clamp_count(p.counts + 1, p.out_capacity);
+    const int edge_total = clamp_count(p.counts, p.edge_capacity);
+    const int row = plan_row(p, blockIdx.x * kPlanTileRows + threadIdx.x);
+    uint32_t mask = 0;
+    if (row >= 0 && row < n_out) {
+        const int begin = max(__ldg(p.row_offsets + row), 0);
+        const int end = min(__ldg(p.row_offsets + row + 1), edge_total);
+        for (int e = begin; e < end; ++e) {
+            const int k = __ldg(p.kernel_ids + e);
+            if (k >= 0 && k < p.kernel_count) {
+                mask |= 1u << k;
+            }
+        }
+    }
+    mask = __reduce_or_sync(0xffffffffu, mask);
+    if ((threadIdx.x & 31) == 0 && mask != 0) {
+        atomicOr(&tile_mask, mask);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        p.tile_info[blockIdx.x] = make_int2(static_cast<int>(tile_mask), 0);
+    }
+}
+
+// pass 2: exclusive scan of the vectors per tile (one block); the entry after the last
+// tile receives (tiles up to the last one with a non-empty mask, vector total)
+__global__ void __launch_bounds__(1024) plan_scan_kernel(int2* tile_info, int num_tiles) {
+    __shared__ int warp_totals[32];
+    __shared__ int carry;
+    __shared__ int active_tiles;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        carry = 0;
+        active_tiles = 0;
+    }
+    __syncthreads();
+    for (int first = 0; first < num_tiles; first += 1024) {
+        const int tile = first + threadIdx.x;
+        int2 info = make_int2(0, 0);
+        if (tile < num_tiles) {
+            info = tile_info[tile];
+        }
+        int wtotal;
+        const int prefix = warp_exclusive_scan(__popc(static_cast<uint32_t>(info.x)), wtotal);
+        if (lane == 0) {
+            warp_totals[warp] = wtotal;
+        }
+        __syncthreads();
+        int before = carry;
+        for (int w = 0; w < warp; ++w) {
+            before += warp_totals[w];
+        }
+        if (tile < num_tiles) {
+            tile_info[tile] = make_int2(info.x, before + prefix);
+            if (info.x != 0) {
+                atomicMax(&active_tiles, tile + 1);
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 1023) {
+            carry = before + prefix + __popc(static_cast<uint32_t>(info.x));
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        tile_info[num_tiles] = make_int2(active_tiles, carry);
+    }
+}
+
+// pass 3: the row vectors
+__global__ void __launch_bounds__(kPlanTileRows) plan_fill_kernel(PlanBuildParams p) {
+    const int n_out = clamp_count(p.counts + 1, p.out_capacity);
+    const int edge_total = clamp_count(p.counts, p.edge_capacity);
+    const int2 info = p.tile_info[blockIdx.x];
+    const uint32_t mask = static_cast<uint32_t>(info.x);
+    const int present = __popc(mask);
+    const int r = threadIdx.x;
+    int32_t* mine = p.vectors + static_cast<size_t>(info.y) * kPlanTileRows + plan_slot(r);
+    for (int o = 0; o < present; ++o) {
+        mine[static_cast<size_t>(o) * kPlanTileRows] = -1;
+    }
+    const int row = plan_row(p, blockIdx.x * kPlanTileRows + r);
+    if (row >= 0 && row < n_out) {
+        const int begin = max(__ldg(p.row_offsets + row), 0);
+        const int end = min(__ldg(p.row_offsets + row + 1), edge_total);
+        for (int e = begin; e < end; ++e) {
+            const int k = __ldg(p.kernel_ids + e);
+            const int in_row = __ldg(p.in_rows + e);
+            if (in_row < 0 || k < 0) {
+                continue;
+            }
+            if (in_row >= p.in_capacity || k >= p.kernel_count) {
+                raise_status(p.status, LAT_STATUS_BAD_INDEX);
+                continue;
+            }
+            const int o = __popc(mask & ((1u << k) - 1u));
+            mine[static_cast<size_t>(o) * kPlanTileRows] = in_row;
+        }
+    }
+}
+
+} // namespace
+
+} // namespace lat
+
+using namespace lat;
+
+extern "C" {
+
+size_t lat_conv_plan_bytes(int32_t out_capacity, int32_t kernel_count) {
+    const size_t tiles = static_cast<size_t>(plan_tiles(out_capacity));
+    return plan_info_bytes(static_cast<int>(tiles)) +
+           tiles * static_cast<size_t>(std::max(kernel_count, 1)) * kPlanTileRows * sizeof(int32_t);
+}
+
+int lat_build_conv_plan(
+    const int32_t* in_rows, const int32_t* kernel_ids, int32_t edge_capacity,
+    const int32_t* counts, const int32_t* row_offsets, int32_t in_capacity,
+    int32_t out_capacity, int32_t kernel_count, const int32_t* row_order,
+    void* plan, size_t plan_bytes, int32_t* status, void* stream_ptr
+) {
+    LAT_REQUIRE(out_capacity >= 0 && edge_capacity >= 0 && in_capacity >= 0,
+                "capacities must be non-negative.");
+    LAT_REQUIRE(kernel_count >= 1 && kernel_count <= 32,
+                "the gather plan serves kernels of at most 32 offsets.");
+    LAT_REQUIRE(counts != nullptr && row_offsets != nullptr, "counts and row_offsets are required.");
+    LAT_REQUIRE((in_rows != nullptr && kernel_ids != nullptr) || edge_capacity == 0,
+                "in_rows and kernel_ids are required.");
+    LAT_REQUIRE(plan != nullptr && reinterpret_cast<uintptr_t>(plan) % 16 == 0,
+                "plan must be a 16-byte aligned device buffer.");
+    LAT_REQUIRE(plan_bytes >= lat_conv_plan_bytes(out_capacity, kernel_count),
+                "plan buffer is smaller than lat_conv_plan_bytes.");
+    if (out_capacity == 0) {
+        return LAT_OK;
+    }
+    cudaStream_t stream = as_stream(stream_ptr);
+    PlanBuildParams p{};
+    p.in_rows = in_rows;
+    p.kernel_ids = kernel_ids;
+    p.row_offsets = row_offsets;
+    p.counts = counts;
+    p.row_order = row_order;
+    p.edge_capacity = edge_capacity;
+    p.in_capacity = in_capacity;
+    p.out_capacity = out_capacity;
+    p.kernel_count = kernel_count;
+    p.num_tiles = plan_tiles(out_capacity);
+    p.tile_info = static_cast<int2*>(plan);
+    p.vectors = reinterpret_cast<int32_t*>(static_cast<char*>(plan) + plan_info_bytes(p.num_tiles));
+    p.status = status;
+    plan_mask_kernel<<<p.num_tiles, kPlanTileRows, 0, stream>>>(p);
+    LAT_LAUNCH_CHECK();
+    plan_scan_kernel<<<1, 1024, 0, stream>>>(p.tile_info, p.num_tiles);
+    LAT_LAUNCH_CHECK();
+    plan_fill_kernel<<<p.num_tiles, kPlanTileRows, 0, stream>>>(p);
+    LAT_LAUNCH_CHECK();
+    return LAT_OK;
+}
+
+} // extern "C"

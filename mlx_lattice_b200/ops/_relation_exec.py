@@ -15,6 +15,14 @@ def _row_order(relation: KernelRelation, uses_tensor_cores: bool):
     return relation.require_row_order()
 
 
+def _conv_plan(relation: KernelRelation, uses_tensor_cores: bool, in_rows: int):
+    """The relation's gather plan when the tensor-core route runs and the features
+    have the row capacity the plan was validated against."""
+    if not uses_tensor_cores or relation.n_in_capacity != in_rows:
+        return None
+    return relation.require_conv_plan()
+
+
 def sparse_quantized_conv_features_from_relation(
     feats: torch.Tensor, weight: QuantizedWeight, relation: KernelRelation, bias=None
 ) -> torch.Tensor:
@@ -49,6 +57,7 @@ def sparse_quantized_conv_features_from_relation(
         weight.bits,
         bias=bias,
         row_order=_row_order(relation, tc),
+        plan=_conv_plan(relation, tc, int(feats.shape[0])),
     )
 
 
@@ -74,6 +83,7 @@ def sparse_conv_features_from_relation(
         n_kernels=relation.n_kernels,
         bias=bias,
         row_order=_row_order(relation, tc),
+        plan=_conv_plan(relation, tc, int(feats.shape[0])),
     )
 
 

@@ -29,10 +29,26 @@ def _max_rel_err(got, want):
     return np.abs(got - want).max() / (scale if scale > 0 else 1.0)
 
 
-def _conv(cuda, feats, weights, rel, out_capacity, n_kernels, bias=None, row_order=None):
+def _plan(cuda, r, in_capacity, out_capacity, n_kernels, row_order):
+    from mlx_lattice_b200 import _ext
+
+    return _ext.build_conv_plan(r['in_rows'], r['kernel_ids'], r['counts'], r['row_offsets'],
+                                in_capacity, out_capacity, n_kernels, row_order)
+
+
+def _conv(cuda, feats, weights, rel, out_capacity, n_kernels, bias=None, row_order=None,
+          with_plan=False):
     from mlx_lattice_b200 import _ext
 
     r = _rel_dev(rel, cuda)
+    order = None if row_order is None else _dev(row_order, cuda)
+    plan = _plan(cuda, r, feats.shape[0], out_capacity, n_kernels, order) if with_plan else None
+    if with_plan:
+        return _ext.sparse_conv_features(
+            _dev(feats, cuda), _dev(weights, cuda), r['in_rows'], r['out_rows'], r['kernel_ids'],
+            r['counts'], r['row_offsets'], out_capacity=out_capacity, n_kernels=n_kernels,
+            bias=None if bias is None else _dev(bias, cuda), row_order=order,
+            plan=plan).cpu().numpy()
     out = _ext.sparse_conv_features(
         _dev(feats, cuda), _dev(weights, cuda), r['in_rows'], r['out_rows'], r['kernel_ids'],
         r['counts'], r['row_offsets'], out_capacity=out_capacity, n_kernels=n_kernels,
@@ -41,10 +57,19 @@ def _conv(cuda, feats, weights, rel, out_capacity, n_kernels, bias=None, row_ord
     return out.cpu().numpy()
 
 
-def _qconv(cuda, feats, q, rel, out_capacity, n_kernels, row_order=None):
+def _qconv(cuda, feats, q, rel, out_capacity, n_kernels, row_order=None, with_plan=False):
     from mlx_lattice_b200 import _ext
 
     r = _rel_dev(rel, cuda)
+    if with_plan:
+        order = None if row_order is None else _dev(row_order, cuda)
+        plan = _plan(cuda, r, feats.shape[0], out_capacity, n_kernels, order)
+        return _ext.sparse_quantized_conv_features(
+            _dev(feats, cuda), _dev(q['weight'].view(np.int32), cuda), _dev(q['scales'], cuda),
+            _dev(q['biases'], cuda), r['in_rows'], r['out_rows'], r['kernel_ids'], r['counts'],
+            r['row_offsets'], None, None, None, out_capacity, n_kernels, q['in_channels'],
+            q['out_channels'], q['storage_in_channels'], q['group_size'], q['bits'],
+            row_order=order, plan=plan).cpu().numpy()
     out = _ext.sparse_quantized_conv_features(
         _dev(feats, cuda), _dev(q['weight'].view(np.int32), cuda), _dev(q['scales'], cuda),
         _dev(q['biases'], cuda), r['in_rows'], r['out_rows'], r['kernel_ids'], r['counts'],
@@ -119,6 +144,53 @@ def test_quantized_conv_float16(cuda, oracle, restatement, sphere, bits, c_in, c
         q['storage_in_channels'], 32, bits)
     got = _qconv(cuda, feats, q, rel, n, 27)
     assert _max_rel_err(got, want) <= FP16_TOL
+
+
+@pytest.mark.parametrize('c_in,c_out', [(32, 32), (64, 128), (128, 64), (96, 48), (256, 256), (32, 16)])
+def test_conv_with_gather_plan(cuda, oracle, restatement, sphere, c_in, c_out):
+    """The plan-driven tensor-core kernel: same bits as the relation-walking one, in
+    natural row order and under a permutation, fp16 and packed int4 weights."""
+    coords, rel = sphere
+    n = coords.shape[0]
+    rng = np.random.default_rng(c_in * 31 + c_out)
+    feats = rng.normal(size=(n, c_in)).astype(np.float16)
+    w5 = (rng.normal(size=(c_out, 3, 3, 3, c_in)) * 0.05).astype(np.float16)
+    bias = rng.normal(size=c_out).astype(np.float16)
+    exact = oracle.sparse_conv(feats.astype(np.float32), w5.astype(np.float32), rel, n, 27)
+    base = _conv(cuda, feats, w5, rel, n, 27)
+    got = _conv(cuda, feats, w5, rel, n, 27, with_plan=True)
+    assert _max_rel_err(got, exact) <= FP16_TOL
+    assert np.array_equal(got, base)
+    order = np.random.default_rng(9).permutation(n).astype(np.int32)
+    assert np.array_equal(_conv(cuda, feats, w5, rel, n, 27, row_order=order, with_plan=True), base)
+    with_bias = _conv(cuda, feats, w5, rel, n, 27, bias=bias, with_plan=True)
+    assert np.array_equal(with_bias, _conv(cuda, feats, w5, rel, n, 27, bias=bias))
+    q = restatement.quantize_weight(w5, 32, 4)
+    want = oracle.sparse_quantized_conv(
+        feats, q['weight'], q['scales'], q['biases'], rel, n, 27, c_in, c_out,
+        q['storage_in_channels'], 32, 4)
+    got_q = _qconv(cuda, feats, q, rel, n, 27, row_order=order, with_plan=True)
+    assert _max_rel_err(got_q, want) <= FP16_TOL
+    assert np.array_equal(got_q, _qconv(cuda, feats, q, rel, n, 27))
+
+
+def test_gather_plan_strided_and_padding_rows(cuda, oracle, restatement):
+    """k=2, s=2 relation whose output capacity exceeds the live rows: plan tiles beyond
+    the live rows are empty and their output rows are zero."""
+    coords = synthetic.sphere_plane_batch(1, 2, 15000, 128)
+    n = coords.shape[0]
+    rel = oracle.build_kernel_relation(coords, None, kernel_size=2, stride=2)
+    n_out = int(rel['counts'][1])
+    rng = np.random.default_rng(12)
+    feats = rng.normal(size=(n, 64)).astype(np.float16)
+    w5 = (rng.normal(size=(128, 2, 2, 2, 64)) * 0.05).astype(np.float16)
+    q = restatement.quantize_weight(w5, 32, 4)
+    base = _qconv(cuda, feats, q, rel, n, 8)
+    got = _qconv(cuda, feats, q, rel, n, 8, with_plan=True)
+    assert np.array_equal(got, base)
+    assert not got[n_out:].any()
+    order = np.random.default_rng(6).permutation(n).astype(np.int32)
+    assert np.array_equal(_qconv(cuda, feats, q, rel, n, 8, row_order=order, with_plan=True), base)
 
 
 def test_quantized_conv_float32_and_group64(cuda, oracle, restatement, sphere):

@@ -40,13 +40,13 @@ constexpr int kSlabBytesA = kTileRows * 128;
 
 struct PlanConvParams {
     const __half* feats;
-    long long feat_stride;
+    int feat_row_bytes;
     int c_in;
     int c_out;
-    // fp16 weights addressed as base + k*w_stride_k + co*w_stride_co + ci
+    // fp16 weights addressed (in bytes) as base + k*w_k_bytes + co*w_co_bytes + 2*ci
     const __half* weights;
-    long long w_stride_k;
-    long long w_stride_co;
+    long long w_k_bytes;
+    long long w_co_bytes;
     const int2* tile_info;     // [num_tiles + 1]; the last entry holds (active tiles, vectors)
     const int32_t* vectors;
     const int32_t* row_order;
@@ -131,12 +131,16 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_plan_kernel(PlanConvParam
         const int a_half = a_chunk >> 2;        // which unit of a slab this thread feeds
         const int q = tid >> 3;                 // rows q + 32 j
         const int col8 = (a_chunk & 3) * 8;
-        uint32_t a_dst[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int r = q + 32 * j;
-            a_dst[j] = static_cast<uint32_t>(r * 128 + ((a_chunk ^ (r & 7)) << 4));
-        }
+        // shared-memory offset of (row q, this chunk); rows q + 32 j are 4096 j bytes on,
+        // with the same swizzle term because (q + 32 j) % 8 == q % 8. The B tile uses the
+        // same offsets for output channels q + 32 i.
+        const uint32_t dst0 = static_cast<uint32_t>(q * 128 + ((a_chunk ^ (q & 7)) << 4));
+        const char* const feat_bytes = reinterpret_cast<const char*>(p.feats);
+        const char* const weight_bytes = reinterpret_cast<const char*>(p.weights);
+        const int feat_row_bytes = p.feat_row_bytes;
+        const long long w_co0 = static_cast<long long>(q) * p.w_co_bytes;
+        const long long w_co_step = 32LL * p.w_co_bytes;
+        const int b_copies = p.c_out >> 5;  // C_out is a multiple of 32 here, or 16 (see below)
         Ring ring{0, 0u};
         bool ok = true;
 
@@ -214,20 +218,31 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_plan_kernel(PlanConvParam
                 ok = false;
                 break;
             }
-            const uint32_t a_addr = smem_u32(smem + ring.index * p.stage_bytes);
+            const uint32_t a_addr = smem_u32(smem + ring.index * p.stage_bytes) + dst0;
             const uint32_t b_addr = a_addr + kSlabBytesA;
-            const __half* col_base = p.feats + col;
+            const char* const col_base = feat_bytes + col * 2;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
+                // absent neighbours (and the unused half of an odd last slab) copy zero
+                // bytes from a valid address: the destination is zero-filled
                 const int in_row = uv ? idx[j] : -1;
-                const bool valid = in_row >= 0;
-                const __half* src = valid ? col_base + static_cast<size_t>(in_row) * p.feat_stride : p.feats;
-                cp_async_16(a_addr + a_dst[j], src, valid);
+                cp_async_16(a_addr + 4096 * j,
+                            col_base + static_cast<long long>(max(in_row, 0)) * feat_row_bytes,
+                            in_row >= 0);
             }
-            const __half* base = p.weights + static_cast<size_t>(k) * p.w_stride_k + col;
-            for (int co = q; co < p.c_out; co += 32) {
-                cp_async_16(b_addr + co * 128 + ((a_chunk ^ (co & 7)) << 4),
-                            base + static_cast<size_t>(co) * p.w_stride_co, uv);
+            const char* w_src = weight_bytes + static_cast<long long>(k) * p.w_k_bytes + col * 2 + w_co0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (i < b_copies) {
+                    cp_async_16(b_addr + 4096 * i, w_src, uv);
+                    w_src += w_co_step;
+                }
+            }
+            if (p.c_out & 16) {
+                // C_out = 32 m + 16: the last 16 output channels
+                if (q < 16) {
+                    cp_async_16(b_addr + 4096 * b_copies, w_src, uv);
+                }
             }
             cp_async_arrive_noinc(&ctl.full[ring.index]);
             ring.advance(p.stages);
@@ -397,12 +412,14 @@ int run_tc_conv_plan(
     }
     PlanConvParams p{};
     p.feats = static_cast<const __half*>(feats);
-    p.feat_stride = feat_stride;
+    LAT_REQUIRE(feat_stride > 0 && feat_stride * 2 < (1LL << 31),
+                "feature row stride is out of range for the tensor-core route.");
+    p.feat_row_bytes = static_cast<int>(feat_stride * 2);
     p.c_in = in_channels;
     p.c_out = out_channels;
     p.weights = static_cast<const __half*>(weights);
-    p.w_stride_k = w_stride_k;
-    p.w_stride_co = w_stride_co;
+    p.w_k_bytes = w_stride_k * 2;
+    p.w_co_bytes = w_stride_co * 2;
     p.num_tiles = plan_tiles(out_capacity);
     p.tile_info = static_cast<const int2*>(plan);
     p.vectors = reinterpret_cast<const int32_t*>(static_cast<const char*>(plan) + plan_info_bytes(p.num_tiles));

@@ -714,7 +714,7 @@ int pow2_at_least(int value, int floor_value) {
 // conv_tc_plan.cu
 int run_tc_conv_plan(
     const void* feats, int in_channels, long long feat_stride, const void* weights,
-    long long w_stride_k, long long w_stride_co, int out_channels, int out_capacity,
+    long long w_stride_k, long long w_stride_co, int n_kernels, int out_channels, int out_capacity,
     const void* bias, const int32_t* row_order, const void* plan, void* out, int32_t* status,
     cudaStream_t stream);
 
@@ -826,7 +826,7 @@ int run_tc_conv(
     if (plan != nullptr && packed == nullptr) {
         // fp16 weights and a prebuilt gather plan: the plan-driven kernel
         return run_tc_conv_plan(feats, in_channels, feat_stride, p.weights, p.w_stride_k,
-                                p.w_stride_co, out_channels, out_capacity, bias, row_order, plan,
+                                p.w_stride_co, n_kernels, out_channels, out_capacity, bias, row_order, plan,
                                 out, status, stream);
     }
     p.in_rows = in_rows;

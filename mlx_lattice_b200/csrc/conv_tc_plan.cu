@@ -17,7 +17,10 @@
 //   warps 8-15 epilogue: tcgen05.ld, optional bias, one cast to fp16, 16-byte stores.
 // Every mbarrier wait is bounded by a clock budget; on expiry the kernel records
 // LAT_STATUS_WAIT_TIMEOUT, every role leaves its loop and the CTA frees its TMEM.
+#include <cuda.h>
+
 #include <algorithm>
+#include <mutex>
 
 #include "common.cuh"
 #include "conv_plan.cuh"
@@ -60,6 +63,8 @@ struct PlanConvParams {
     int acc_cols;
     int acc_stages;
     int num_tiles;
+    int b_tma;           // 1: the B tile of a slab is one TMA box (C_in a multiple of 64)
+    int b_k_outer;       // tensor-map dimension order: 1 = (C_in, C_out, K), 0 = (C_in, K, C_out)
 };
 
 struct Ring {
@@ -86,7 +91,8 @@ __device__ __forceinline__ int2 load_info(const PlanConvParams& p, int tile, int
     return tile < active ? __ldg(p.tile_info + tile) : make_int2(0, 0);
 }
 
-__global__ void __launch_bounds__(kThreads, 1) tc_conv_plan_kernel(PlanConvParams p) {
+__global__ void __launch_bounds__(kThreads, 1)
+tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -101,7 +107,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_plan_kernel(PlanConvParam
 
     if (tid == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
-            mbar_init(&ctl.full[s], kProducerThreads);
+            mbar_init(&ctl.full[s], kProducerThreads + (p.b_tma ? 1 : 0));
             mbar_init(&ctl.empty[s], 1);
         }
         for (int a = 0; a < kMaxAccStages; ++a) {
@@ -144,6 +150,98 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_plan_kernel(PlanConvParam
         Ring ring{0, 0u};
         bool ok = true;
 
+        if ((upo & 1) == 0) {
+            // ---- C_in a multiple of 64: both units of a slab belong to one kernel offset ----
+            // The loop nest is tile > offset > slab; everything that depends on the input
+            // rows (eight source addresses and their zero-fill flags) is computed once per
+            // offset, and the next offset's row vector is loaded while the current one's
+            // slabs are issued, so a slab costs its copies and little else.
+            const int reps = upo >> 1;  // slabs per offset
+            const int unit_bytes = a_half * 64 + col8 * 2;  // this thread's 16 bytes inside a 128-byte K slab
+            int tile = blockIdx.x;
+            int2 info = load_info(p, tile, active);
+            int4 v0 = make_int4(-1, -1, -1, -1), v1 = v0;
+            auto load_vector = [&](int vector_index, int4& d0, int4& d1) {
+                const int4* src = reinterpret_cast<const int4*>(
+                    p.vectors + static_cast<size_t>(vector_index) * kTileRows + q * 8);
+                d0 = __ldg(src);
+                d1 = __ldg(src + 1);
+            };
+            if (tile < active && info.x != 0) {
+                load_vector(info.y, v0, v1);
+            }
+            while (tile < active && ok) {
+                int next_tile = tile + grid;
+                int2 next_info = load_info(p, next_tile, active);
+                uint32_t rem = static_cast<uint32_t>(info.x);
+                const int present = __popc(rem);
+                for (int o = 0; o < present && ok; ++o) {
+                    const int k = __ffs(rem) - 1;
+                    rem &= rem - 1;
+                    const int idx[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                    const char* src[8];
+                    uint32_t valid = 0;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        src[j] = feat_bytes + unit_bytes +
+                                 static_cast<long long>(max(idx[j], 0)) * feat_row_bytes;
+                        valid |= idx[j] >= 0 ? (1u << j) : 0u;
+                    }
+                    // the row vector of the next offset (of this tile, or the first of the
+                    // next tile that has any) travels while this offset's slabs are issued
+                    if (o + 1 < present) {
+                        load_vector(info.y + o + 1, v0, v1);
+                    } else {
+                        while (next_tile < active && next_info.x == 0) {
+                            next_tile += grid;
+                            next_info = load_info(p, next_tile, active);
+                        }
+                        if (next_tile < active) {
+                            load_vector(next_info.y, v0, v1);
+                        }
+                    }
+                    for (int r = 0; r < reps; ++r) {
+                        if (!mbar_wait(&ctl.empty[ring.index], ring.phase ^ 1u, abort_flag, p.status)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t a_addr = smem_u32(smem + ring.index * p.stage_bytes) + dst0;
+                        const uint32_t b_addr = a_addr + kSlabBytesA;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            cp_async_16(a_addr + 4096 * j, src[j] + r * 128, (valid >> j) & 1u);
+                        }
+                        if (p.b_tma) {
+                            if (tid == 0) {
+                                mbar_arrive_expect_tx(&ctl.full[ring.index],
+                                                      static_cast<uint32_t>(p.c_out) * 128u);
+                                tma_load_3d(b_addr - dst0, &b_map, r * 64, p.b_k_outer ? 0 : k,
+                                            p.b_k_outer ? k : 0, &ctl.full[ring.index]);
+                            }
+                        } else {
+                            const char* w_src = weight_bytes + static_cast<long long>(k) * p.w_k_bytes +
+                                                r * 128 + unit_bytes + w_co0;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                if (i < b_copies) {
+                                    cp_async_16(b_addr + 4096 * i, w_src, true);
+                                    w_src += w_co_step;
+                                }
+                            }
+                            if ((p.c_out & 16) && q < 16) {
+                                cp_async_16(b_addr + 4096 * b_copies, w_src, true);
+                            }
+                        }
+                        cp_async_arrive_noinc(&ctl.full[ring.index]);
+                        ring.advance(p.stages);
+                    }
+                }
+                tile = next_tile;
+                info = next_info;
+            }
+            cp_async_wait<0>();
+        } else {
+        // ---- general case: a slab may straddle two kernel offsets ----
         int tile = blockIdx.x;
         int2 info = load_info(p, tile, active);
         int2 next_info = load_info(p, tile + grid, active);
@@ -230,18 +328,30 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_plan_kernel(PlanConvParam
                             col_base + static_cast<long long>(max(in_row, 0)) * feat_row_bytes,
                             in_row >= 0);
             }
-            const char* w_src = weight_bytes + static_cast<long long>(k) * p.w_k_bytes + col * 2 + w_co0;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                if (i < b_copies) {
-                    cp_async_16(b_addr + 4096 * i, w_src, uv);
-                    w_src += w_co_step;
+            if (p.b_tma) {
+                // both units of the slab share the offset k: the B tile is one box of
+                // C_out rows x 64 channels, fetched by the TMA unit (thread 0's unit is the
+                // slab's first, so its k and column are the box origin)
+                if (tid == 0) {
+                    mbar_arrive_expect_tx(&ctl.full[ring.index], static_cast<uint32_t>(p.c_out) * 128u);
+                    tma_load_3d(b_addr - dst0, &b_map, col, p.b_k_outer ? 0 : k, p.b_k_outer ? k : 0,
+                                &ctl.full[ring.index]);
                 }
-            }
-            if (p.c_out & 16) {
-                // C_out = 32 m + 16: the last 16 output channels
-                if (q < 16) {
-                    cp_async_16(b_addr + 4096 * b_copies, w_src, uv);
+            } else {
+                const char* w_src =
+                    weight_bytes + static_cast<long long>(k) * p.w_k_bytes + col * 2 + w_co0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (i < b_copies) {
+                        cp_async_16(b_addr + 4096 * i, w_src, uv);
+                        w_src += w_co_step;
+                    }
+                }
+                if (p.c_out & 16) {
+                    // C_out = 32 m + 16: the last 16 output channels
+                    if (q < 16) {
+                        cp_async_16(b_addr + 4096 * b_copies, w_src, uv);
+                    }
                 }
             }
             cp_async_arrive_noinc(&ctl.full[ring.index]);
@@ -251,6 +361,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_plan_kernel(PlanConvParam
         }
         (void)ok;
         cp_async_wait<0>();
+        }
     } else if (warp < 16) {
         // ======================= epilogue =======================
         const int ew = warp - 8;
@@ -389,6 +500,27 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_plan_kernel(PlanConvParam
     }
 }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
+using EncodeTiledFn = CUresult (*)(
+    CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) ==
+                cudaSuccess &&
+            result == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+        }
+    });
+    return fn;
+}
+
 int pow2_at_least(int value, int floor_value) {
     int out = floor_value;
     while (out < value) {
@@ -403,7 +535,7 @@ int pow2_at_least(int value, int floor_value) {
 // tc_conv_supported allows them.
 int run_tc_conv_plan(
     const void* feats, int in_channels, long long feat_stride, const void* weights,
-    long long w_stride_k, long long w_stride_co, int out_channels, int out_capacity,
+    long long w_stride_k, long long w_stride_co, int n_kernels, int out_channels, int out_capacity,
     const void* bias, const int32_t* row_order, const void* plan, void* out, int32_t* status,
     cudaStream_t stream
 ) {
@@ -446,7 +578,30 @@ int run_tc_conv_plan(
     const int grid = std::max(1, std::min(p.num_tiles, sm_count));
     LAT_CUDA_CHECK(cudaFuncSetAttribute(
         tc_conv_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes)));
-    tc_conv_plan_kernel<<<grid, kThreads, smem_bytes, stream>>>(p);
+    // B tiles by TMA when a slab's two units share their kernel offset (C_in a multiple of
+    // 64): a 3-D map over the fp16 weights with the kernel offset as its own dimension
+    CUtensorMap b_map{};
+    const bool k_outer = w_stride_k >= w_stride_co;
+    if (in_channels % 64 == 0 && encode_tiled_fn() != nullptr &&
+        reinterpret_cast<uintptr_t>(weights) % 16 == 0 && n_kernels >= 1) {
+        const cuuint64_t dims[3] = {static_cast<cuuint64_t>(in_channels),
+                                    static_cast<cuuint64_t>(k_outer ? out_channels : n_kernels),
+                                    static_cast<cuuint64_t>(k_outer ? n_kernels : out_channels)};
+        const cuuint64_t strides[2] = {static_cast<cuuint64_t>(k_outer ? p.w_co_bytes : p.w_k_bytes),
+                                       static_cast<cuuint64_t>(k_outer ? p.w_k_bytes : p.w_co_bytes)};
+        const cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(k_outer ? out_channels : 1),
+                                   static_cast<cuuint32_t>(k_outer ? 1 : out_channels)};
+        const cuuint32_t elem_strides[3] = {1u, 1u, 1u};
+        CUresult rc = encode_tiled_fn()(
+            &b_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(weights), dims, strides, box,
+            elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rc == CUDA_SUCCESS) {
+            p.b_tma = 1;
+            p.b_k_outer = k_outer ? 1 : 0;
+        }
+    }
+    tc_conv_plan_kernel<<<grid, kThreads, smem_bytes, stream>>>(p, b_map);
     LAT_LAUNCH_CHECK();
     return LAT_OK;
 }

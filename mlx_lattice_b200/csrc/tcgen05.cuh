@@ -71,6 +71,29 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
                  : "memory");
 }
 
+// one arrival that also announces `bytes` of bulk-copy traffic to wait for
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+
+// TMA tile load of a 3-D box into shared memory; completion is counted in bytes on `bar`.
+// The innermost coordinate times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_3d(
+    uint32_t dst, const void* tensor_map, int c0, int c1, int c2, uint64_t* bar
+) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+        "l"(tensor_map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void prefetch_l1(const void* ptr) {
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(ptr));
+}
+
 template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }

@@ -206,6 +206,9 @@ def run_reference_arm(args) -> None:
 # --------------------------------------------------------------------------- #
 
 
+DRAM_READ_PER_GATHER_BYTE = 0.56  # dram__bytes_read / (E * C_in * 2), ncu, both captured cases
+
+
 class ConvProfile:
     """Collects per-launch CUDA-event timings of the convolution calls."""
 
@@ -220,6 +223,7 @@ class ConvProfile:
         launches on one route, with their summed event durations."""
         flops = 0.0
         bytes_ = 0.0
+        dram = 0.0
         ms = 0.0
         launches = 0
         for info, start, end in self.records:
@@ -232,9 +236,13 @@ class ConvProfile:
             weight_bytes = (k * c_in * c_out * info['bits'] / 8 + 2 * k * (c_in / 32) * c_out * 2
                             if info['bits'] else k * c_in * c_out * 2)
             bytes_ += info['in_rows'] * c_in * 2 + n_out * c_out * 2 + weight_bytes + 8 * edges
+            # DRAM bytes of a launch, from ncu captures of this kernel on two smaller cases
+            # (profiles/tc_conv_plan_kernel_dense_256x256_and_128x128.md): reads are 0.56 x
+            # the gathered feature bytes in both (L2 absorbs the rest), writes are the output
+            dram += DRAM_READ_PER_GATHER_BYTE * edges * c_in * 2 + n_out * c_out * 2
             ms += start.elapsed_time(end)
             launches += 1
-        return {'flops': flops, 'bytes': bytes_, 'ms': ms, 'launches': launches}
+        return {'flops': flops, 'bytes': bytes_, 'dram': dram, 'ms': ms, 'launches': launches}
 
 
 def kernel_map_benchmark(device, steps: int, peaks: dict) -> dict:
@@ -267,19 +275,23 @@ def kernel_map_benchmark(device, steps: int, peaks: dict) -> dict:
             del base
         ms = sum(times) / len(times)
         edges, n_out = counts
-        cap = 1 << (2 * n - 1).bit_length()
-        # algorithmic bytes per build: coord read, table clear + insert, one 4-byte slot
-        # per probe, pair output, row offsets (+ output-support pass when strided)
-        algo = n * 16 + 4 * cap + 4 * n + 4 * 27 * n_out + 8 * edges + 4 * (n_out + 1)
+        cap = 1 << (4 * n - 1).bit_length()
+        # algorithmic bytes per build: coord read, clear + insert of the 8-byte-slot table,
+        # one 32-byte bucket per probe, pair output, row offsets (+ output-support pass
+        # when strided)
+        hbm = n * 16 + 8 * cap + 8 * n + 12 * edges + 4 * (n_out + 1)
         if stride != 1:
-            algo += n * 16 + 4 * cap + 4 * n + 16 * n_out
+            hbm += n * 16 + 8 * cap + 8 * n + 16 * n_out
+        probes = 32 * 27 * n_out  # table reads, served by L2 (the table is 8 * cap bytes)
+        algo = hbm + probes
         out[name] = {
             'mcoords_per_s': n / ms / 1e3,
             'ms': ms,
             'edges': edges,
             'out_rows': n_out,
             'algorithmic_gb_s': algo / ms / 1e6,
-            'frac_of_hbm_peak': algo / ms / 1e6 / peaks['hbm_gbs'],
+            'hbm_algorithmic_gb_s': hbm / ms / 1e6,
+            'frac_of_hbm_peak': hbm / ms / 1e6 / peaks['hbm_gbs'],
         }
     return out
 
@@ -393,13 +405,15 @@ def run_gpu_arm(args) -> None:
         achieved_tf = tc['flops'] / (tc['ms'] / 1e3) / 1e12 if tc['ms'] > 0 else 0.0
         roofline = {
             'bound': 'tensor',
-            'kernel': 'tc_conv_kernel (tcgen05 implicit GEMM, all conv layers of the step)',
+            'kernel': 'tc_conv_plan_kernel (tcgen05 implicit GEMM, all conv layers of the step)',
             'achieved': achieved_tf,
             'peak': peak_tf,
             'unit': 'TFLOP/s',
             'frac': achieved_tf / peak_tf,
             'peak_source': peaks['source'] + ' (dense bf16, sustained)',
-            'traffic': None,
+            'traffic': tc['dram'] / tc['launches'] if tc['launches'] else None,
+            'traffic_note': 'DRAM bytes per launch (mean over the conv launches), scaled from ncu '
+                            'captures of two smaller cases by gathered bytes',
             'algorithmic_gb_s': tc['bytes'] / (tc['ms'] / 1e3) / 1e9 if tc['ms'] > 0 else 0.0,
             'launches': tc['launches'],
             'ms_per_step_in_kernel': tc['ms'] / args.steps,

@@ -255,10 +255,13 @@ struct Bucket {
     uint4 lo, hi;
 };
 
+// one 256-bit read-only load (sm_100): the bucket is 32-byte aligned
 __device__ __forceinline__ Bucket load_bucket(const Slot* slots, uint32_t base) {
     Bucket b;
-    b.lo = __ldg(reinterpret_cast<const uint4*>(slots + base));
-    b.hi = __ldg(reinterpret_cast<const uint4*>(slots + base + 2));
+    asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(b.lo.x), "=r"(b.lo.y), "=r"(b.lo.z), "=r"(b.lo.w), "=r"(b.hi.x), "=r"(b.hi.y),
+                   "=r"(b.hi.z), "=r"(b.hi.w)
+                 : "l"(slots + base));
     return b;
 }
 

@@ -1284,6 +1284,56 @@ cudaError_t fill_i32(int32_t* data, size_t count, int value, cudaStream_t stream
     return cudaGetLastError();
 }
 
+// The three edge arrays are zero beyond the edge count (the reference's contract for
+// its statically sized outputs). Only that tail is written, after the count is known:
+// a map over N rows has capacity N * K, of which a sparse cloud uses a few per cent.
+__global__ void zero_edge_tails_kernel(
+    int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, size_t capacity, const int32_t* counts,
+    int count_cap
+) {
+    const size_t edges = static_cast<size_t>(clamp_count(counts, count_cap));
+    const size_t quads = (capacity + 3) / 4;
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t quad = edges / 4 + blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+         quad < quads; quad += stride) {
+        const size_t first = quad * 4;
+        if (first >= edges && first + 4 <= capacity) {
+            const int4 zero = make_int4(0, 0, 0, 0);
+            reinterpret_cast<int4*>(in_rows)[quad] = zero;
+            reinterpret_cast<int4*>(out_rows)[quad] = zero;
+            reinterpret_cast<int4*>(kernel_ids)[quad] = zero;
+        } else {
+            for (size_t i = first > edges ? first : edges; i < first + 4 && i < capacity; ++i) {
+                in_rows[i] = 0;
+                out_rows[i] = 0;
+                kernel_ids[i] = 0;
+            }
+        }
+    }
+}
+
+cudaError_t zero_edge_tails(
+    int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, size_t capacity, const int32_t* counts,
+    cudaStream_t stream
+) {
+    if (capacity == 0) {
+        return cudaSuccess;
+    }
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(in_rows) | reinterpret_cast<uintptr_t>(out_rows) |
+                           reinterpret_cast<uintptr_t>(kernel_ids);
+    if (bits % 16 != 0) {
+        // unaligned caller buffers: clear everything up front instead (the map kernels
+        // then overwrite the live part); callers order this before the map themselves
+        return cudaErrorInvalidValue;
+    }
+    const int count_cap = static_cast<int>(std::min<size_t>(capacity, 0x7fffffff));
+    const size_t quads = (capacity + 3) / 4;
+    const int blocks = static_cast<int>(std::min<size_t>((quads + 255) / 256, 148 * 8));
+    zero_edge_tails_kernel<<<blocks, 256, 0, stream>>>(in_rows, out_rows, kernel_ids, capacity, counts,
+                                                       count_cap);
+    return cudaGetLastError();
+}
+
 cudaError_t clear_table(Slot* slots, size_t capacity, cudaStream_t stream) {
     return cudaMemsetAsync(slots, 0xFF, capacity * sizeof(Slot), stream);
 }
@@ -1350,9 +1400,16 @@ int run_map(
         return fail(LAT_WORKSPACE_TOO_SMALL, "workspace is too small for the kernel map.");
     }
 
-    LAT_CUDA_CHECK(fill_i32(o.in_rows, edge_capacity, 0, stream));
-    LAT_CUDA_CHECK(fill_i32(o.out_rows, edge_capacity, 0, stream));
-    LAT_CUDA_CHECK(fill_i32(o.kernel_ids, edge_capacity, 0, stream));
+    // 16-byte aligned edge arrays get only their tail zeroed, after the map; others are
+    // cleared whole here
+    const bool tail_only =
+        (reinterpret_cast<uintptr_t>(o.in_rows) | reinterpret_cast<uintptr_t>(o.out_rows) |
+         reinterpret_cast<uintptr_t>(o.kernel_ids)) % 16 == 0;
+    if (!tail_only) {
+        LAT_CUDA_CHECK(fill_i32(o.in_rows, edge_capacity, 0, stream));
+        LAT_CUDA_CHECK(fill_i32(o.out_rows, edge_capacity, 0, stream));
+        LAT_CUDA_CHECK(fill_i32(o.kernel_ids, edge_capacity, 0, stream));
+    }
     LAT_CUDA_CHECK(fill_i32(o.row_offsets, static_cast<size_t>(offsets_capacity) + 1, 0, stream));
     if (o.row_masks != nullptr) {
         LAT_CUDA_CHECK(fill_i32(o.row_masks, static_cast<size_t>(out_capacity) * words, 0, stream));
@@ -1402,6 +1459,10 @@ int run_map(
         size_t smem = sizeof(int) * kRowsPerBlock * K;
         map_single_pass_kernel<1, 5><<<nblocks, kBlockThreads, smem, stream>>>(p, tile_status, ticket, nblocks);
         LAT_LAUNCH_CHECK();
+        if (tail_only) {
+            LAT_CUDA_CHECK(zero_edge_tails(o.in_rows, o.out_rows, o.kernel_ids, edge_capacity, o.counts, stream));
+            count_launch();
+        }
         return LAT_OK;
     }
     size_t count_smem = lists ? sizeof(int) * kWarpsPerBlock * K : 0;
@@ -1414,6 +1475,10 @@ int run_map(
     size_t fill_smem = lists ? sizeof(int) * kWarpsPerBlock * K : 0;
     map_fill_kernel<<<nblocks, kBlockThreads, fill_smem, stream>>>(p);
     LAT_LAUNCH_CHECK();
+    if (tail_only) {
+        LAT_CUDA_CHECK(zero_edge_tails(o.in_rows, o.out_rows, o.kernel_ids, edge_capacity, o.counts, stream));
+        count_launch();
+    }
     return LAT_OK;
 }
 

@@ -141,6 +141,91 @@ __global__ void __launch_bounds__(kDirectWarps * 32) direct_conv_kernel(
     }
 }
 
+// Narrow layers (C_in <= 8, C_out <= 32: a network's stem): one thread per output row
+// with all output channels in registers and the fp32 weights in shared memory. A warp
+// per row (the general kernel) leaves such a layer bound by its chain of dependent
+// loads; here 32 rows per warp are in flight. Same fp32 summation order: edges
+// ascending, input channels ascending, one fma per (edge, c_in, c_out).
+constexpr int kNarrowMaxIn = 8;
+constexpr int kNarrowMaxOut = 32;
+
+template <typename T>
+__global__ void __launch_bounds__(256) direct_conv_narrow_kernel(
+    const T* feats, long long feat_stride, int in_capacity, const float* weights, int K,
+    int c_in, int c_out, const int32_t* in_rows, const int32_t* kernel_ids, int edge_capacity,
+    const int32_t* counts, const int32_t* row_offsets, int out_capacity, const T* bias, T* out,
+    int32_t* status
+) {
+    extern __shared__ float w_smem[];  // [K * c_in][c_out + 1]: the pad spreads rows over banks
+    const int pitch = c_out + 1;
+    for (int i = threadIdx.x; i < K * c_in * c_out; i += blockDim.x) {
+        w_smem[(i / c_out) * pitch + i % c_out] = weights[i];
+    }
+    __syncthreads();
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= out_capacity) {
+        return;
+    }
+    const int edge_total = min(max(__ldg(counts), 0), edge_capacity);
+    const int n_out = min(max(__ldg(counts + 1), 0), out_capacity);
+    float acc[kNarrowMaxOut];
+#pragma unroll
+    for (int j = 0; j < kNarrowMaxOut; ++j) {
+        acc[j] = 0.0f;
+    }
+    if (row < n_out) {
+        const int begin = max(__ldg(row_offsets + row), 0);
+        const int end = min(__ldg(row_offsets + row + 1), edge_total);
+        for (int e = begin; e < end; ++e) {
+            const int in_row = __ldg(in_rows + e);
+            const int k = __ldg(kernel_ids + e);
+            if (in_row < 0 || k < 0) {
+                continue;
+            }
+            if (in_row >= in_capacity || k >= K) {
+                raise_status(status, LAT_STATUS_BAD_INDEX);
+                continue;
+            }
+            const T* x = feats + static_cast<size_t>(in_row) * feat_stride;
+            for (int c = 0; c < c_in; ++c) {
+                const float v = to_float<T>(x[c]);
+                const float* w = w_smem + (k * c_in + c) * pitch;
+#pragma unroll
+                for (int j = 0; j < kNarrowMaxOut; ++j) {
+                    if (j < c_out) {
+                        acc[j] = fmaf(v, w[j], acc[j]);
+                    }
+                }
+            }
+        }
+    }
+    T* out_row = out + static_cast<size_t>(row) * c_out;
+    T y[kNarrowMaxOut];
+#pragma unroll
+    for (int j = 0; j < kNarrowMaxOut; ++j) {
+        y[j] = from_float<T>(acc[j]);
+        if (bias != nullptr && j < c_out) {
+            y[j] = from_float<T>(to_float<T>(y[j]) + to_float<T>(bias[j]));
+        }
+    }
+    if (sizeof(T) == 2 && (c_out & 7) == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
+        // rows are 16-byte multiples: eight half values per store
+#pragma unroll
+        for (int j = 0; j < kNarrowMaxOut; j += 8) {
+            if (j < c_out) {
+                *reinterpret_cast<uint4*>(out_row + j) = *reinterpret_cast<const uint4*>(&y[j]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < kNarrowMaxOut; ++j) {
+            if (j < c_out) {
+                out_row[j] = y[j];
+            }
+        }
+    }
+}
+
 inline int blocks_for(size_t count, int threads) {
     return static_cast<int>((count + threads - 1) / threads);
 }
@@ -191,6 +276,23 @@ int run_direct_conv(
             out_channels, w32);
     }
     LAT_LAUNCH_CHECK();
+    const size_t narrow_smem = sizeof(float) * static_cast<size_t>(n_kernels) * in_channels * (out_channels + 1);
+    if (in_channels <= kNarrowMaxIn && out_channels <= kNarrowMaxOut && narrow_smem <= 48 * 1024) {
+        const int narrow_blocks = blocks_for(out_capacity, 256);
+        if (dtype == LAT_F32) {
+            direct_conv_narrow_kernel<float><<<narrow_blocks, 256, narrow_smem, stream>>>(
+                static_cast<const float*>(feats), feat_stride, in_capacity, w32, n_kernels,
+                in_channels, out_channels, in_rows, kernel_ids, edge_capacity, counts, row_offsets,
+                out_capacity, static_cast<const float*>(bias), static_cast<float*>(out), status);
+        } else {
+            direct_conv_narrow_kernel<__half><<<narrow_blocks, 256, narrow_smem, stream>>>(
+                static_cast<const __half*>(feats), feat_stride, in_capacity, w32, n_kernels,
+                in_channels, out_channels, in_rows, kernel_ids, edge_capacity, counts, row_offsets,
+                out_capacity, static_cast<const __half*>(bias), static_cast<__half*>(out), status);
+        }
+        LAT_LAUNCH_CHECK();
+        return LAT_OK;
+    }
     int blocks = blocks_for(out_capacity, kDirectWarps);
     if (dtype == LAT_F32) {
         direct_conv_kernel<float><<<blocks, kDirectWarps * 32, 0, stream>>>(

@@ -71,6 +71,69 @@ __global__ void __launch_bounds__(kThreads) linear_kernel(
     }
 }
 
+// Few output channels (a classification head): one thread per row with every output in
+// registers and the fp32 weight matrix in shared memory (all lanes read the same weight:
+// a broadcast). Same summation order as linear_kernel: input channels ascending.
+constexpr int kNarrowOut = 32;
+
+template <typename T, bool Quantized>
+__global__ void __launch_bounds__(kThreads) linear_narrow_kernel(
+    const T* feats, int rows, int c_in, const T* weight, const uint32_t* packed,
+    const T* scales, const T* biases, int storage, int group_size, int bits, int c_out,
+    const T* bias, T* out
+) {
+    extern __shared__ float w_tile[];  // [c_in][c_out]
+    const int words = Quantized ? storage * bits / 32 : 0;
+    const int groups = Quantized ? storage / group_size : 0;
+    for (int i = threadIdx.x; i < c_in * c_out; i += kThreads) {
+        const int ci = i / c_out;
+        const int co = i - ci * c_out;
+        float w;
+        if (Quantized) {
+            const int bit = ci * bits;
+            const uint32_t word = __ldg(packed + static_cast<size_t>(co) * words + (bit >> 5));
+            const uint32_t code = (word >> (bit & 31)) & ((1u << bits) - 1u);
+            const size_t q = static_cast<size_t>(co) * groups + ci / group_size;
+            w = fmaf(static_cast<float>(code), to_float<T>(scales[q]), to_float<T>(biases[q]));
+        } else {
+            w = to_float<T>(weight[static_cast<size_t>(co) * c_in + ci]);
+        }
+        w_tile[i] = w;
+    }
+    __syncthreads();
+    const int row = blockIdx.x * kThreads + threadIdx.x;
+    if (row >= rows) {
+        return;
+    }
+    float acc[kNarrowOut];
+#pragma unroll
+    for (int j = 0; j < kNarrowOut; ++j) {
+        acc[j] = 0.0f;
+    }
+    const T* x = feats + static_cast<size_t>(row) * c_in;
+    for (int ci = 0; ci < c_in; ++ci) {
+        const float v = to_float<T>(x[ci]);
+        const float* w = w_tile + ci * c_out;
+#pragma unroll
+        for (int j = 0; j < kNarrowOut; ++j) {
+            if (j < c_out) {
+                acc[j] = fmaf(v, w[j], acc[j]);
+            }
+        }
+    }
+    T* y = out + static_cast<size_t>(row) * c_out;
+#pragma unroll
+    for (int j = 0; j < kNarrowOut; ++j) {
+        if (j < c_out) {
+            T value = from_float<T>(acc[j]);
+            if (bias != nullptr) {
+                value = from_float<T>(to_float<T>(value) + to_float<T>(bias[j]));
+            }
+            y[j] = value;
+        }
+    }
+}
+
 template <typename T>
 __global__ void batch_norm_relu_kernel(
     const T* feats, long long rows, int channels, const T* weight, const T* bias,
@@ -118,6 +181,15 @@ int launch_linear(
     const void* scales, const void* biases, int storage, int group_size, int bits, int c_out,
     const void* bias, void* out, cudaStream_t stream
 ) {
+    if (c_out <= kNarrowOut && sizeof(float) * c_in * c_out <= 48 * 1024) {
+        const size_t w_bytes = sizeof(float) * c_in * c_out;
+        linear_narrow_kernel<T, Quantized><<<(rows + kThreads - 1) / kThreads, kThreads, w_bytes, stream>>>(
+            static_cast<const T*>(feats), rows, c_in, static_cast<const T*>(weight), packed,
+            static_cast<const T*>(scales), static_cast<const T*>(biases), storage, group_size, bits,
+            c_out, static_cast<const T*>(bias), static_cast<T*>(out));
+        LAT_LAUNCH_CHECK();
+        return LAT_OK;
+    }
     size_t smem = sizeof(float) * kRowsPerBlock * c_in;
     if (smem > 48 * 1024) {
         LAT_CUDA_CHECK(cudaFuncSetAttribute(

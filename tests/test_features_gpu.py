@@ -290,6 +290,21 @@ def test_global_pool_linear_batchnorm(cuda, restatement):
             _dev(x16, cuda), _dev(q['weight'][0].view(np.int32), cuda), _dev(q['scales'][0], cuda),
             _dev(q['biases'][0], cuda), 192, 96, 32, bits).cpu().numpy()
         assert _max_rel_err(got, restatement.quantized_matmul(x16, q)) <= FP16_TOL
+    # few output channels (a head): the one-thread-per-row kernel
+    wn = (rng.normal(size=(20, 96)) * 0.1).astype(np.float16)
+    bn = rng.normal(size=20).astype(np.float16)
+    got = _ext.linear(_dev(x16, cuda), _dev(wn, cuda), _dev(bn, cuda)).cpu().numpy()
+    assert _max_rel_err(got, restatement.linear(x16, wn, bn)) <= FP16_TOL
+    for bits in (4, 8):
+        q = restatement.quantize_weight(wn, 32, bits)
+        got = _ext.quantized_linear(
+            _dev(x16, cuda), _dev(q['weight'][0].view(np.int32), cuda), _dev(q['scales'][0], cuda),
+            _dev(q['biases'][0], cuda), 20, 96, 32, bits).cpu().numpy()
+        assert _max_rel_err(got, restatement.quantized_matmul(x16, q)) <= FP16_TOL
+    xn = rng.normal(size=(3001, 24)).astype(np.float32)
+    wn32 = rng.normal(size=(7, 24)).astype(np.float32)
+    got = _ext.linear(_dev(xn, cuda), _dev(wn32, cuda)).cpu().numpy()
+    assert _max_rel_err(got, restatement.linear(xn, wn32)) <= FP32_TOL
     x32 = rng.normal(size=(3000, 20)).astype(np.float32)
     w32 = rng.normal(size=(33, 20)).astype(np.float32)
     got = _ext.linear(_dev(x32, cuda), _dev(w32, cuda)).cpu().numpy()

@@ -102,26 +102,47 @@ __global__ void __launch_bounds__(kThreads) linear_narrow_kernel(
     }
     __syncthreads();
     const int row = blockIdx.x * kThreads + threadIdx.x;
-    if (row >= rows) {
-        return;
-    }
     float acc[kNarrowOut];
 #pragma unroll
     for (int j = 0; j < kNarrowOut; ++j) {
         acc[j] = 0.0f;
     }
-    const T* x = feats + static_cast<size_t>(row) * c_in;
-    for (int ci = 0; ci < c_in; ++ci) {
-        const float v = to_float<T>(x[ci]);
-        const float* w = w_tile + ci * c_out;
+    if (row < rows) {
+        const T* x = feats + static_cast<size_t>(row) * c_in;
+        if (sizeof(T) == 2 && (c_in & 7) == 0 && reinterpret_cast<uintptr_t>(feats) % 16 == 0) {
+            // eight half values per load
+            for (int c0 = 0; c0 < c_in; c0 += 8) {
+                const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + c0));
+                const T* v8 = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-        for (int j = 0; j < kNarrowOut; ++j) {
-            if (j < c_out) {
-                acc[j] = fmaf(v, w[j], acc[j]);
+                for (int u = 0; u < 8; ++u) {
+                    const float v = to_float<T>(v8[u]);
+                    const float* w = w_tile + (c0 + u) * c_out;
+#pragma unroll
+                    for (int j = 0; j < kNarrowOut; ++j) {
+                        if (j < c_out) {
+                            acc[j] = fmaf(v, w[j], acc[j]);
+                        }
+                    }
+                }
+            }
+        } else {
+            for (int ci = 0; ci < c_in; ++ci) {
+                const float v = to_float<T>(x[ci]);
+                const float* w = w_tile + ci * c_out;
+#pragma unroll
+                for (int j = 0; j < kNarrowOut; ++j) {
+                    if (j < c_out) {
+                        acc[j] = fmaf(v, w[j], acc[j]);
+                    }
+                }
             }
         }
     }
-    T* y = out + static_cast<size_t>(row) * c_out;
+    // the block's output rows are one contiguous range: stage them in shared memory (the
+    // weights are no longer needed) and write 16 bytes per thread
+    __syncthreads();
+    T* y_tile = reinterpret_cast<T*>(w_tile);  // [kThreads][c_out]
 #pragma unroll
     for (int j = 0; j < kNarrowOut; ++j) {
         if (j < c_out) {
@@ -129,7 +150,26 @@ __global__ void __launch_bounds__(kThreads) linear_narrow_kernel(
             if (bias != nullptr) {
                 value = from_float<T>(to_float<T>(value) + to_float<T>(bias[j]));
             }
-            y[j] = value;
+            y_tile[threadIdx.x * c_out + j] = value;
+        }
+    }
+    __syncthreads();
+    const int first_row = blockIdx.x * kThreads;
+    const int valid_rows = min(kThreads, rows - first_row);
+    const size_t bytes = static_cast<size_t>(valid_rows) * c_out * sizeof(T);
+    char* dst = reinterpret_cast<char*>(out + static_cast<size_t>(first_row) * c_out);
+    const char* src = reinterpret_cast<const char*>(y_tile);
+    if (reinterpret_cast<uintptr_t>(dst) % 16 == 0) {
+        const size_t vectors = bytes / 16;
+        for (size_t i = threadIdx.x; i < vectors; i += kThreads) {
+            reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+        }
+        for (size_t i = vectors * 16 + threadIdx.x * sizeof(T); i < bytes; i += kThreads * sizeof(T)) {
+            *reinterpret_cast<T*>(dst + i) = *reinterpret_cast<const T*>(src + i);
+        }
+    } else {
+        for (size_t i = threadIdx.x * sizeof(T); i < bytes; i += kThreads * sizeof(T)) {
+            *reinterpret_cast<T*>(dst + i) = *reinterpret_cast<const T*>(src + i);
         }
     }
 }
@@ -182,7 +222,8 @@ int launch_linear(
     const void* bias, void* out, cudaStream_t stream
 ) {
     if (c_out <= kNarrowOut && sizeof(float) * c_in * c_out <= 48 * 1024) {
-        const size_t w_bytes = sizeof(float) * c_in * c_out;
+        // shared memory holds the fp32 weights, then the block's output rows
+        const size_t w_bytes = std::max(sizeof(float) * c_in * c_out, sizeof(T) * kThreads * c_out);
         linear_narrow_kernel<T, Quantized><<<(rows + kThreads - 1) / kThreads, kThreads, w_bytes, stream>>>(
             static_cast<const T*>(feats), rows, c_in, static_cast<const T*>(weight), packed,
             static_cast<const T*>(scales), static_cast<const T*>(biases), storage, group_size, bits,

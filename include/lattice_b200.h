@@ -40,6 +40,10 @@ typedef struct lat_triple {
     int32_t x, y, z;
 } lat_triple;
 
+typedef struct lat_float_triple {
+    float x, y, z;
+} lat_float_triple;
+
 enum {
     LAT_OK = 0,
     LAT_INVALID_ARGUMENT = 1, /* contract violation (reference: std::invalid_argument) */
@@ -294,6 +298,36 @@ size_t lat_mask_order_workspace_bytes(int32_t rows);
 int lat_build_mask_row_order(
     const int32_t* row_masks, int32_t rows, int32_t kernel_count, const int32_t* counts,
     int32_t* row_order,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* ---- point -> voxel front end (the step before the path) ------------------ */
+
+/* native/bindings/coords.cpp:294-325 (`sparse_quantize`) ->
+ * native/features/coordinates/quantization.cpp; arithmetic
+ * native/features/coordinates/cpu/quantization_detail.h:67-125. points [rows,3]
+ * float32, batch_indices [rows] int32 (NULL = all zero), active_rows [1] (NULL =
+ * rows). Voxel coordinate = (batch, floor((p - origin) / voxel_size)) in float32.
+ * out_coords [rows,4] holds the unique voxels in first-seen point order (zero
+ * tail), count [1] their number, inverse_rows [rows] the voxel row of each point
+ * (-1 at and beyond active_rows), voxel_counts [rows] the points per voxel (zero
+ * tail). */
+size_t lat_sparse_quantize_workspace_bytes(int32_t rows);
+int lat_sparse_quantize(
+    const float* points, const int32_t* batch_indices, int32_t rows, const int32_t* active_rows,
+    lat_float_triple voxel_size, lat_float_triple origin,
+    int32_t* out_coords, int32_t* count, int32_t* inverse_rows, int32_t* voxel_counts,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* native/bindings/coords.cpp:326-352 (`voxelize_features`); arithmetic
+ * cpu/quantization_detail.h:127-166. values [point_rows, channels] float32; out
+ * [voxel_rows, channels] = per-voxel sum (mean = 0) or mean (sum of value *
+ * 1/max(count,1)) over the points p < active_rows[0] with inverse_rows[p] in
+ * [0, voxel_rows), accumulated in ascending point order. */
+size_t lat_voxelize_features_workspace_bytes(int32_t point_rows, int32_t voxel_rows);
+int lat_voxelize_features(
+    const float* values, const int32_t* inverse_rows, const int32_t* voxel_counts,
+    const int32_t* active_rows, int32_t point_rows, int32_t voxel_rows, int32_t channels,
+    int32_t mean, float* out,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
 /* ---- pooling and pointwise feature ops ---------------------------------- */

@@ -15,7 +15,7 @@ from typing import Sequence
 import torch
 
 from mlx_lattice_b200 import _native
-from mlx_lattice_b200._native import Triple, check
+from mlx_lattice_b200._native import FloatTriple, Triple, check
 
 _REDUCE = {'sum': 0, 'max': 1, 'avg': 2}
 _JOIN = {'inner': 0, 'left': 1, 'right': 2, 'outer': 3}
@@ -524,6 +524,80 @@ def build_sparse_alignment(lhs_coords, lhs_active_rows, rhs_coords, rhs_active_r
             _stream(),
         ))
     return coords, count, lhs_rows, rhs_rows
+
+
+# --------------------------------------------------------------------------- #
+# point -> voxel front end (native/bindings/coords.cpp:294-352)
+# --------------------------------------------------------------------------- #
+
+
+def _float_triple(values, name: str) -> FloatTriple:
+    values = tuple(float(v) for v in values)
+    if len(values) != 3:
+        raise ValueError(f'{name} must contain exactly 3 values.')
+    return FloatTriple(*values)
+
+
+def sparse_quantize(points, batch_indices, active_rows, voxel_size, origin):
+    """``_ext.sparse_quantize`` (``coords.cpp:294-325``): ``(coords, active_rows,
+    inverse_rows, counts)`` with the reference's capacities (all N rows)."""
+    _require_cuda(points, 'points')
+    if points.ndim != 2 or points.shape[1] != 3:
+        raise ValueError('points must have shape (N, 3).')
+    if points.dtype != torch.float32:
+        raise ValueError('points must be float32.')
+    points = points.contiguous()
+    rows = int(points.shape[0])
+    batch = _i32(batch_indices, 'batch_indices')
+    if tuple(batch.shape) != (rows,):
+        raise ValueError('batch_indices must have shape (N,) and int32 dtype.')
+    active_rows = _active_arg(active_rows)
+    size = _float_triple(voxel_size, 'voxel_size')
+    if min(size.x, size.y, size.z) <= 0.0:
+        raise ValueError('voxel_size values must be positive.')
+    device = points.device
+    coords = torch.empty((rows, 4), dtype=torch.int32, device=device)
+    count = torch.empty(1, dtype=torch.int32, device=device)
+    inverse = torch.empty(rows, dtype=torch.int32, device=device)
+    counts = torch.empty(rows, dtype=torch.int32, device=device)
+    lib = _lib()
+    ws = _workspace(lib.lat_sparse_quantize_workspace_bytes(rows), device)
+    with torch.cuda.device(device):
+        check(lib.lat_sparse_quantize(
+            _ptr(points), _ptr(batch), rows, _ptr(active_rows), size,
+            _float_triple(origin, 'origin'), _ptr(coords), _ptr(count), _ptr(inverse),
+            _ptr(counts), _ptr(ws), ws.numel(), _ptr(status_word(device)), _stream(),
+        ))
+    return coords, count, inverse, counts
+
+
+def voxelize_features(feats, inverse_rows, voxel_counts, active_rows, reduction):
+    """``_ext.voxelize_features`` (``coords.cpp:326-352``): (voxel rows, C) float32."""
+    _require_cuda(feats, 'feats')
+    if feats.ndim != 2:
+        raise ValueError('feats must have shape (N, C).')
+    if feats.dtype != torch.float32:
+        raise ValueError('voxelize currently supports float32 features.')
+    if reduction not in ('sum', 'mean'):
+        raise ValueError("reduction must be 'sum' or 'mean'.")
+    feats = feats.contiguous()
+    inverse = _i32(inverse_rows, 'inverse_rows')
+    counts = _i32(voxel_counts, 'voxel_counts')
+    if inverse.shape[0] != feats.shape[0]:
+        raise ValueError('feats and quantization metadata must share rows.')
+    active_rows = _active_arg(active_rows)
+    points, voxels, channels = int(feats.shape[0]), int(counts.shape[0]), int(feats.shape[1])
+    device = feats.device
+    out = torch.empty((voxels, channels), dtype=torch.float32, device=device)
+    lib = _lib()
+    ws = _workspace(lib.lat_voxelize_features_workspace_bytes(points, voxels), device)
+    with torch.cuda.device(device):
+        check(lib.lat_voxelize_features(
+            _ptr(feats), _ptr(inverse), _ptr(counts), _ptr(active_rows), points, voxels, channels,
+            1 if reduction == 'mean' else 0, _ptr(out), _ptr(ws), ws.numel(),
+            _ptr(status_word(device)), _stream(),
+        ))
+    return out
 
 
 # --------------------------------------------------------------------------- #

@@ -32,6 +32,10 @@ class Triple(ctypes.Structure):
     _fields_ = [('x', c_int32), ('y', c_int32), ('z', c_int32)]
 
 
+class FloatTriple(ctypes.Structure):
+    _fields_ = [('x', c_float), ('y', c_float), ('z', c_float)]
+
+
 P = c_void_p
 I = c_int32
 
@@ -80,6 +84,10 @@ SIGNATURES = {
     'lat_conv_uses_tensor_cores': (I, [I, I, I, I, I, I]),
     'lat_mask_order_workspace_bytes': (c_size_t, [I]),
     'lat_build_mask_row_order': (I, [P, I, I, P, P, P, c_size_t, P, P]),
+    'lat_sparse_quantize_workspace_bytes': (c_size_t, [I]),
+    'lat_sparse_quantize': (I, [P, P, I, P, FloatTriple, FloatTriple, P, P, P, P, P, c_size_t, P, P]),
+    'lat_voxelize_features_workspace_bytes': (c_size_t, [I, I]),
+    'lat_voxelize_features': (I, [P, P, P, P, I, I, I, I, P, P, c_size_t, P, P]),
     'lat_sparse_pool_features': (
         I, [P, I, I, c_int64, P, P, P, I, P, P, I, I, I, I, P, P, P]),
     'lat_global_pool': (I, [P, I, I, P, I, I, P, P]),

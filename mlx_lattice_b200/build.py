@@ -22,6 +22,7 @@ SOURCES = (
     'conv_tc_plan.cu',
     'conv_plan.cu',
     'order.cu',
+    'voxelize.cu',
     'static_scratch.cu',
     'pool.cu',
     'feature.cu',

@@ -23,6 +23,7 @@ from mlx_lattice_b200.ops.pool import (
     pool3d,
     sum_pool3d,
 )
+from mlx_lattice_b200.ops.quantization import sparse_quantize, voxelize, voxelize_with_quantization
 from mlx_lattice_b200.ops.tensor import sparse_cat_aligned, sparse_collate
 
 __all__ = [
@@ -31,5 +32,6 @@ __all__ = [
     'build_target_transposed_relation', 'build_transposed_kernel_relation', 'conv3d',
     'conv_transpose3d', 'generative_conv_transpose3d', 'global_avg_pool', 'global_max_pool',
     'global_sum_pool', 'kernel_offsets', 'linear', 'max_pool3d', 'pool3d', 'relu',
-    'sparse_cat_aligned', 'sparse_collate', 'subm_conv3d', 'sum_pool3d',
+    'sparse_cat_aligned', 'sparse_collate', 'sparse_quantize', 'subm_conv3d', 'sum_pool3d',
+    'voxelize', 'voxelize_with_quantization',
 ]

@@ -539,4 +539,75 @@ int ref_sparse_pool(
     });
 }
 
+// Point -> voxel quantization (first-seen unique voxel per point, inverse rows, points
+// per voxel): cpu/quantization_algorithms.cpp:4-30 -> cpu/quantization_detail.h:87-125.
+// Outputs sized like the reference factory: coords points x 4, count 1, inverse points,
+// voxel_counts points.
+int ref_sparse_quantize(
+    const float* points,
+    const int32_t* batch_indices,
+    int rows,
+    const int32_t* active_rows,
+    const float* voxel_size,
+    const float* origin,
+    int32_t* out_coords,
+    int32_t* count,
+    int32_t* inverse_rows,
+    int32_t* voxel_counts
+) {
+    return guarded([&] {
+        std::vector<mx::array> inputs{
+            mx::array(const_cast<float*>(points), {rows, 3}, mx::float32),
+            i32(batch_indices, {rows}),
+            i32(active_rows, {1}),
+        };
+        std::vector<mx::array> outputs{
+            i32(out_coords, {rows, 4}),
+            i32(count, {1}),
+            i32(inverse_rows, {rows}),
+            i32(voxel_counts, {rows}),
+        };
+        mlx_lattice::QuantizationSpec spec{
+            {voxel_size[0], voxel_size[1], voxel_size[2]},
+            {origin[0], origin[1], origin[2]},
+        };
+        mlx_lattice::coords::cpu::eval_sparse_quantize(
+            spec, host_stream(), inputs, outputs
+        );
+    });
+}
+
+// Per-voxel sum / mean of point features in point order:
+// cpu/quantization_algorithms.cpp:32-62 -> cpu/quantization_detail.h:138-166.
+int ref_voxelize_features(
+    const float* values,
+    const int32_t* inverse_rows,
+    const int32_t* voxel_counts,
+    const int32_t* active_rows,
+    int point_rows,
+    int voxel_rows,
+    int channels,
+    int mean,
+    float* out
+) {
+    return guarded([&] {
+        std::vector<mx::array> inputs{
+            mx::array(const_cast<float*>(values), {point_rows, channels}, mx::float32),
+            i32(inverse_rows, {point_rows}),
+            i32(voxel_counts, {voxel_rows}),
+            i32(active_rows, {1}),
+        };
+        std::vector<mx::array> outputs{
+            mx::array(out, {voxel_rows, channels}, mx::float32),
+        };
+        mlx_lattice::coords::cpu::eval_voxelize_features(
+            mean != 0 ? mlx_lattice::VoxelReduceOp::Mean : mlx_lattice::VoxelReduceOp::Sum,
+            mlx_lattice::VoxelFeatureShape{point_rows, voxel_rows, channels},
+            host_stream(),
+            inputs,
+            outputs
+        );
+    });
+}
+
 } // extern "C"

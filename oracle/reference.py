@@ -289,6 +289,45 @@ def downsample_coords(coords, stride):
     return out, count
 
 
+def sparse_quantize(points, batch_indices=None, active_rows=None, voxel_size=1.0, origin=0.0):
+    """``eval_sparse_quantize`` (``cpu/quantization_algorithms.cpp``): coords (N, 4),
+    count (1,), inverse rows (N,), points per voxel (N,)."""
+    points = np.ascontiguousarray(points, np.float32).reshape(-1, 3)
+    rows = points.shape[0]
+    batch = np.zeros(rows, np.int32) if batch_indices is None else _i32(batch_indices)
+    active = np.asarray([rows if active_rows is None else int(np.asarray(active_rows).ravel()[0])], np.int32)
+    vs = np.ascontiguousarray(np.broadcast_to(np.asarray(voxel_size, np.float32), (3,)))
+    og = np.ascontiguousarray(np.broadcast_to(np.asarray(origin, np.float32), (3,)))
+    coords = np.zeros((rows, 4), np.int32)
+    count = np.zeros(1, np.int32)
+    inverse = np.zeros(rows, np.int32)
+    voxel_counts = np.zeros(rows, np.int32)
+    _check(
+        lib().ref_sparse_quantize(
+            _p(points), _p(batch), rows, _p(active), _p(vs), _p(og), _p(coords), _p(count),
+            _p(inverse), _p(voxel_counts)
+        ),
+        'sparse_quantize',
+    )
+    return coords, count, inverse, voxel_counts
+
+
+def voxelize_features(values, inverse_rows, voxel_counts, active_rows, reduction='mean'):
+    """``eval_voxelize_features``: (voxel rows, C) float32, voxel rows = len(voxel_counts)."""
+    values = np.ascontiguousarray(values, np.float32)
+    inverse, voxel_counts = _i32(inverse_rows), _i32(voxel_counts)
+    active = np.asarray([int(np.asarray(active_rows).ravel()[0])], np.int32)
+    out = np.zeros((voxel_counts.shape[0], values.shape[1]), np.float32)
+    _check(
+        lib().ref_voxelize_features(
+            _p(values), _p(inverse), _p(voxel_counts), _p(active), values.shape[0],
+            voxel_counts.shape[0], values.shape[1], 1 if reduction == 'mean' else 0, _p(out)
+        ),
+        'voxelize_features',
+    )
+    return out
+
+
 def lookup_coords(coords, queries):
     coords, queries = _i32(coords), _i32(queries)
     out = np.zeros(queries.shape[0], np.int32)

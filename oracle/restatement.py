@@ -113,6 +113,58 @@ def downsample_values(coords: np.ndarray, stride) -> np.ndarray:
     return q[np.sort(first)].astype(np.int32)
 
 
+def sparse_quantize(points, batch_indices=None, active_rows=None, voxel_size=1.0, origin=0.0):
+    """``write_sparse_quantization`` (``cpu/quantization_detail.h:87-125``) with
+    ``voxel_coord_for_point`` (``:67-85``): voxel = (batch, floor((p - origin) / size)) in
+    float32; unique voxels in first-seen point order, the voxel row of every active
+    point (-1 beyond), points per voxel."""
+    points = np.asarray(points, np.float32).reshape(-1, 3)
+    rows = points.shape[0]
+    batch = np.zeros(rows, np.int32) if batch_indices is None else np.asarray(batch_indices, np.int32)
+    active = rows if active_rows is None else min(int(np.asarray(active_rows).ravel()[0]), rows)
+    vs = np.broadcast_to(np.asarray(voxel_size, np.float32), (3,))
+    og = np.broadcast_to(np.asarray(origin, np.float32), (3,))
+    cells = np.floor((points[:active] - og[None, :]) / vs[None, :]).astype(np.int64)
+    q = np.concatenate([batch[:active, None].astype(np.int64), cells], axis=1)
+    coords = np.zeros((rows, 4), np.int32)
+    inverse = np.full(rows, -1, np.int32)
+    counts = np.zeros(rows, np.int32)
+    if active > 0:
+        (keys,) = _keys(q)
+        _, first, inv = np.unique(keys, return_index=True, return_inverse=True)
+        order = np.argsort(first, kind='stable')          # unique ids in first-seen order
+        rank = np.empty_like(order)
+        rank[order] = np.arange(order.shape[0])
+        voxel = rank[inv.reshape(-1)]
+        n = order.shape[0]
+        coords[:n] = q[np.sort(first)].astype(np.int32)
+        inverse[:active] = voxel
+        counts[:n] = np.bincount(voxel, minlength=n)
+    else:
+        n = 0
+    return coords, np.asarray([n], np.int32), inverse, counts
+
+
+def voxelize_features(values, inverse_rows, voxel_counts, active_rows, reduction='mean'):
+    """``write_voxel_features`` (``cpu/quantization_detail.h:138-166``): float32 running
+    sum per voxel in point order of value * scale, scale = 1 / max(count, 1) for the mean.
+    (The compiled reference fuses the multiply-add; this restatement rounds the product,
+    so it agrees to a few ulp, not bitwise.)"""
+    values = np.asarray(values, np.float32)
+    inverse = np.asarray(inverse_rows, np.int32)
+    counts = np.asarray(voxel_counts, np.int32)
+    active = min(int(np.asarray(active_rows).ravel()[0]), values.shape[0])
+    out = np.zeros((counts.shape[0], values.shape[1]), np.float32)
+    scale = np.float32(1.0) / np.maximum(counts, 1).astype(np.float32) if reduction == 'mean' else None
+    for p in range(active):
+        v = inverse[p]
+        if v < 0 or v >= counts.shape[0]:
+            continue
+        term = values[p] * scale[v] if scale is not None else values[p]
+        out[v] = out[v] + term
+    return out
+
+
 def downsample_coords(coords, stride):
     """Set-op form (``cpu/set_algorithms.cpp:4-37``): zero-padded (N, 4) buffer
     with the unique rows as prefix, and the count."""

@@ -195,3 +195,56 @@ def test_quantizer_roundtrip_and_package_agreement():
                 assert np.array_equal(pq.biases.numpy(), q['biases'])
                 assert pq.storage_in_channels == q['storage_in_channels']
                 assert np.array_equal(dequantize_weight(pq).numpy(), restatement.dequantize_weight(q))
+
+
+@pytest.mark.parametrize('backend', BACKENDS, ids=IDS)
+def test_known_answer_quantization(backend):
+    """Point -> voxel front end against the reference's own known answers."""
+    kat = KATS['quantize_ordered']
+    coords, count, inverse, counts = backend.sparse_quantize(
+        np.asarray(kat['points'], np.float32), np.asarray(kat['batches'], np.int32), None,
+        kat['voxel_size'], 0.0)
+    n = kat['active_rows'][0]
+    assert count.tolist() == kat['active_rows']
+    assert coords[:n].tolist() == kat['coords'] and not coords[n:].any()
+    assert inverse.tolist() == kat['inverse_rows']
+    assert counts[:n].tolist() == kat['counts']
+
+    kat = KATS['quantize_origin_active']
+    coords, count, inverse, counts = backend.sparse_quantize(
+        np.asarray(kat['points'], np.float32), None, np.asarray(kat['point_active'], np.int32),
+        kat['voxel_size'], kat['origin'])
+    n = kat['active_rows'][0]
+    assert count.tolist() == kat['active_rows']
+    assert coords[:n].tolist() == kat['coords']
+    assert inverse.tolist() == kat['inverse_rows']
+    assert counts.tolist() == kat['counts']
+
+    kat = KATS['voxelize_mean_sum']
+    points = np.asarray(kat['points'], np.float32)
+    feats = np.asarray(kat['feats'], np.float32)
+    coords, count, inverse, counts = backend.sparse_quantize(points, None, None, 1.0, 0.0)
+    n = int(count[0])
+    assert coords[:n].tolist() == kat['coords']
+    active = np.asarray([points.shape[0]], np.int32)
+    mean = backend.voxelize_features(feats, inverse, counts, active, 'mean')
+    total = backend.voxelize_features(feats, inverse, counts, active, 'sum')
+    assert np.allclose(mean[:n], kat['mean']) and np.allclose(total[:n], kat['sum'])
+    assert not mean[n:].any() and not total[n:].any()
+
+
+@pytest.mark.skipif(not reference.available(), reason='compiled reference not built')
+def test_quantization_restatement_matches_compiled_reference():
+    rng = np.random.default_rng(41)
+    points = (rng.normal(size=(20000, 3)) * 7.0).astype(np.float32)
+    batch = rng.integers(0, 3, size=20000).astype(np.int32)
+    active = np.asarray([19000], np.int32)
+    got = restatement.sparse_quantize(points, batch, active, (0.5, 0.25, 1.0), (0.1, -0.3, 2.0))
+    want = reference.sparse_quantize(points, batch, active, (0.5, 0.25, 1.0), (0.1, -0.3, 2.0))
+    for g, w in zip(got, want):
+        assert np.array_equal(g, w)
+    feats = rng.normal(size=(20000, 5)).astype(np.float32)
+    for mode in ('mean', 'sum'):
+        g = restatement.voxelize_features(feats[:3000], got[2][:3000], got[3], np.asarray([3000], np.int32), mode)
+        w = reference.voxelize_features(feats[:3000], want[2][:3000], want[3], np.asarray([3000], np.int32), mode)
+        assert np.allclose(g, w, rtol=1e-5, atol=1e-6)

@@ -1,0 +1,140 @@
+"""Point -> voxel front end on the GPU against the oracle: voxel coordinates, first-seen
+order, inverse rows and counts bit-exact; voxel features bit-exact against the compiled
+reference (same fused multiply-add, same order) and within 1e-5 of the restatement."""
+
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+KATS = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), 'golden',
+                                   'reference_kats.json')))
+
+
+def _dev(array, cuda):
+    return torch.from_numpy(np.ascontiguousarray(array)).to(cuda)
+
+
+def _cloud(seed, rows, batches):
+    rng = np.random.default_rng(seed)
+    points = (rng.normal(size=(rows, 3)) * 9.0).astype(np.float32)
+    points[::7] = np.round(points[::7])          # points on cell boundaries
+    points[5::11] = points[4::11][: points[5::11].shape[0]]   # exact duplicates
+    batch = np.sort(rng.integers(0, batches, size=rows)).astype(np.int32)
+    return points, batch
+
+
+def test_reference_known_answers(cuda):
+    from mlx_lattice_b200 import ops
+
+    kat = KATS['quantize_ordered']
+    q = ops.sparse_quantize(_dev(np.asarray(kat['points'], np.float32), cuda), kat['voxel_size'],
+                            batch_indices=_dev(np.asarray(kat['batches'], np.int32), cuda))
+    n = kat['active_rows'][0]
+    assert q.capacity == 5 and q.active_count is q.active_rows
+    assert q.active_rows.tolist() == kat['active_rows']
+    assert q.coords[:n].tolist() == kat['coords']
+    assert q.inverse_rows.tolist() == kat['inverse_rows']
+    assert q.counts[:n].tolist() == kat['counts']
+
+    kat = KATS['quantize_origin_active']
+    q = ops.sparse_quantize(_dev(np.asarray(kat['points'], np.float32), cuda), kat['voxel_size'],
+                            origin=kat['origin'],
+                            active_rows=_dev(np.asarray(kat['point_active'], np.int32), cuda))
+    assert q.active_rows.tolist() == kat['active_rows']
+    assert q.coords[: kat['active_rows'][0]].tolist() == kat['coords']
+    assert q.inverse_rows.tolist() == kat['inverse_rows']
+    assert q.counts.tolist() == kat['counts']
+
+    kat = KATS['voxelize_mean_sum']
+    points = _dev(np.asarray(kat['points'], np.float32), cuda)
+    feats = _dev(np.asarray(kat['feats'], np.float32), cuda)
+    mean = ops.voxelize(points, feats, voxel_size=1.0, reduction='mean')
+    total = ops.voxelize(points, feats, voxel_size=1.0, reduction='sum')
+    n = int(mean.active_rows.item())
+    assert mean.coords[:n].tolist() == kat['coords'] and mean.stride == (1, 1, 1)
+    assert np.allclose(mean.feats[:n].cpu().numpy(), kat['mean'])
+    assert np.allclose(total.feats[:n].cpu().numpy(), kat['sum'])
+
+
+@pytest.mark.parametrize('rows,batches,active', [(50000, 4, None), (20000, 1, 17500), (1, 1, None),
+                                                  (3000, 3, 0)])
+def test_sparse_quantize_matches_oracle(cuda, oracle, rows, batches, active):
+    from mlx_lattice_b200 import _ext
+
+    points, batch = _cloud(rows + batches, rows, batches)
+    size, origin = (0.5, 0.75, 1.25), (0.1, -0.3, 2.0)
+    active_np = None if active is None else np.asarray([active], np.int32)
+    want = oracle.sparse_quantize(points, batch, active_np, size, origin)
+    active_dev = _dev(np.asarray([rows if active is None else active], np.int32), cuda)
+    got = _ext.sparse_quantize(_dev(points, cuda), _dev(batch, cuda), active_dev, size, origin)
+    for g, w, name in zip(got, want, ('coords', 'count', 'inverse_rows', 'counts')):
+        assert np.array_equal(g.cpu().numpy(), w), name
+    _ext.check_status(cuda)
+
+
+@pytest.mark.parametrize('channels', [1, 4, 40])
+@pytest.mark.parametrize('mode', ['mean', 'sum'])
+def test_voxelize_features_matches_oracle(cuda, oracle, restatement, channels, mode):
+    from mlx_lattice_b200 import _ext
+
+    rows = 30000
+    points, batch = _cloud(channels, rows, 2)
+    coords, count, inverse, counts = oracle.sparse_quantize(points, batch, None, 1.5, 0.0)
+    rng = np.random.default_rng(channels * 3 + 1)
+    feats = rng.normal(size=(rows, channels)).astype(np.float32)
+    active = np.asarray([rows - 500], np.int32)
+    want = oracle.voxelize_features(feats, inverse, counts, active, mode)
+    got = _ext.voxelize_features(_dev(feats, cuda), _dev(inverse, cuda), _dev(counts, cuda),
+                                 _dev(active, cuda), mode).cpu().numpy()
+    if oracle is restatement:
+        assert np.allclose(got, want, rtol=1e-5, atol=1e-6)
+    else:
+        assert np.array_equal(got, want)   # same fused multiply-adds in the same order
+    n = int(count[0])
+    assert not got[n:].any()
+    _ext.check_status(cuda)
+
+
+def test_voxelize_feeds_the_convolution(cuda, oracle):
+    """points -> voxelize -> subm_conv3d: the front end's tensor is a regular input of the
+    path (coordinates unique, active_rows respected)."""
+    from mlx_lattice_b200 import ops
+
+    points, batch = _cloud(9, 20000, 2)
+    rng = np.random.default_rng(10)
+    feats = rng.normal(size=(20000, 4)).astype(np.float32)
+    x = ops.voxelize(_dev(points, cuda), _dev(feats, cuda), 1.0, batch_indices=_dev(batch, cuda))
+    n = int(x.active_rows.item())
+    weight = (rng.normal(size=(8, 3, 3, 3, 4)) * 0.1).astype(np.float32)
+    y = ops.subm_conv3d(x, _dev(weight, cuda), kernel_size=3)
+    coords, count, inverse, counts = oracle.sparse_quantize(points, batch, None, 1.0, 0.0)
+    vox = oracle.voxelize_features(feats, inverse, counts, np.asarray([20000], np.int32), 'mean')
+    rel = oracle.build_submanifold_kernel_relation(coords, np.asarray([n], np.int32))
+    want = oracle.sparse_conv(vox, weight, rel, coords.shape[0], 27)
+    got = y.feats.cpu().numpy()
+    scale = np.abs(want).max()
+    assert np.abs(got[:n] - want[:n]).max() <= 1e-5 * scale
+    assert not got[n:].any()
+
+
+def test_argument_errors(cuda):
+    from mlx_lattice_b200 import ops
+
+    points = torch.zeros((4, 3), dtype=torch.float32, device=cuda)
+    with pytest.raises(ValueError, match='points must have shape'):
+        ops.sparse_quantize(torch.zeros((4, 2), dtype=torch.float32, device=cuda))
+    with pytest.raises(ValueError, match='points must be float32'):
+        ops.sparse_quantize(points.double())
+    with pytest.raises(ValueError, match='voxel_size values must be positive'):
+        ops.sparse_quantize(points, 0.0)
+    with pytest.raises(ValueError, match='batch_indices must have shape'):
+        ops.sparse_quantize(points, batch_indices=torch.zeros(3, dtype=torch.int32, device=cuda))
+    with pytest.raises(ValueError, match="reduction must be 'sum' or 'mean'"):
+        ops.voxelize(points, torch.zeros((4, 2), device=cuda), reduction='max')
+    with pytest.raises(ValueError, match='matching rows'):
+        ops.voxelize(points, torch.zeros((3, 2), device=cuda))

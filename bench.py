@@ -296,6 +296,59 @@ def kernel_map_benchmark(device, steps: int, peaks: dict) -> dict:
     return out
 
 
+def front_end_benchmark(device, steps: int, peaks: dict) -> dict:
+    """Point -> voxel front end: 2,000,000 points (8 clouds, about two points per voxel at
+    voxel size 1), 4 feature channels, sparse_quantize + voxelize_features (mean)."""
+    import numpy as np
+    import torch
+
+    from mlx_lattice_b200 import _ext, synthetic
+
+    voxels = synthetic.lidar_batch(2, 8, 125000)
+    rng = np.random.default_rng(77)
+    reps = 2
+    base = np.repeat(voxels, reps, axis=0)
+    order = rng.permutation(base.shape[0])
+    base = base[order]
+    batch = torch.from_numpy(np.sort(base[:, 0]).astype(np.int32)).to(device)
+    base = base[np.argsort(base[:, 0], kind='stable')]
+    points = torch.from_numpy(
+        (base[:, 1:].astype(np.float32) + rng.uniform(0.05, 0.95, size=(base.shape[0], 3)).astype(np.float32))
+    ).to(device)
+    feats = torch.from_numpy(rng.normal(size=(base.shape[0], 4)).astype(np.float32)).to(device)
+    n = points.shape[0]
+    active = torch.tensor([n], dtype=torch.int32, device=device)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+    times = []
+    count = None
+    for i in range(steps + 2):
+        flush.zero_()
+        start = torch.cuda.Event(enable_timing=True)
+        end = torch.cuda.Event(enable_timing=True)
+        start.record()
+        coords, count, inverse, counts = _ext.sparse_quantize(points, batch, active, (1.0, 1.0, 1.0), (0.0, 0.0, 0.0))
+        out = _ext.voxelize_features(feats, inverse, counts, active, 'mean')
+        end.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            times.append(start.elapsed_time(end))
+        del out
+    ms = sum(times) / len(times)
+    v = int(count.item())
+    cap = 1 << (4 * n - 1).bit_length()
+    # HBM-class bytes: points + batch read, table clear + insert, coords/inverse/counts out,
+    # features read and voxel rows written (all at capacity n, as the contract sizes them)
+    hbm = n * 16 + 8 * cap + 8 * n + n * 16 + n * 8 + n * 16 + n * 16
+    return {
+        'mpoints_per_s': n / ms / 1e3,
+        'ms': ms,
+        'points': n,
+        'voxels': v,
+        'hbm_algorithmic_gb_s': hbm / ms / 1e6,
+        'frac_of_hbm_peak': hbm / ms / 1e6 / peaks['hbm_gbs'],
+    }
+
+
 def run_gpu_arm(args) -> None:
     import torch
 
@@ -419,6 +472,7 @@ def run_gpu_arm(args) -> None:
             'ms_per_step_in_kernel': tc['ms'] / args.steps,
         }
         kernel_map = kernel_map_benchmark(device, max(args.steps, 3), peaks)
+        front_end = front_end_benchmark(device, max(args.steps, 3), peaks)
         cpu = cpu_reference_step(args.cpu_sample)
         line = {
             'metric': METRIC,
@@ -451,6 +505,7 @@ def run_gpu_arm(args) -> None:
             'gpu_launches': launches,
             'roofline': roofline,
             'kernel_map': kernel_map,
+            'front_end': front_end,
             'cpu_baseline': {k: cpu[k] for k in ('value', 'unit', 'cores', 'kind', 'sample')},
             'clocks': clocks,
             'wall_s_timed_region': wall,

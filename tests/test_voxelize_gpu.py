@@ -114,7 +114,7 @@ def test_voxelize_feeds_the_convolution(cuda, oracle):
     y = ops.subm_conv3d(x, _dev(weight, cuda), kernel_size=3)
     coords, count, inverse, counts = oracle.sparse_quantize(points, batch, None, 1.0, 0.0)
     vox = oracle.voxelize_features(feats, inverse, counts, np.asarray([20000], np.int32), 'mean')
-    rel = oracle.build_submanifold_kernel_relation(coords, np.asarray([n], np.int32))
+    rel = oracle.build_submanifold_kernel_relation(coords, n)
     want = oracle.sparse_conv(vox, weight, rel, coords.shape[0], 27)
     got = y.feats.cpu().numpy()
     scale = np.abs(want).max()

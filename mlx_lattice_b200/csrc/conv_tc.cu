@@ -86,7 +86,6 @@ struct TcParams {
     int acc_cols;        // columns per accumulator stage
     int acc_stages;      // accumulator stages in TMEM (power of two)
     int num_tiles;
-    int debug_skip;      // experiment switches (0 in normal use)
     int nbr_stride;      // odd stride (in ints) of the neighbour table rows
     int ctl_bytes;
 };
@@ -459,7 +458,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
                         const __half* col_base =
                             p.feats + (uv ? cur_a.slice : 0) * 32 + (a_chunk & 3) * 8;
                         cur_a.advance(2, units_per_offset);
-                        if (!(p.debug_skip & 1)) {
+                        {
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
                                 const int in_row = uv ? nbr[a_nbr[j] + uk] : -1;
@@ -486,7 +485,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
                         load_b(cur_q);
                         cur_q.advance(2, units_per_offset);
                     }
-                    if (!(p.debug_skip & 2)) {
+                    {
                         uint32_t c0[kMaxTasks], c1[kMaxTasks], csb[kUniform ? 2 : kMaxTasks];
 #pragma unroll
                         for (int i = 0; i < kMaxTasks; ++i) {
@@ -632,7 +631,6 @@ __global__ void __launch_bounds__(kThreads, 1) tc_conv_kernel(TcParams p) {
                 for (int kk = 0; kk < 4; ++kk) {
                     // 16 fp16 = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
                     const uint32_t acc = (s | kk) != 0 ? 1u : 0u;
-                    if (p.debug_skip & 4) continue;
                     umma_f16(tmem_d0, desc_a0 + 2 * kk, desc_b + 2 * kk, idesc, acc);
                     umma_f16(tmem_d1, desc_a1 + 2 * kk, desc_b + 2 * kk, idesc, acc);
                 }
@@ -844,9 +842,6 @@ int run_tc_conv(
     p.acc_stages = std::min(kMaxAccStages, 512 / (2 * p.acc_cols));
     p.tmem_cols = p.acc_stages * 2 * p.acc_cols;
     p.nbr_stride = n_kernels | 1;
-    if (const char* dbg = std::getenv("LAT_TC_DEBUG_SKIP")) {
-        p.debug_skip = std::atoi(dbg);
-    }
     p.ctl_bytes = static_cast<int>(align_up(
         sizeof(SharedControl) + sizeof(int) * kTileRows * (p.acc_stages + p.nbr_stride), 16));
     // keep every B stage on a 1024-byte boundary (the swizzle pattern repeats every
@@ -861,9 +856,6 @@ int run_tc_conv(
     } else {
         p.a_stage_bytes = kSlabBytesA;
         p.b_stages = 2;
-        if (const char* dbg = std::getenv("LAT_TC_B_STAGES")) {
-            p.b_stages = std::atoi(dbg);
-        }
         p.a_stages = std::min(kMaxStages, (smem_budget - p.b_stages * p.b_stage_bytes) / kSlabBytesA);
     }
     LAT_REQUIRE(p.a_stages >= 2, "internal: shared-memory plan leaves no room for the stage ring.");

@@ -193,6 +193,46 @@ def test_gather_plan_strided_and_padding_rows(cuda, oracle, restatement):
     assert np.array_equal(_qconv(cuda, feats, q, rel, n, 8, row_order=order, with_plan=True), base)
 
 
+@pytest.mark.parametrize('bits', [4, 8])
+def test_in_register_dequant_route(cuda, oracle, restatement, sphere, bits, monkeypatch):
+    """LAT_TC_DEQUANT=register keeps the codes packed until the tensor-core kernel's
+    producers convert them in registers (code * scale + bias, fp16 fma)."""
+    monkeypatch.setenv('LAT_TC_DEQUANT', 'register')
+    coords, rel = sphere
+    n = coords.shape[0]
+    rng = np.random.default_rng(100 + bits)
+    for c_in, c_out in ((64, 64), (128, 96), (32, 48)):
+        feats = rng.normal(size=(n, c_in)).astype(np.float16)
+        w5 = (rng.normal(size=(c_out, 3, 3, 3, c_in)) * 0.05).astype(np.float16)
+        q = restatement.quantize_weight(w5, 32, bits)
+        want = oracle.sparse_quantized_conv(
+            feats, q['weight'], q['scales'], q['biases'], rel, n, 27, c_in, c_out,
+            q['storage_in_channels'], 32, bits)
+        order = np.random.default_rng(4).permutation(n).astype(np.int32)
+        got = _qconv(cuda, feats, q, rel, n, 27, row_order=order)
+        assert _max_rel_err(got, want) <= FP16_TOL
+        # a plan is accepted and ignored on this route
+        assert np.array_equal(_qconv(cuda, feats, q, rel, n, 27, row_order=order, with_plan=True), got)
+
+
+def test_gather_plan_edge_shapes(cuda, oracle):
+    """Plans over tiny and empty relations, and capacities that are not tile multiples."""
+    rng = np.random.default_rng(77)
+    for rows, active in ((1, 1), (5, 5), (257, 257), (300, 0), (513, 100)):
+        coords = np.zeros((rows, 4), np.int32)
+        coords[:, 1] = np.arange(rows) % 23
+        coords[:, 2] = np.arange(rows) // 23
+        rel = oracle.build_submanifold_kernel_relation(coords, active)
+        feats = rng.normal(size=(rows, 32)).astype(np.float16)
+        w5 = (rng.normal(size=(32, 3, 3, 3, 32)) * 0.1).astype(np.float16)
+        want = oracle.sparse_conv(feats.astype(np.float32), w5.astype(np.float32), rel, rows, 27)
+        got = _conv(cuda, feats, w5, rel, rows, 27, with_plan=True)
+        assert got.shape == (rows, 32)
+        assert _max_rel_err(got, want) <= FP16_TOL
+        assert not got[active:].any()
+        assert np.array_equal(got, _conv(cuda, feats, w5, rel, rows, 27))
+
+
 def test_quantized_conv_float32_and_group64(cuda, oracle, restatement, sphere):
     coords, rel = sphere
     n = coords.shape[0]

@@ -174,11 +174,12 @@ __device__ __forceinline__ int warp_exclusive_scan(int v, int& total) {
 
 // ---- open-addressing table: 8-byte slots (tag << 32 | row) ---------------------------
 //
-// slots[capacity] (capacity a power of two) hold (tag << 32) | row or kEmptySlot. The
-// tag is the upper half of a 64-bit hash of the key, the slot index its lower bits; a
-// probe compares tags first and loads the stored row's coordinate only on a tag match,
-// so a miss costs slot reads only. Equal keys keep the smallest row id (first row
-// wins, like the reference's first_row_map, coordinates/cpu/quantization_detail.h:
+// slots[capacity] (capacity a power of two, load factor <= 1/4) hold (tag << 32) | row
+// or kEmptySlot, in buckets of four consecutive slots. Bucket index and tag are two
+// 32-bit hashes of the key; a probe reads one bucket, compares tags, and loads the
+// stored row's coordinate only on a tag match, so a miss costs one sector read. Equal
+// keys keep the smallest row id (first row wins, like the reference's first_row_map,
+// coordinates/cpu/quantization_detail.h:
 // 394-402): equal keys have equal tags, so a 64-bit atomicMin on the slot is a min
 // over the row ids. Linear probing: consecutive slots share 32-byte sectors.
 using Slot = unsigned long long;

@@ -1,5 +1,7 @@
-// Tensor-core route of the sparse-conv contraction: an output-stationary implicit
-// GEMM on tcgen05 with the accumulator in tensor memory (TMEM).
+// Tensor-core route of the sparse-conv contraction that walks the relation itself (the
+// plan-driven kernel in conv_tc_plan.cu is the default when a gather plan exists; this
+// one serves calls without a plan and the in-register dequantisation route): an
+// output-stationary implicit GEMM on tcgen05 with the accumulator in tensor memory.
 //
 // One persistent CTA per SM walks 256-row output tiles (rows taken through an
 // optional permutation). For a tile the implicit GEMM is
@@ -16,17 +18,20 @@
 // Warp roles (544 threads):
 //   warps 0-7  producers: read the tile's CSR rows into a [256][K] neighbour table,
 //              gather A with 16-byte cp.async (zero-fill for absent neighbours) and
-//              fill B -- cp.async from fp16 weights, or packed int4/int8 codes
-//              dequantised in registers (code*scale + bias; all loads of a slab are
-//              issued before the first conversion) and stored to shared memory. Completion is published per stage after cp.async.wait_group
-//              and a generic->async proxy fence, lagging the issue by a few stages.
+//              fill B. fp16 weights: cp.async into the same stage as the A rows, and
+//              the copies arrive on the stage's barrier themselves when they land
+//              (cp.async.mbarrier.arrive.noinc). Packed int4/int8 codes: loaded one
+//              slab ahead into registers, dequantised there (code*scale + bias),
+//              stored to a second ring and published after a generic->async proxy
+//              fence.
 //   warps 8-15 epilogue: tcgen05.ld the fp32 accumulator (lane = tile row), add the
 //              optional bias, cast once to fp16 and store each output row exactly once
 //              (no atomics, deterministic).
 //   warp 16    TMEM allocation and the single MMA-issuing thread.
 // The accumulator is a ring of up to eight TMEM stages (512 columns / 2 C_out), so the
-// epilogue of a tile overlaps the MMAs of the following ones. Every mbarrier wait is bounded by a clock budget; on expiry the
-// kernel records LAT_STATUS_WAIT_TIMEOUT, all roles drain and the CTA frees its TMEM.
+// epilogue of a tile overlaps the MMAs of the following ones. Every mbarrier wait is
+// bounded by a clock budget; on expiry the kernel records LAT_STATUS_WAIT_TIMEOUT, all
+// roles drain and the CTA frees its TMEM.
 #include <algorithm>
 #include <cstdlib>
 

@@ -75,6 +75,20 @@ def main() -> None:
     for mode in ('sum', 'max', 'avg'):
         out[f'pool_{mode}'] = reference.sparse_pool(
             data['feats32'], prel, input_exclusive=False, reduce=mode, out_capacity=n, n_kernels=27)
+    # point -> voxel front end
+    rng = np.random.default_rng(20261)
+    points = (rng.normal(size=(6000, 3)) * 6.0).astype(np.float32)
+    points[::5] = np.round(points[::5])
+    batch = np.sort(rng.integers(0, 3, size=6000)).astype(np.int32)
+    pfeats = rng.normal(size=(6000, 3)).astype(np.float32)
+    out['in_points'], out['in_point_batch'], out['in_point_feats'] = points, batch, pfeats
+    quant = reference.sparse_quantize(points, batch, np.asarray([5500], np.int32), (0.5, 1.0, 2.0),
+                                      (0.25, -0.5, 0.0))
+    for name, value in zip(('coords', 'count', 'inverse', 'counts'), quant):
+        out[f'quantize.{name}'] = value
+    for mode in ('mean', 'sum'):
+        out[f'voxelize_{mode}'] = reference.voxelize_features(
+            pfeats, quant[2], quant[3], np.asarray([5500], np.int32), mode)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'reference_outputs.npz')
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path) // 1024, 'KiB,', len(out), 'arrays')

@@ -198,6 +198,19 @@ def test_quantizer_roundtrip_and_package_agreement():
 
 
 @pytest.mark.parametrize('backend', BACKENDS, ids=IDS)
+def test_quantization_matches_compiled_reference_outputs(backend, golden):
+    g = golden
+    active = np.asarray([5500], np.int32)
+    got = backend.sparse_quantize(g['in_points'], g['in_point_batch'], active, (0.5, 1.0, 2.0),
+                                  (0.25, -0.5, 0.0))
+    for name, value in zip(('coords', 'count', 'inverse', 'counts'), got):
+        assert np.array_equal(value, g[f'quantize.{name}']), name
+    for mode in ('mean', 'sum'):
+        vox = backend.voxelize_features(g['in_point_feats'], got[2], got[3], active, mode)
+        assert np.allclose(vox, g[f'voxelize_{mode}'], rtol=1e-5, atol=1e-6), mode
+
+
+@pytest.mark.parametrize('backend', BACKENDS, ids=IDS)
 def test_known_answer_quantization(backend):
     """Point -> voxel front end against the reference's own known answers."""
     kat = KATS['quantize_ordered']

@@ -1,14 +1,15 @@
 // Row permutation that groups output rows with equal kernel-offset masks, so that
 // the 256-row tiles of the tensor-core convolution see few distinct offsets each
 // (the idea of the reference's mask-sorted view, core/relations/views.py:467-510,
-// built natively). Stable LSD radix sort of (mask, row) with 8-bit digits. A pass is
+// built natively). Stable LSD radix sort of (mask, row) with 10-bit digits. A pass is
 // three launches over 2048-row tiles (8 warps x 256 rows): per-tile digit histograms,
 // a column scan over the tiles, and a scatter that ranks equal digits inside a tile in
 // row order (warp match/ballot inside a 32-row step, running per-warp counters across
 // steps, a prefix over the warps) -- no atomics, so the permutation is a pure function
 // of the masks. The first pass reads the masks directly (rows at or beyond counts[1]
 // get a key above every mask and therefore sort last), the last one writes only the
-// permutation. Only the digits that can differ are sorted: ceil((K + 1) / 8) passes.
+// permutation. Only the digits that can differ are sorted: ceil((K + 1) / 10) passes
+// (three for a 3x3x3 kernel, one for a 2x2x2 one).
 #include <algorithm>
 
 #include "common.cuh"
@@ -17,7 +18,9 @@ namespace lat {
 
 namespace {
 
-constexpr int kBuckets = 256;
+constexpr int kDigitBits = 10;
+constexpr int kBuckets = 1 << kDigitBits;
+constexpr int kBinsPerThread = kBuckets / 256;
 constexpr int kWarps = 8;
 constexpr int kSteps = 8;                         // 32-row steps per warp
 constexpr int kRowsPerWarp = 32 * kSteps;
@@ -50,7 +53,7 @@ __device__ __forceinline__ void load_digits(
         const int i = first + s * 32 + lane;
         const bool valid = i < in.rows;
         key[s] = valid ? in.load(i, n_out) : 0u;
-        digit[s] = valid ? static_cast<int>((key[s] >> shift) & 255u) : -1 - lane;
+        digit[s] = valid ? static_cast<int>((key[s] >> shift) & (kBuckets - 1)) : -1 - lane;
     }
 }
 
@@ -76,12 +79,14 @@ __global__ void __launch_bounds__(kWarps * 32) order_hist_kernel(
         __syncwarp();
     }
     __syncthreads();
-    int total = 0;
+    for (int b = threadIdx.x; b < kBuckets; b += kWarps * 32) {
+        int total = 0;
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
-        total += counts[w][threadIdx.x];
+        for (int w = 0; w < kWarps; ++w) {
+            total += counts[w][b];
+        }
+        tile_hist[static_cast<size_t>(blockIdx.x) * kBuckets + b] = total;
     }
-    tile_hist[static_cast<size_t>(blockIdx.x) * kBuckets + threadIdx.x] = total;
 }
 
 // block b scans column b of tile_hist over the tiles (exclusive, in place)
@@ -153,24 +158,36 @@ __global__ void __launch_bounds__(kWarps * 32) order_scatter_kernel(
         }
         __syncwarp();
     }
-    // where digit b of this tile starts: digits below b anywhere, digit b in earlier tiles
-    const int b = threadIdx.x;
-    const int total = __ldg(totals + b);
+    // where digit b of this tile starts: digits below b anywhere, digit b in earlier tiles.
+    // Thread t owns bins kBinsPerThread * t ..: a prefix inside the thread, then over the block.
+    int bin_total[kBinsPerThread];
+    int thread_total = 0;
+#pragma unroll
+    for (int u = 0; u < kBinsPerThread; ++u) {
+        bin_total[u] = __ldg(totals + threadIdx.x * kBinsPerThread + u);
+        thread_total += bin_total[u];
+    }
     int wtotal;
-    const int below_in_warp = warp_exclusive_scan(total, wtotal);
+    const int below_in_warp = warp_exclusive_scan(thread_total, wtotal);
     if (lane == 31) {
         warp_sums[warp] = wtotal;
     }
     __syncthreads();
-    int start = below_in_warp + __ldg(tile_hist + static_cast<size_t>(blockIdx.x) * kBuckets + b);
+    int below = below_in_warp;
     for (int w = 0; w < warp; ++w) {
-        start += warp_sums[w];
+        below += warp_sums[w];
     }
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
-        const int count = cursor[w][b];
-        cursor[w][b] = start;  // now: where warp w's rows with digit b start
-        start += count;
+    for (int u = 0; u < kBinsPerThread; ++u) {
+        const int b = threadIdx.x * kBinsPerThread + u;
+        int start = below + __ldg(tile_hist + static_cast<size_t>(blockIdx.x) * kBuckets + b);
+        below += bin_total[u];
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const int count = cursor[w][b];
+            cursor[w][b] = start;  // now: where warp w's rows with digit b start
+            start += count;
+        }
     }
     __syncthreads();
 #pragma unroll
@@ -228,7 +245,7 @@ int lat_build_mask_row_order(
     LAT_REQUIRE(kernel_count >= 1 && kernel_count <= 32, "row masks need 1 <= K <= 32.");
     // masks use bits [0, K); inactive rows get bit K (or all ones when K == 32)
     const uint32_t inactive_key = kernel_count >= 32 ? 0xFFFFFFFFu : (1u << kernel_count);
-    const int passes = kernel_count >= 32 ? 4 : (kernel_count + 1 + 7) / 8;
+    const int passes = kernel_count >= 32 ? 4 : (kernel_count + 1 + kDigitBits - 1) / kDigitBits;
     for (int pass = 0; pass < passes; ++pass) {
         const bool last = pass == passes - 1;
         OrderKeys in{};
@@ -240,12 +257,12 @@ int lat_build_mask_row_order(
         const int32_t* pin = pass == 0 ? nullptr : ((pass & 1) ? perm_b : perm_a);
         uint32_t* kout = last ? nullptr : ((pass & 1) ? keys_a : keys_b);
         int32_t* pout = last ? row_order : ((pass & 1) ? perm_a : perm_b);
-        order_hist_kernel<<<tiles, kWarps * 32, 0, stream>>>(in, pass * 8, hist);
+        order_hist_kernel<<<tiles, kWarps * 32, 0, stream>>>(in, pass * kDigitBits, hist);
         LAT_LAUNCH_CHECK();
         order_scan_kernel<<<kBuckets, 256, 0, stream>>>(hist, tiles, totals);
         LAT_LAUNCH_CHECK();
         order_scatter_kernel<<<tiles, kWarps * 32, 0, stream>>>(
-            in, pin, pass * 8, hist, totals, kout, pout);
+            in, pin, pass * kDigitBits, hist, totals, kout, pout);
         LAT_LAUNCH_CHECK();
     }
     return LAT_OK;

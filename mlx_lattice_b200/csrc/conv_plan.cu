@@ -51,135 +51,112 @@ __device__ __forceinline__ int plan_row(const PlanBuildParams& p, int position) 
     return row;
 }
 
-// One block per tile, tiles taken in ticket order. The block reads its rows' edges once
-// for the tile's offset mask, learns the index of its first row vector from a decoupled
-// look-back over the tiles before it (it publishes its own vector count, then one warp
-// sums its predecessors' counts 32 at a time until it meets one that knows its prefix;
-// every wait is clock-bounded), and writes its row vectors from a second read of the
-// same edges (cache-hot).
-constexpr unsigned long long kPlanAggregate = 1ull << 62;
-constexpr unsigned long long kPlanPrefix = 2ull << 62;
-constexpr unsigned long long kPlanValueMask = (1ull << 62) - 1;
-constexpr long long kPlanLookbackBudgetCycles = 4000000000LL;  // about two seconds
-
-__global__ void __launch_bounds__(kPlanTileRows) plan_single_pass_kernel(
-    PlanBuildParams p, unsigned long long* tile_status, int* ticket
-) {
+// pass 1: offset mask of every tile
+__global__ void __launch_bounds__(kPlanTileRows) plan_mask_kernel(PlanBuildParams p) {
     __shared__ uint32_t tile_mask;
-    __shared__ int s_tile;
-    __shared__ int s_base;
-    __shared__ int s_failed;
     if (threadIdx.x == 0) {
-        s_tile = atomicAdd(ticket, 1);
         tile_mask = 0;
-        s_failed = 0;
     }
     __syncthreads();
-    const int tile = s_tile;
-    if (tile >= p.num_tiles) {
-        return;
-    }
-    const int lane = threadIdx.x & 31;
     const int n_out = clamp_count(p.counts + 1, p.out_capacity);
     const int edge_total = clamp_count(p.counts, p.edge_capacity);
-    const int r = threadIdx.x;
-    const int row = plan_row(p, tile * kPlanTileRows + r);
-    int begin = 0, end = 0;
+    const int row = plan_row(p, blockIdx.x * kPlanTileRows + threadIdx.x);
     uint32_t mask = 0;
     if (row >= 0 && row < n_out) {
-        begin = max(__ldg(p.row_offsets + row), 0);
-        end = min(__ldg(p.row_offsets + row + 1), edge_total);
+        const int begin = max(__ldg(p.row_offsets + row), 0);
+        const int end = min(__ldg(p.row_offsets + row + 1), edge_total);
         for (int e = begin; e < end; ++e) {
             const int k = __ldg(p.kernel_ids + e);
-            const int in_row = __ldg(p.in_rows + e);
-            if (in_row >= 0 && in_row < p.in_capacity && k >= 0 && k < p.kernel_count) {
+            if (k >= 0 && k < p.kernel_count) {
                 mask |= 1u << k;
             }
         }
     }
     mask = __reduce_or_sync(0xffffffffu, mask);
-    if (lane == 0 && mask != 0) {
+    if ((threadIdx.x & 31) == 0 && mask != 0) {
         atomicOr(&tile_mask, mask);
     }
     __syncthreads();
-    const uint32_t used = tile_mask;
-    const int present = __popc(used);
-    if (threadIdx.x < 32) {
-        volatile unsigned long long* status = tile_status;
-        long long exclusive = 0;
-        bool failed = false;
-        if (tile > 0) {
-            if (lane == 0) {
-                status[tile] = kPlanAggregate | static_cast<unsigned long long>(present);
-            }
-            const long long start = clock64();
-            int top = tile - 1;
-            while (true) {
-                const int t = top - lane;
-                unsigned long long v = 2ull << 62;  // before tile 0: a prefix of zero
-                if (t >= 0) {
-                    v = status[t];
-                }
-                const unsigned ready = __ballot_sync(0xffffffffu, v != 0);
-                const unsigned prefix = __ballot_sync(0xffffffffu, (v >> 63) != 0);
-                const int nearest = prefix != 0 ? __ffs(prefix) - 1 : 31;
-                const unsigned need = nearest >= 31 ? 0xffffffffu : ((2u << nearest) - 1u);
-                if ((ready & need) != need) {
-                    if (clock64() - start > kPlanLookbackBudgetCycles) {
-                        failed = true;
-                        break;
-                    }
-                    continue;
-                }
-                long long part = lane <= nearest ? static_cast<long long>(v & kPlanValueMask) : 0;
-#pragma unroll
-                for (int d = 16; d > 0; d >>= 1) {
-                    part += __shfl_xor_sync(0xffffffffu, part, d);
-                }
-                exclusive += part;
-                if (prefix != 0) {
-                    break;
-                }
-                top -= 32;
-            }
-        }
-        if (lane == 0) {
-            if (failed) {
-                s_failed = 1;
-                raise_status(p.status, LAT_STATUS_WAIT_TIMEOUT);
-            } else {
-                status[tile] = kPlanPrefix | static_cast<unsigned long long>(exclusive + present);
-                p.tile_info[tile] = make_int2(static_cast<int>(used), static_cast<int>(exclusive));
-                if (used != 0) {
-                    atomicMax(&p.tile_info[p.num_tiles].x, tile + 1);
-                }
-                if (tile == p.num_tiles - 1) {
-                    p.tile_info[p.num_tiles].y = static_cast<int>(exclusive + present);
-                }
-            }
-            s_base = static_cast<int>(exclusive);
-        }
+    if (threadIdx.x == 0) {
+        p.tile_info[blockIdx.x] = make_int2(static_cast<int>(tile_mask), 0);
+    }
+}
+
+// pass 2: exclusive scan of the vectors per tile (one block); the entry after the last
+// tile receives (tiles up to the last one with a non-empty mask, vector total)
+__global__ void __launch_bounds__(1024) plan_scan_kernel(int2* tile_info, int num_tiles) {
+    __shared__ int warp_totals[32];
+    __shared__ int carry;
+    __shared__ int active_tiles;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        carry = 0;
+        active_tiles = 0;
     }
     __syncthreads();
-    if (s_failed) {
-        return;
+    for (int first = 0; first < num_tiles; first += 1024) {
+        const int tile = first + threadIdx.x;
+        int2 info = make_int2(0, 0);
+        if (tile < num_tiles) {
+            info = tile_info[tile];
+        }
+        int wtotal;
+        const int prefix = warp_exclusive_scan(__popc(static_cast<uint32_t>(info.x)), wtotal);
+        if (lane == 0) {
+            warp_totals[warp] = wtotal;
+        }
+        __syncthreads();
+        int before = carry;
+        for (int w = 0; w < warp; ++w) {
+            before += warp_totals[w];
+        }
+        if (tile < num_tiles) {
+            tile_info[tile] = make_int2(info.x, before + prefix);
+            if (info.x != 0) {
+                atomicMax(&active_tiles, tile + 1);
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 1023) {
+            carry = before + prefix + __popc(static_cast<uint32_t>(info.x));
+        }
+        __syncthreads();
     }
-    int32_t* mine = p.vectors + static_cast<size_t>(s_base) * kPlanTileRows + plan_slot(r);
+    if (threadIdx.x == 0) {
+        tile_info[num_tiles] = make_int2(active_tiles, carry);
+    }
+}
+
+// pass 3: the row vectors
+__global__ void __launch_bounds__(kPlanTileRows) plan_fill_kernel(PlanBuildParams p) {
+    const int n_out = clamp_count(p.counts + 1, p.out_capacity);
+    const int edge_total = clamp_count(p.counts, p.edge_capacity);
+    const int2 info = p.tile_info[blockIdx.x];
+    const uint32_t mask = static_cast<uint32_t>(info.x);
+    const int present = __popc(mask);
+    const int r = threadIdx.x;
+    int32_t* mine = p.vectors + static_cast<size_t>(info.y) * kPlanTileRows + plan_slot(r);
     for (int o = 0; o < present; ++o) {
         mine[static_cast<size_t>(o) * kPlanTileRows] = -1;
     }
-    for (int e = begin; e < end; ++e) {
-        const int k = __ldg(p.kernel_ids + e);
-        const int in_row = __ldg(p.in_rows + e);
-        if (in_row < 0 || k < 0) {
-            continue;
+    const int row = plan_row(p, blockIdx.x * kPlanTileRows + r);
+    if (row >= 0 && row < n_out) {
+        const int begin = max(__ldg(p.row_offsets + row), 0);
+        const int end = min(__ldg(p.row_offsets + row + 1), edge_total);
+        for (int e = begin; e < end; ++e) {
+            const int k = __ldg(p.kernel_ids + e);
+            const int in_row = __ldg(p.in_rows + e);
+            if (in_row < 0 || k < 0) {
+                continue;
+            }
+            if (in_row >= p.in_capacity || k >= p.kernel_count) {
+                raise_status(p.status, LAT_STATUS_BAD_INDEX);
+                continue;
+            }
+            const int o = __popc(mask & ((1u << k) - 1u));
+            mine[static_cast<size_t>(o) * kPlanTileRows] = in_row;
         }
-        if (in_row >= p.in_capacity || k >= p.kernel_count) {
-            raise_status(p.status, LAT_STATUS_BAD_INDEX);
-            continue;
-        }
-        const int o = __popc(used & ((1u << k) - 1u));
-        mine[static_cast<size_t>(o) * kPlanTileRows] = in_row;
     }
 }
 
@@ -232,13 +209,11 @@ int lat_build_conv_plan(
     p.tile_info = static_cast<int2*>(plan);
     p.vectors = reinterpret_cast<int32_t*>(static_cast<char*>(plan) + plan_info_bytes(p.num_tiles));
     p.status = status;
-    // the look-back words, the ticket and the trailing tile_info entry start at zero
-    char* scratch = static_cast<char*>(plan) + plan_tile_info_bytes(p.num_tiles);
-    unsigned long long* tile_status = reinterpret_cast<unsigned long long*>(scratch);
-    int* ticket = reinterpret_cast<int*>(tile_status + p.num_tiles);
-    LAT_CUDA_CHECK(cudaMemsetAsync(scratch, 0, sizeof(unsigned long long) * (p.num_tiles + 1), stream));
-    LAT_CUDA_CHECK(cudaMemsetAsync(p.tile_info + p.num_tiles, 0, sizeof(int2), stream));
-    plan_single_pass_kernel<<<p.num_tiles, kPlanTileRows, 0, stream>>>(p, tile_status, ticket);
+    plan_mask_kernel<<<p.num_tiles, kPlanTileRows, 0, stream>>>(p);
+    LAT_LAUNCH_CHECK();
+    plan_scan_kernel<<<1, 1024, 0, stream>>>(p.tile_info, p.num_tiles);
+    LAT_LAUNCH_CHECK();
+    plan_fill_kernel<<<p.num_tiles, kPlanTileRows, 0, stream>>>(p);
     LAT_LAUNCH_CHECK();
     return LAT_OK;
 }

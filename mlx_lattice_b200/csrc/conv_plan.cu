@@ -65,10 +65,17 @@ __global__ void __launch_bounds__(kPlanTileRows) plan_mask_kernel(PlanBuildParam
     if (row >= 0 && row < n_out) {
         const int begin = max(__ldg(p.row_offsets + row), 0);
         const int end = min(__ldg(p.row_offsets + row + 1), edge_total);
-        for (int e = begin; e < end; ++e) {
-            const int k = __ldg(p.kernel_ids + e);
-            if (k >= 0 && k < p.kernel_count) {
-                mask |= 1u << k;
+        for (int e0 = begin; e0 < end; e0 += 4) {
+            int k[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                k[u] = e0 + u < end ? __ldg(p.kernel_ids + e0 + u) : -1;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (k[u] >= 0 && k[u] < p.kernel_count) {
+                    mask |= 1u << k[u];
+                }
             }
         }
     }
@@ -144,18 +151,27 @@ __global__ void __launch_bounds__(kPlanTileRows) plan_fill_kernel(PlanBuildParam
     if (row >= 0 && row < n_out) {
         const int begin = max(__ldg(p.row_offsets + row), 0);
         const int end = min(__ldg(p.row_offsets + row + 1), edge_total);
-        for (int e = begin; e < end; ++e) {
-            const int k = __ldg(p.kernel_ids + e);
-            const int in_row = __ldg(p.in_rows + e);
-            if (in_row < 0 || k < 0) {
-                continue;
+        // four edges per step: their loads are independent and overlap
+        for (int e0 = begin; e0 < end; e0 += 4) {
+            int k[4], in_row[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const bool live = e0 + u < end;
+                k[u] = live ? __ldg(p.kernel_ids + e0 + u) : -1;
+                in_row[u] = live ? __ldg(p.in_rows + e0 + u) : -1;
             }
-            if (in_row >= p.in_capacity || k >= p.kernel_count) {
-                raise_status(p.status, LAT_STATUS_BAD_INDEX);
-                continue;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (in_row[u] < 0 || k[u] < 0) {
+                    continue;
+                }
+                if (in_row[u] >= p.in_capacity || k[u] >= p.kernel_count) {
+                    raise_status(p.status, LAT_STATUS_BAD_INDEX);
+                    continue;
+                }
+                const int o = __popc(mask & ((1u << k[u]) - 1u));
+                mine[static_cast<size_t>(o) * kPlanTileRows] = in_row[u];
             }
-            const int o = __popc(mask & ((1u << k) - 1u));
-            mine[static_cast<size_t>(o) * kPlanTileRows] = in_row;
         }
     }
 }

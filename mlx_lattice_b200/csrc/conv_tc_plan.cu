@@ -11,7 +11,11 @@
 //              fill where the row has no neighbour), C_out/32 cp.async for the fp16 B
 //              tile, then cp.async.mbarrier.arrive.noinc so that the stage's barrier
 //              completes when the copies land. The stream of slabs runs across tile
-//              boundaries; tile headers are prefetched a tile ahead.
+//              boundaries; tile headers are prefetched a tile ahead. When C_in is a
+//              multiple of 64 both units of a slab share their kernel offset: the loop
+//              nest is tile > offset > slab with the row addresses computed once per
+//              offset, and the weight tile of a slab is one TMA box
+//              (cp.async.bulk.tensor.3d, 128-byte swizzle) issued by one thread.
 //   warp 16    one thread issues the MMAs (8 per slab), commits the stage back to the
 //              producers and, per tile, the accumulator to the epilogue.
 //   warps 8-15 epilogue: tcgen05.ld, optional bias, one cast to fp16, 16-byte stores.
@@ -359,7 +363,6 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
             i0 = n0;
             i1 = n1;
         }
-        (void)ok;
         cp_async_wait<0>();
         }
     } else if (warp < 16) {

@@ -277,9 +277,11 @@ def kernel_map_benchmark(device, steps: int, peaks: dict) -> dict:
         edges, n_out = counts
         cap = 1 << (4 * n - 1).bit_length()
         # algorithmic bytes per build: coord read, clear + insert of the 8-byte-slot table,
-        # one 32-byte bucket per probe, pair output, row offsets (+ output-support pass
+        # one 32-byte bucket per probe, edge arrays, row offsets (+ output-support pass
         # when strided)
-        hbm = n * 16 + 8 * cap + 8 * n + 12 * edges + 4 * (n_out + 1)
+        # the three edge arrays are outputs of static capacity n * 27 that the contract
+        # defines everywhere (pairs, then a zero tail): every byte of them is written
+        hbm = n * 16 + 8 * cap + 8 * n + 12 * n * 27 + 4 * (n + 1)
         if stride != 1:
             hbm += n * 16 + 8 * cap + 8 * n + 16 * n_out
         probes = 32 * 27 * n_out  # table reads, served by L2 (the table is 8 * cap bytes)

@@ -472,10 +472,10 @@ __global__ void __launch_bounds__(kBlockThreads) map_fill_kernel(MapParams p) {
 // ---- single-pass kernel map (K <= 32) --------------------------------------------------
 //
 // One block per 256 output rows (tiles taken in ticket order), one warp per 32 rows.
-//  1. probe, lane = kernel offset: every candidate's bucket is read once and scanned by
-//     tag only; the hit rows wait in shared memory. For the forward rule the candidate is
-//     `row base + offset`, so its two linear hash forms are the row's forms (computed once
-//     per row) plus a per-lane constant.
+//  1. probe, lane = output row: the K candidates of a row are K independent bucket reads,
+//     scanned by tag only; the hit rows wait in shared memory. For the forward rule the
+//     candidate is `row base + offset`, so its two linear hash forms are the row's forms
+//     (computed once per row) plus a per-offset constant from shared memory.
 //  2. verify, lane = output row: each tag hit is compared with the coordinate it stands
 //     for; a false tag match (one in 2^32) falls back to the exact table lookup.
 //  3. the block learns where its edges start from a decoupled look-back over the tiles
@@ -487,12 +487,11 @@ constexpr unsigned long long kTilePrefix = 2ull << 62;
 constexpr unsigned long long kTileValueMask = (1ull << 62) - 1;
 constexpr long long kLookbackBudgetCycles = 4000000000LL;  // about two seconds
 
-template <int kProbeRows, int kMinBlocks>
-__global__ void __launch_bounds__(kBlockThreads, kMinBlocks) map_single_pass_kernel(
+__global__ void __launch_bounds__(kBlockThreads, 5) map_single_pass_kernel(
     MapParams p, unsigned long long* tile_status, int* ticket, int num_tiles
 ) {
     extern __shared__ int s_hits[];            // [256][K]
-    __shared__ int4 s_row[kRowsPerBlock];      // forward rule: (u, t, -, -) of the row base; else the row's coords
+    __shared__ int2 s_offset_hash[32];         // forward rule: linear hash forms of the offsets
     __shared__ int4 s_offset[32];              // kernel offsets by id
     __shared__ int s_tile;
     __shared__ int s_base;
@@ -511,6 +510,9 @@ __global__ void __launch_bounds__(kBlockThreads, kMinBlocks) map_single_pass_ker
     }
     if (warp == 0) {
         s_offset[lane] = make_int4(ox, oy, oz, 0);
+        uint32_t u_off, t_off;
+        hash_linear(Coord{0, ox, oy, oz}, u_off, t_off);
+        s_offset_hash[lane] = make_int2(static_cast<int>(u_off), static_cast<int>(t_off));
     }
     __syncthreads();
     const int tile = s_tile;
@@ -527,61 +529,41 @@ __global__ void __launch_bounds__(kBlockThreads, kMinBlocks) map_single_pass_ker
     if (my_row < n_out) {
         mine = load_coord(p.out_coords, my_row);
     }
-    uint32_t u_lane = 0, t_lane = 0;  // linear hash forms of this lane's offset
+    // 1. probe, lane = output row: K independent bucket reads per lane
+    uint32_t u_row = 0, t_row = 0;  // linear hash forms of this row's base coordinate
     if (forward) {
-        hash_linear(Coord{0, ox, oy, oz}, u_lane, t_lane);
-        uint32_t u_row, t_row;
         hash_linear(Coord{mine.b, mine.x * p.sx - p.px, mine.y * p.sy - p.py, mine.z * p.sz - p.pz},
                     u_row, t_row);
-        s_row[warp * 32 + lane] = make_int4(static_cast<int>(u_row), static_cast<int>(t_row), 0, 0);
-    } else {
-        s_row[warp * 32 + lane] = make_int4(mine.b, mine.x, mine.y, mine.z);
     }
-    __syncwarp();
-
-    // 1. probe
     unsigned my_mask = 0;
     unsigned my_overflow = 0;  // offsets whose first bucket was full without a tag match
     int* warp_hits = s_hits + warp * 32 * K;
-    for (int j = 0; j < 32; j += kProbeRows) {
-        if (row0 + j >= n_out) {
-            break;
-        }
-        bool live[kProbeRows];
-        uint32_t tag[kProbeRows];
-        Bucket bucket[kProbeRows];
-#pragma unroll
-        for (int u = 0; u < kProbeRows; ++u) {
-            const int4 r = s_row[warp * 32 + j + u];
-            live[u] = lane < K && row0 + j + u < n_out;
-            uint32_t index = 0;
-            tag[u] = 0;
+    int* my_hits = warp_hits + lane * K;
+    const bool row_live = my_row < n_out;
+    if (row0 < n_out) {
+#pragma unroll 3
+        for (int k = 0; k < K; ++k) {
+            bool live = row_live;
+            uint32_t index = 0, tag = 0;
             if (forward) {
-                index = hash_finalize(static_cast<uint32_t>(r.x) + u_lane);
-                tag[u] = static_cast<uint32_t>(r.y) + t_lane;
-            } else if (live[u]) {
+                const int2 h = s_offset_hash[k];
+                index = hash_finalize(u_row + static_cast<uint32_t>(h.x));
+                tag = t_row + static_cast<uint32_t>(h.y);
+            } else if (live) {
+                const int4 off = s_offset[k];
                 Coord cand;
-                live[u] = candidate_of(p, Coord{r.x, r.y, r.z, r.w}, ox, oy, oz, cand);
-                hash_coord(cand, index, tag[u]);
+                live = candidate_of(p, mine, off.x, off.y, off.z, cand);
+                hash_coord(cand, index, tag);
             }
-            if (live[u]) {
-                bucket[u] = load_bucket(p.table, index & p.table_mask & ~(kBucketSlots - 1));
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kProbeRows; ++u) {
             int found = -1;
-            if (live[u]) {
-                found = scan_bucket_tags(bucket[u], tag[u]);
+            if (live) {
+                const Bucket bucket = load_bucket(p.table, index & p.table_mask & ~(kBucketSlots - 1));
+                found = scan_bucket_tags(bucket, tag);
             }
-            const unsigned m = __ballot_sync(0xffffffffu, found >= 0);
-            const unsigned full = __ballot_sync(0xffffffffu, found == -2);
-            if (lane == j + u) {
-                my_mask = m;
-                my_overflow = full;
-            }
-            if (lane < K) {
-                warp_hits[(j + u) * K + lane] = found;
+            my_mask |= found >= 0 ? (1u << k) : 0u;
+            my_overflow |= found == -2 ? (1u << k) : 0u;
+            if (found >= 0) {
+                my_hits[k] = found;
             }
         }
     }
@@ -1457,7 +1439,7 @@ int run_map(
         LAT_CUDA_CHECK(cudaMemsetAsync(ticket, 0, sizeof(int), stream));
         p.masks = o.row_masks;  // optional output; no scratch copy needed
         size_t smem = sizeof(int) * kRowsPerBlock * K;
-        map_single_pass_kernel<1, 5><<<nblocks, kBlockThreads, smem, stream>>>(p, tile_status, ticket, nblocks);
+        map_single_pass_kernel<<<nblocks, kBlockThreads, smem, stream>>>(p, tile_status, ticket, nblocks);
         LAT_LAUNCH_CHECK();
         if (tail_only) {
             LAT_CUDA_CHECK(zero_edge_tails(o.in_rows, o.out_rows, o.kernel_ids, edge_capacity, o.counts, stream));

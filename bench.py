@@ -438,6 +438,26 @@ def run_gpu_arm(args) -> None:
     launches = _ext.launch_count() - launches_before
     total_ms = sum(step_ms)
 
+    # ---- the same step captured once in a CUDA graph and replayed (informational) ----
+    graph_ms = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            resident_step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            resident_step()
+        graph.replay()
+        torch.cuda.synchronize()
+        graph_ms = sum(timed_steps(graph.replay, args.steps)) / args.steps
+        del graph
+    except Exception:  # noqa: BLE001 - capture support is optional for the headline number
+        graph_ms = None
+    barrier()
+
     # ---- end to end: pinned host buffers in, logits back to the host, every step ----
     for _ in range(2):
         e2e_step()
@@ -508,6 +528,8 @@ def run_gpu_arm(args) -> None:
             'roofline': roofline,
             'kernel_map': kernel_map,
             'front_end': front_end,
+            'cuda_graph_replay': None if graph_ms is None else {
+                'ms_per_step': graph_ms, 'value': voxels * world / (graph_ms / 1e3), 'unit': 'voxels/s'},
             'cpu_baseline': {k: cpu[k] for k in ('value', 'unit', 'cores', 'kind', 'sample')},
             'clocks': clocks,
             'wall_s_timed_region': wall,

@@ -44,7 +44,7 @@ def _active_rows(value: torch.Tensor | None, coords: torch.Tensor) -> torch.Tens
         if tuple(value.shape) != (1,) or value.dtype != torch.int32:
             raise ValueError('active_rows must have shape (1,) and int32 dtype.')
         return value
-    return torch.tensor([coords.shape[0]], dtype=torch.int32, device=coords.device)
+    return torch.full((1,), int(coords.shape[0]), dtype=torch.int32, device=coords.device)
 
 
 def _require_positive(values: Triple, name: str) -> None:

@@ -58,7 +58,7 @@ class CoordinateManager:
             default_key = (id(coords), normalized)
             if default_key in self._default_identity_keys:
                 return self._default_identity_keys[default_key]
-            active = torch.tensor([coords.shape[0]], dtype=torch.int32, device=coords.device)
+            active = torch.full((1,), int(coords.shape[0]), dtype=torch.int32, device=coords.device)
         else:
             active = active_rows
         cache_key = (id(coords), id(active), normalized)

@@ -64,7 +64,7 @@ def _batch_indices(value: torch.Tensor | None, rows: int, device) -> torch.Tenso
 
 def _active_rows(value: torch.Tensor | None, rows: int, device) -> torch.Tensor:
     if value is None:
-        return torch.tensor([rows], dtype=torch.int32, device=device)
+        return torch.full((1,), int(rows), dtype=torch.int32, device=device)
     if tuple(value.shape) != (1,) or value.dtype != torch.int32:
         raise ValueError('active_rows must have shape (1,) and int32 dtype.')
     return value

@@ -132,3 +132,37 @@ def test_module_surface_and_errors(cuda):
         ops.max_pool3d(x)
     with pytest.raises(ValueError, match='quantized weight input channels must match'):
         ops.subm_conv3d(x, quantize_weight(torch.randn(8, 3, 3, 3, 64).half(), group_size=32))
+
+
+def test_forward_pass_captures_into_a_cuda_graph(cuda):
+    """No call on the path synchronises or copies from pageable host memory: a whole
+    forward pass (maps, orders, plans, convolutions, head) is captured once and replayed
+    with the same bits as the eager run."""
+    from mlx_lattice_b200 import workloads
+    from mlx_lattice_b200.core import SparseTensor
+
+    coords_np, feats_np = workloads.minkunet_inputs(4, 2, 6000)
+    model = workloads.MinkUNet(workloads.quantize_all(workloads.minkunet_dense_weights(20264)), cuda)
+    coords = torch.from_numpy(coords_np).to(cuda)
+    feats = torch.from_numpy(feats_np).to(cuda)
+
+    def forward():
+        return model(SparseTensor(coords, feats, batch_counts=(6000, 6000))).feats
+
+    eager = forward()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        forward()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = forward()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(captured, eager)
+    feats.mul_(2)                      # new data in the same buffers
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(captured, forward())

@@ -146,7 +146,8 @@ def test_quantized_conv_float16(cuda, oracle, restatement, sphere, bits, c_in, c
     assert _max_rel_err(got, want) <= FP16_TOL
 
 
-@pytest.mark.parametrize('c_in,c_out', [(32, 32), (64, 128), (128, 64), (96, 48), (256, 256), (32, 16)])
+@pytest.mark.parametrize('c_in,c_out', [(32, 32), (64, 128), (128, 64), (96, 48), (256, 256), (32, 16),
+                                        (64, 16), (128, 48), (192, 240)])
 def test_conv_with_gather_plan(cuda, oracle, restatement, sphere, c_in, c_out):
     """The plan-driven tensor-core kernel: same bits as the relation-walking one, in
     natural row order and under a permutation, fp16 and packed int4 weights."""

@@ -228,13 +228,11 @@ table_insert(Slot* slots, uint32_t mask, int row, Coord key, KeyOf key_of, bool*
 #pragma unroll
         for (uint32_t i = 0; i < kBucketSlots; ++i) {
             Slot* ptr = slots + base + i;
-            Slot cur = *reinterpret_cast<volatile Slot*>(ptr);
+            // at this load factor the slot is usually empty: try to take it outright
+            // (one round trip) instead of reading it first
+            const Slot cur = atomicCAS(ptr, kEmptySlot, want);
             if (cur == kEmptySlot) {
-                Slot old = atomicCAS(ptr, kEmptySlot, want);
-                if (old == kEmptySlot) {
-                    return true;
-                }
-                cur = old;
+                return true;
             }
             if (static_cast<uint32_t>(cur >> 32) == tag &&
                 key_of(static_cast<int>(cur & 0xFFFFFFFFu)) == key) {

@@ -179,6 +179,31 @@ __global__ void __launch_bounds__(kVoxThreads) voxel_reduce_kernel(
     }
 }
 
+// few channels: one thread per output element (a warp per voxel would idle most lanes);
+// same order and arithmetic
+__global__ void __launch_bounds__(kVoxThreads) voxel_reduce_narrow_kernel(
+    const float* values, const int32_t* row_offsets, const int32_t* point_ids,
+    const int32_t* voxel_counts, int point_rows, long long elements, int channels, int mean, float* out
+) {
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (i >= elements) {
+        return;
+    }
+    const int voxel = static_cast<int>(i / channels);
+    const int c = static_cast<int>(i - static_cast<long long>(voxel) * channels);
+    const int begin = row_offsets[voxel];
+    const int end = row_offsets[voxel + 1];
+    const float scale = mean != 0 ? __fdiv_rn(1.0f, static_cast<float>(max(voxel_counts[voxel], 1))) : 1.0f;
+    float acc = 0.0f;
+    for (int e = begin; e < end; ++e) {
+        const int point = point_ids[e];
+        if (point >= 0 && point < point_rows) {
+            acc = fmaf(values[static_cast<size_t>(point) * channels + c], scale, acc);
+        }
+    }
+    out[i] = acc;
+}
+
 // inverse rows outside [0, voxel_rows) take no part (the reference skips them): they are
 // mapped to one extra trailing group that nobody reads
 __global__ void voxel_group_ids_kernel(
@@ -305,6 +330,13 @@ int lat_voxelize_features(
                                              point_ids, view_ws, view_bytes, status, stream_ptr);
     if (rc != LAT_OK) {
         return rc;
+    }
+    if (channels < 16) {
+        const long long elements = static_cast<long long>(voxel_rows) * channels;
+        voxel_reduce_narrow_kernel<<<vox_blocks(elements), kVoxThreads, 0, stream>>>(
+            values, row_offsets, point_ids, voxel_counts, point_rows, elements, channels, mean, out);
+        LAT_LAUNCH_CHECK();
+        return LAT_OK;
     }
     const int warps_per_block = kVoxThreads / 32;
     voxel_reduce_kernel<<<(voxel_rows + warps_per_block - 1) / warps_per_block, kVoxThreads, 0, stream>>>(

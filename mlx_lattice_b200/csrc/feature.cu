@@ -118,10 +118,24 @@ __global__ void __launch_bounds__(kThreads) linear_narrow_kernel(
                 for (int u = 0; u < 8; ++u) {
                     const float v = to_float<T>(v8[u]);
                     const float* w = w_tile + (c0 + u) * c_out;
+                    if ((c_out & 3) == 0) {
+                        // four weights per shared-memory read (rows of w_tile stay 16-byte aligned)
 #pragma unroll
-                    for (int j = 0; j < kNarrowOut; ++j) {
-                        if (j < c_out) {
-                            acc[j] = fmaf(v, w[j], acc[j]);
+                        for (int j = 0; j < kNarrowOut; j += 4) {
+                            if (j < c_out) {
+                                const float4 w4 = *reinterpret_cast<const float4*>(w + j);
+                                acc[j] = fmaf(v, w4.x, acc[j]);
+                                acc[j + 1] = fmaf(v, w4.y, acc[j + 1]);
+                                acc[j + 2] = fmaf(v, w4.z, acc[j + 2]);
+                                acc[j + 3] = fmaf(v, w4.w, acc[j + 3]);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < kNarrowOut; ++j) {
+                            if (j < c_out) {
+                                acc[j] = fmaf(v, w[j], acc[j]);
+                            }
                         }
                     }
                 }

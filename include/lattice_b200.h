@@ -330,6 +330,28 @@ int lat_voxelize_features(
     int32_t mean, float* out,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
+/* native/bindings/coords.cpp:353-395 (`build_point_voxel_map`); arithmetic
+ * cpu/quantization_detail.h:203-315. rows_out / weights_out [point_rows, 8]: for
+ * `linear` = 0 slot 0 holds the voxel at floor(position + 0.5) with weight 1, for
+ * `linear` = 1 slot c holds the cell corner (c & 1, c >> 1 & 1, c >> 2 & 1) above
+ * floor(position) with its trilinear weight; absent voxels and points at or beyond
+ * point_active_rows are (-1, 0). Voxel rows at or beyond voxel_active_rows are not
+ * looked up; duplicates resolve to the first row. */
+size_t lat_point_voxel_map_workspace_bytes(int32_t voxel_rows);
+int lat_build_point_voxel_map(
+    const float* points, const int32_t* batch_indices, int32_t point_rows,
+    const int32_t* point_active_rows, const int32_t* voxel_coords, int32_t voxel_rows,
+    const int32_t* voxel_active_rows, lat_float_triple voxel_size, lat_float_triple origin,
+    int32_t linear, int32_t* rows_out, float* weights_out,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* native/bindings/coords.cpp (`interpolate_point_features`); arithmetic
+ * cpu/quantization_detail.h:317-346: out [point_rows, channels] = sum over the eight
+ * slots, in slot order, of values[row] * weight (float32). */
+int lat_interpolate_point_features(
+    const float* values, const int32_t* rows, const float* weights, int32_t point_rows,
+    int32_t voxel_rows, int32_t channels, float* out, void* stream);
+
 /* ---- pooling and pointwise feature ops ---------------------------------- */
 
 /* native/bindings/pooling.cpp:17-72 (`sparse_pool_features`) ->

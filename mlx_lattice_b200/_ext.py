@@ -600,6 +600,70 @@ def voxelize_features(feats, inverse_rows, voxel_counts, active_rows, reduction)
     return out
 
 
+def build_point_voxel_map(points, batch_indices, point_active_rows, voxel_coords,
+                          voxel_active_rows, voxel_size, origin, interpolation):
+    """``_ext.build_point_voxel_map`` (``coords.cpp:353-395``): ``(rows, weights)``, both
+    ``(N, 8)``."""
+    _require_cuda(points, 'points')
+    if points.ndim != 2 or points.shape[1] != 3:
+        raise ValueError('points must have shape (N, 3).')
+    if points.dtype != torch.float32:
+        raise ValueError('points must be float32.')
+    if interpolation not in ('nearest', 'linear'):
+        raise ValueError("interpolation must be 'nearest' or 'linear'.")
+    points = points.contiguous()
+    rows = int(points.shape[0])
+    batch = _i32(batch_indices, 'batch_indices')
+    if tuple(batch.shape) != (rows,):
+        raise ValueError('batch_indices must have shape (N,) and int32 dtype.')
+    voxel_coords = _coords_arg(voxel_coords, 'voxel_coords')
+    point_active = _active_arg(point_active_rows)
+    _require_cuda(voxel_active_rows, 'voxel_active_rows')
+    if tuple(voxel_active_rows.shape) != (1,) or voxel_active_rows.dtype != torch.int32:
+        raise ValueError('voxel_active_rows must have shape (1,) and int32 dtype.')
+    size = _float_triple(voxel_size, 'voxel_size')
+    if min(size.x, size.y, size.z) <= 0.0:
+        raise ValueError('voxel_size values must be positive.')
+    device = points.device
+    voxels = int(voxel_coords.shape[0])
+    out_rows = torch.empty((rows, 8), dtype=torch.int32, device=device)
+    weights = torch.empty((rows, 8), dtype=torch.float32, device=device)
+    lib = _lib()
+    ws = _workspace(lib.lat_point_voxel_map_workspace_bytes(voxels), device)
+    with torch.cuda.device(device):
+        check(lib.lat_build_point_voxel_map(
+            _ptr(points), _ptr(batch), rows, _ptr(point_active), _ptr(voxel_coords), voxels,
+            _ptr(voxel_active_rows), size, _float_triple(origin, 'origin'),
+            1 if interpolation == 'linear' else 0, _ptr(out_rows), _ptr(weights), _ptr(ws),
+            ws.numel(), _ptr(status_word(device)), _stream(),
+        ))
+    return out_rows, weights
+
+
+def interpolate_point_features(voxel_feats, rows, weights):
+    """``_ext.interpolate_point_features``: (points, C) float32."""
+    _require_cuda(voxel_feats, 'voxel_feats')
+    if voxel_feats.ndim != 2:
+        raise ValueError('voxel_feats must have shape (N, C).')
+    if voxel_feats.dtype != torch.float32:
+        raise ValueError('point interpolation currently supports float32.')
+    rows = _i32(rows, 'rows')
+    _require_cuda(weights, 'weights')
+    if rows.ndim != 2 or rows.shape[1] != 8:
+        raise ValueError('rows must have shape (N, 8) and int32 dtype.')
+    if weights.shape != rows.shape or weights.dtype != torch.float32:
+        raise ValueError('weights must be float32.')
+    voxel_feats, weights = voxel_feats.contiguous(), weights.contiguous()
+    points, voxels, channels = int(rows.shape[0]), int(voxel_feats.shape[0]), int(voxel_feats.shape[1])
+    device = voxel_feats.device
+    out = torch.empty((points, channels), dtype=torch.float32, device=device)
+    with torch.cuda.device(device):
+        check(_lib().lat_interpolate_point_features(
+            _ptr(voxel_feats), _ptr(rows), _ptr(weights), points, voxels, channels, _ptr(out), _stream(),
+        ))
+    return out
+
+
 # --------------------------------------------------------------------------- #
 # convolution (native/bindings/convolution.cpp:12-146)
 # --------------------------------------------------------------------------- #

@@ -88,6 +88,9 @@ SIGNATURES = {
     'lat_sparse_quantize': (I, [P, P, I, P, FloatTriple, FloatTriple, P, P, P, P, P, c_size_t, P, P]),
     'lat_voxelize_features_workspace_bytes': (c_size_t, [I, I]),
     'lat_voxelize_features': (I, [P, P, P, P, I, I, I, I, P, P, c_size_t, P, P]),
+    'lat_point_voxel_map_workspace_bytes': (c_size_t, [I]),
+    'lat_build_point_voxel_map': (I, [P, P, I, P, P, I, P, FloatTriple, FloatTriple, I, P, P, P, c_size_t, P, P]),
+    'lat_interpolate_point_features': (I, [P, P, P, I, I, I, P, P]),
     'lat_sparse_pool_features': (
         I, [P, I, I, c_int64, P, P, P, I, P, P, I, I, I, I, P, P, P]),
     'lat_global_pool': (I, [P, I, I, P, I, I, P, P]),

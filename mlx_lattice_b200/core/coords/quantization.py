@@ -47,6 +47,27 @@ class SparseQuantization:
         return self.active_rows
 
 
+@dataclass(frozen=True, slots=True)
+class PointVoxelMap:
+    """Fixed-width point-to-voxel interpolation rows and weights (``:64-89``): both
+    ``(N, 8)``; linear interpolation uses up to eight voxel rows per point, nearest one."""
+
+    rows: torch.Tensor
+    weights: torch.Tensor
+
+    def __post_init__(self) -> None:
+        if self.rows.ndim != 2 or self.rows.shape[1] != 8 or self.rows.dtype != torch.int32:
+            raise ValueError('rows must have shape (N, 8) and int32 dtype.')
+        if self.weights.shape != self.rows.shape:
+            raise ValueError('weights must have the same shape as rows.')
+        if self.weights.dtype != torch.float32:
+            raise ValueError('weights must be float32.')
+
+    @property
+    def point_count(self) -> int:
+        return int(self.rows.shape[0])
+
+
 def _validate_points(points: torch.Tensor) -> None:
     if points.ndim != 2 or points.shape[1] != 3:
         raise ValueError('points must have shape (N, 3).')
@@ -128,3 +149,47 @@ def voxelize_features(
         feats, quantization.inverse_rows, quantization.counts, point_rows,
         _validate_reduction(reduction),
     )
+
+
+def _validate_interpolation(value: str) -> str:
+    if value in ('nearest', 'linear'):
+        return value
+    raise ValueError("interpolation must be 'nearest' or 'linear'.")
+
+
+def build_point_voxel_map(
+    points: torch.Tensor,
+    voxel_coords: torch.Tensor,
+    voxel_active_rows: torch.Tensor,
+    voxel_size: float | Sequence[float] = 1.0,
+    *,
+    batch_indices: torch.Tensor | None = None,
+    point_active_rows: torch.Tensor | None = None,
+    origin: float | Sequence[float] = 0.0,
+    interpolation: str = 'linear',
+) -> PointVoxelMap:
+    """Build fixed-width interpolation rows from points to voxel centers (``:148-189``)."""
+    _validate_points(points)
+    validate_coords(voxel_coords)
+    if voxel_coords.dtype != torch.int32:
+        raise ValueError('voxel_coords must be int32.')
+    rows = int(points.shape[0])
+    batches = _batch_indices(batch_indices, rows, points.device)
+    point_rows = _active_rows(point_active_rows, rows, points.device)
+    if tuple(voxel_active_rows.shape) != (1,) or voxel_active_rows.dtype != torch.int32:
+        raise ValueError('voxel_active_rows must have shape (1,) and int32 dtype.')
+    native = _ext.build_point_voxel_map(
+        points, batches, point_rows, voxel_coords, voxel_active_rows,
+        _float_triple(voxel_size, 'voxel_size'), _float_triple(origin, 'origin'),
+        _validate_interpolation(interpolation),
+    )
+    return PointVoxelMap(*native)
+
+
+def interpolate_point_features(voxel_feats: torch.Tensor, point_voxel_map: PointVoxelMap) -> torch.Tensor:
+    """Interpolate voxel features back to point rows (``:192-208``)."""
+    if voxel_feats.ndim != 2:
+        raise ValueError('voxel_feats must have shape (N, C).')
+    if voxel_feats.dtype != torch.float32:
+        raise ValueError('point interpolation currently supports float32.')
+    return _ext.interpolate_point_features(voxel_feats, point_voxel_map.rows, point_voxel_map.weights)

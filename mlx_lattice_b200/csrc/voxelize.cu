@@ -11,6 +11,11 @@
 // ascending point order with one fused multiply-add per term (the order and rounding of
 // the reference's sequential loop): the points of a voxel come from the stable grouped
 // view of the inverse rows, one warp per voxel, lanes across channels.
+//
+// lat_build_point_voxel_map / lat_interpolate_point_features: the way back. Every point
+// gets eight (voxel row, weight) slots: the nearest voxel centre with weight 1, or the
+// eight corners of its cell with trilinear weights; corners that are not voxels stay
+// (-1, 0). Interpolation is the weighted sum over the slots in slot order.
 #include <algorithm>
 
 #include "common.cuh"
@@ -222,6 +227,99 @@ __global__ void voxel_group_ids_kernel(
     }
 }
 
+struct PointFrame {
+    const float* points;
+    const int32_t* batch;
+    float vx, vy, vz;
+    float ox, oy, oz;
+    // (p - origin) / voxel_size per axis, float32
+    __device__ __forceinline__ void position(int row, float (&pos)[3]) const {
+        const float* p = points + static_cast<size_t>(row) * 3;
+        pos[0] = __fdiv_rn(__fsub_rn(p[0], ox), vx);
+        pos[1] = __fdiv_rn(__fsub_rn(p[1], oy), vy);
+        pos[2] = __fdiv_rn(__fsub_rn(p[2], oz), vz);
+    }
+};
+
+__global__ void __launch_bounds__(kVoxThreads) voxel_table_insert_kernel(
+    const int32_t* coords, const int32_t* active_ptr, int rows, Slot* table, uint32_t mask, int32_t* status
+) {
+    const int active = clamp_count(active_ptr, rows);
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    PlainKey key_of{coords};
+    if (row < active && !table_insert(table, mask, row, key_of(row), key_of, nullptr)) {
+        raise_status(status, LAT_STATUS_HASH_FULL);
+    }
+}
+
+// one thread per (point, slot)
+__global__ void __launch_bounds__(kVoxThreads) point_voxel_map_kernel(
+    PointFrame frame, const int32_t* point_active_ptr, int point_rows, const int32_t* voxel_coords,
+    const Slot* table, uint32_t mask, int linear, int32_t* rows_out, float* weights_out
+) {
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (i >= static_cast<long long>(point_rows) * 8) {
+        return;
+    }
+    const int point = static_cast<int>(i >> 3);
+    const int corner = static_cast<int>(i & 7);
+    int row = -1;
+    float weight = 0.0f;
+    if (point < clamp_count(point_active_ptr, point_rows)) {
+        float pos[3];
+        frame.position(point, pos);
+        const int b = frame.batch != nullptr ? frame.batch[point] : 0;
+        PlainKey key_of{voxel_coords};
+        if (linear == 0) {
+            if (corner == 0) {
+                const Coord query{b, static_cast<int>(floorf(__fadd_rn(pos[0], 0.5f))),
+                                  static_cast<int>(floorf(__fadd_rn(pos[1], 0.5f))),
+                                  static_cast<int>(floorf(__fadd_rn(pos[2], 0.5f)))};
+                row = table_find(table, mask, query, key_of);
+                weight = row >= 0 ? 1.0f : 0.0f;
+            }
+        } else {
+            const float lower[3] = {floorf(pos[0]), floorf(pos[1]), floorf(pos[2])};
+            const float frac[3] = {__fsub_rn(pos[0], lower[0]), __fsub_rn(pos[1], lower[1]),
+                                   __fsub_rn(pos[2], lower[2])};
+            const int dx = corner & 1, dy = (corner >> 1) & 1, dz = (corner >> 2) & 1;
+            const Coord query{b, static_cast<int>(lower[0]) + dx, static_cast<int>(lower[1]) + dy,
+                              static_cast<int>(lower[2]) + dz};
+            row = table_find(table, mask, query, key_of);
+            if (row >= 0) {
+                const float wx = dx == 0 ? __fsub_rn(1.0f, frac[0]) : frac[0];
+                const float wy = dy == 0 ? __fsub_rn(1.0f, frac[1]) : frac[1];
+                const float wz = dz == 0 ? __fsub_rn(1.0f, frac[2]) : frac[2];
+                weight = __fmul_rn(__fmul_rn(wx, wy), wz);
+            }
+        }
+    }
+    rows_out[i] = row;
+    weights_out[i] = weight;
+}
+
+// one thread per output element; slots in order, one fused multiply-add each
+__global__ void __launch_bounds__(kVoxThreads) point_interpolate_kernel(
+    const float* values, const int32_t* rows, const float* weights, long long elements, int voxel_rows,
+    int channels, float* out
+) {
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (i >= elements) {
+        return;
+    }
+    const long long point = i / channels;
+    const int c = static_cast<int>(i - point * channels);
+    float acc = 0.0f;
+#pragma unroll
+    for (int corner = 0; corner < 8; ++corner) {
+        const int voxel = rows[point * 8 + corner];
+        if (voxel >= 0 && voxel < voxel_rows) {
+            acc = fmaf(values[static_cast<size_t>(voxel) * channels + c], weights[point * 8 + corner], acc);
+        }
+    }
+    out[i] = acc;
+}
+
 inline int vox_blocks(long long count) { return static_cast<int>((count + kVoxThreads - 1) / kVoxThreads); }
 
 } // namespace
@@ -341,6 +439,68 @@ int lat_voxelize_features(
     const int warps_per_block = kVoxThreads / 32;
     voxel_reduce_kernel<<<(voxel_rows + warps_per_block - 1) / warps_per_block, kVoxThreads, 0, stream>>>(
         values, row_offsets, point_ids, voxel_counts, point_rows, voxel_rows, channels, mean, out);
+    LAT_LAUNCH_CHECK();
+    return LAT_OK;
+}
+
+size_t lat_point_voxel_map_workspace_bytes(int32_t voxel_rows) {
+    return align_up(sizeof(Slot) * table_slots(std::max(voxel_rows, 1))) + 1024;
+}
+
+int lat_build_point_voxel_map(
+    const float* points, const int32_t* batch_indices, int32_t point_rows,
+    const int32_t* point_active_rows, const int32_t* voxel_coords, int32_t voxel_rows,
+    const int32_t* voxel_active_rows, lat_float_triple voxel_size, lat_float_triple origin,
+    int32_t linear, int32_t* rows_out, float* weights_out,
+    void* workspace, size_t workspace_bytes, int32_t* status, void* stream_ptr
+) {
+    LAT_REQUIRE(point_rows >= 0 && voxel_rows >= 0, "points must have shape (N, 3).");
+    LAT_REQUIRE(voxel_size.x > 0.0f && voxel_size.y > 0.0f && voxel_size.z > 0.0f,
+                "voxel_size values must be positive.");
+    LAT_REQUIRE(point_active_rows != nullptr && voxel_active_rows != nullptr,
+                "active_rows must have shape (1,) and int32 dtype.");
+    if (point_rows == 0) {
+        return LAT_OK;
+    }
+    LAT_REQUIRE(points != nullptr && rows_out != nullptr && weights_out != nullptr &&
+                    (voxel_coords != nullptr || voxel_rows == 0),
+                "points, voxel_coords, rows and weights are required.");
+    cudaStream_t stream = as_stream(stream_ptr);
+    Workspace ws(workspace, workspace_bytes);
+    const int capacity = table_slots(std::max(voxel_rows, 1));
+    Slot* table = ws.take<Slot>(capacity);
+    if (!ws.ok) {
+        return fail(LAT_WORKSPACE_TOO_SMALL, "workspace is too small for the point-voxel map.");
+    }
+    const uint32_t mask = static_cast<uint32_t>(capacity - 1);
+    LAT_CUDA_CHECK(cudaMemsetAsync(table, 0xFF, sizeof(Slot) * capacity, stream));
+    if (voxel_rows > 0) {
+        voxel_table_insert_kernel<<<vox_blocks(voxel_rows), kVoxThreads, 0, stream>>>(
+            voxel_coords, voxel_active_rows, voxel_rows, table, mask, status);
+        LAT_LAUNCH_CHECK();
+    }
+    PointFrame frame{points, batch_indices, voxel_size.x, voxel_size.y, voxel_size.z,
+                     origin.x, origin.y, origin.z};
+    point_voxel_map_kernel<<<vox_blocks(static_cast<long long>(point_rows) * 8), kVoxThreads, 0, stream>>>(
+        frame, point_active_rows, point_rows, voxel_coords, table, mask, linear, rows_out, weights_out);
+    LAT_LAUNCH_CHECK();
+    return LAT_OK;
+}
+
+int lat_interpolate_point_features(
+    const float* values, const int32_t* rows, const float* weights, int32_t point_rows,
+    int32_t voxel_rows, int32_t channels, float* out, void* stream_ptr
+) {
+    LAT_REQUIRE(point_rows >= 0 && voxel_rows >= 0 && channels >= 0,
+                "voxel_feats must have shape (N, C).");
+    if (point_rows == 0 || channels == 0) {
+        return LAT_OK;
+    }
+    LAT_REQUIRE(rows != nullptr && weights != nullptr && out != nullptr && (values != nullptr || voxel_rows == 0),
+                "voxel_feats, rows, weights and out are required.");
+    const long long elements = static_cast<long long>(point_rows) * channels;
+    point_interpolate_kernel<<<vox_blocks(elements), kVoxThreads, 0, as_stream(stream_ptr)>>>(
+        values, rows, weights, elements, voxel_rows, channels, out);
     LAT_LAUNCH_CHECK();
     return LAT_OK;
 }

@@ -23,11 +23,19 @@ from mlx_lattice_b200.ops.pool import (
     pool3d,
     sum_pool3d,
 )
-from mlx_lattice_b200.ops.quantization import sparse_quantize, voxelize, voxelize_with_quantization
+from mlx_lattice_b200.ops.quantization import (
+    build_point_voxel_map,
+    devoxelize,
+    interpolate_point_features,
+    sparse_quantize,
+    voxelize,
+    voxelize_with_quantization,
+)
 from mlx_lattice_b200.ops.tensor import sparse_cat_aligned, sparse_collate
 
 __all__ = [
-    'avg_pool3d', 'batch_norm', 'build_generative_relation', 'build_kernel_relation',
+    'avg_pool3d', 'batch_norm', 'build_generative_relation', 'build_point_voxel_map', 'devoxelize',
+    'interpolate_point_features', 'build_kernel_relation',
     'build_submanifold_kernel_relation', 'build_target_kernel_relation',
     'build_target_transposed_relation', 'build_transposed_kernel_relation', 'conv3d',
     'conv_transpose3d', 'generative_conv_transpose3d', 'global_avg_pool', 'global_max_pool',

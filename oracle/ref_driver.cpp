@@ -610,4 +610,77 @@ int ref_voxelize_features(
     });
 }
 
+// Point -> voxel interpolation slots (nearest or trilinear):
+// cpu/quantization_algorithms.cpp -> cpu/quantization_detail.h:203-315.
+int ref_point_voxel_map(
+    const float* points,
+    const int32_t* batch_indices,
+    int point_rows,
+    const int32_t* point_active_rows,
+    const int32_t* voxel_coords,
+    int voxel_rows,
+    const int32_t* voxel_active_rows,
+    const float* voxel_size,
+    const float* origin,
+    int linear,
+    int32_t* rows,
+    float* weights
+) {
+    return guarded([&] {
+        std::vector<mx::array> inputs{
+            mx::array(const_cast<float*>(points), {point_rows, 3}, mx::float32),
+            i32(batch_indices, {point_rows}),
+            i32(point_active_rows, {1}),
+            i32(voxel_coords, {voxel_rows, 4}),
+            i32(voxel_active_rows, {1}),
+        };
+        std::vector<mx::array> outputs{
+            i32(rows, {point_rows, 8}),
+            mx::array(weights, {point_rows, 8}, mx::float32),
+        };
+        mlx_lattice::QuantizationSpec spec{
+            {voxel_size[0], voxel_size[1], voxel_size[2]},
+            {origin[0], origin[1], origin[2]},
+        };
+        mlx_lattice::coords::cpu::eval_point_voxel_map(
+            spec,
+            linear != 0 ? mlx_lattice::PointVoxelInterpolationOp::Linear
+                        : mlx_lattice::PointVoxelInterpolationOp::Nearest,
+            mlx_lattice::PointVoxelMapShape{point_rows, voxel_rows},
+            host_stream(),
+            inputs,
+            outputs
+        );
+    });
+}
+
+// Weighted sum of voxel features over a point's slots:
+// cpu/quantization_detail.h:317-346.
+int ref_interpolate_point_features(
+    const float* values,
+    const int32_t* rows,
+    const float* weights,
+    int point_rows,
+    int voxel_rows,
+    int channels,
+    float* out
+) {
+    return guarded([&] {
+        std::vector<mx::array> inputs{
+            mx::array(const_cast<float*>(values), {voxel_rows, channels}, mx::float32),
+            i32(rows, {point_rows, 8}),
+            mx::array(const_cast<float*>(weights), {point_rows, 8}, mx::float32),
+        };
+        std::vector<mx::array> outputs{
+            mx::array(out, {point_rows, channels}, mx::float32),
+        };
+        mlx_lattice::coords::cpu::eval_interpolate_point_features(
+            mlx_lattice::VoxelFeatureShape{point_rows, voxel_rows, channels},
+            host_stream(),
+            inputs,
+            outputs
+        );
+    });
+}
+
 } // extern "C"

@@ -328,6 +328,45 @@ def voxelize_features(values, inverse_rows, voxel_counts, active_rows, reduction
     return out
 
 
+def point_voxel_map(points, batch_indices, point_active, voxel_coords, voxel_active,
+                    voxel_size=1.0, origin=0.0, interpolation='linear'):
+    """``eval_point_voxel_map``: rows (P, 8) int32 and weights (P, 8) float32."""
+    points = np.ascontiguousarray(points, np.float32).reshape(-1, 3)
+    rows = points.shape[0]
+    batch = np.zeros(rows, np.int32) if batch_indices is None else _i32(batch_indices)
+    voxel_coords = _i32(voxel_coords).reshape(-1, 4)
+    p_active = np.asarray([rows if point_active is None else int(np.asarray(point_active).ravel()[0])], np.int32)
+    v_active = np.asarray([voxel_coords.shape[0] if voxel_active is None
+                           else int(np.asarray(voxel_active).ravel()[0])], np.int32)
+    vs = np.ascontiguousarray(np.broadcast_to(np.asarray(voxel_size, np.float32), (3,)))
+    og = np.ascontiguousarray(np.broadcast_to(np.asarray(origin, np.float32), (3,)))
+    out_rows = np.zeros((rows, 8), np.int32)
+    weights = np.zeros((rows, 8), np.float32)
+    _check(
+        lib().ref_point_voxel_map(
+            _p(points), _p(batch), rows, _p(p_active), _p(voxel_coords), voxel_coords.shape[0],
+            _p(v_active), _p(vs), _p(og), 1 if interpolation == 'linear' else 0, _p(out_rows),
+            _p(weights)
+        ),
+        'point_voxel_map',
+    )
+    return out_rows, weights
+
+
+def interpolate_point_features(values, rows, weights):
+    """``eval_interpolate_point_features``: (P, C) float32."""
+    values = np.ascontiguousarray(values, np.float32)
+    rows, weights = _i32(rows), np.ascontiguousarray(weights, np.float32)
+    out = np.zeros((rows.shape[0], values.shape[1]), np.float32)
+    _check(
+        lib().ref_interpolate_point_features(
+            _p(values), _p(rows), _p(weights), rows.shape[0], values.shape[0], values.shape[1], _p(out)
+        ),
+        'interpolate_point_features',
+    )
+    return out
+
+
 def lookup_coords(coords, queries):
     coords, queries = _i32(coords), _i32(queries)
     out = np.zeros(queries.shape[0], np.int32)

@@ -165,6 +165,62 @@ def voxelize_features(values, inverse_rows, voxel_counts, active_rows, reduction
     return out
 
 
+def point_voxel_map(points, batch_indices, point_active, voxel_coords, voxel_active,
+                    voxel_size=1.0, origin=0.0, interpolation='linear'):
+    """``write_nearest_point_voxel_map`` / ``write_linear_point_voxel_map``
+    (``cpu/quantization_detail.h:203-315``): eight (voxel row, weight) slots per point;
+    positions (p - origin) / size in float32; nearest = floor(position + 0.5) in slot 0 with
+    weight 1; linear = the eight corners above floor(position) with weights
+    (wx * wy) * wz, w = 1 - frac or frac; absent voxels and inactive points stay (-1, 0)."""
+    points = np.asarray(points, np.float32).reshape(-1, 3)
+    rows = points.shape[0]
+    batch = np.zeros(rows, np.int32) if batch_indices is None else np.asarray(batch_indices, np.int32)
+    voxel_coords = np.asarray(voxel_coords, np.int32).reshape(-1, 4)
+    p_active = rows if point_active is None else min(int(np.asarray(point_active).ravel()[0]), rows)
+    v_active = voxel_coords.shape[0] if voxel_active is None else min(
+        int(np.asarray(voxel_active).ravel()[0]), voxel_coords.shape[0])
+    vs = np.broadcast_to(np.asarray(voxel_size, np.float32), (3,))
+    og = np.broadcast_to(np.asarray(origin, np.float32), (3,))
+    out_rows = np.full((rows, 8), -1, np.int32)
+    weights = np.zeros((rows, 8), np.float32)
+    pos = (points[:p_active] - og[None, :]) / vs[None, :]
+    if interpolation == 'nearest':
+        cell = np.floor(pos + np.float32(0.5)).astype(np.int64)
+        q = np.concatenate([batch[:p_active, None].astype(np.int64), cell], axis=1)
+        found = lookup_coords(voxel_coords[:v_active], q.astype(np.int32))
+        out_rows[:p_active, 0] = found
+        weights[:p_active, 0] = (found >= 0).astype(np.float32)
+        return out_rows, weights
+    lower = np.floor(pos)
+    frac = (pos - lower).astype(np.float32)
+    lower = lower.astype(np.int64)
+    for corner in range(8):
+        d = np.asarray([corner & 1, (corner >> 1) & 1, (corner >> 2) & 1])
+        q = np.concatenate([batch[:p_active, None].astype(np.int64), lower + d[None, :]], axis=1)
+        found = lookup_coords(voxel_coords[:v_active], q.astype(np.int32))
+        w = [np.where(d[a] == 0, np.float32(1.0) - frac[:, a], frac[:, a]).astype(np.float32) for a in range(3)]
+        weight = ((w[0] * w[1]).astype(np.float32) * w[2]).astype(np.float32)
+        out_rows[:p_active, corner] = found
+        weights[:p_active, corner] = np.where(found >= 0, weight, np.float32(0.0))
+    return out_rows, weights
+
+
+def interpolate_point_features(values, rows, weights):
+    """``write_point_features`` (``cpu/quantization_detail.h:317-346``): running float32
+    sum over the eight slots in order of value * weight (the compiled reference fuses the
+    multiply-add; this restatement rounds the product)."""
+    values = np.asarray(values, np.float32)
+    rows = np.asarray(rows, np.int32)
+    weights = np.asarray(weights, np.float32)
+    out = np.zeros((rows.shape[0], values.shape[1]), np.float32)
+    for corner in range(8):
+        r = rows[:, corner]
+        ok = (r >= 0) & (r < values.shape[0])
+        term = values[np.where(ok, r, 0)] * weights[:, corner, None]
+        out = np.where(ok[:, None], out + term, out).astype(np.float32)
+    return out
+
+
 def downsample_coords(coords, stride):
     """Set-op form (``cpu/set_algorithms.cpp:4-37``): zero-padded (N, 4) buffer
     with the unique rows as prefix, and the count."""

@@ -261,3 +261,38 @@ def test_quantization_restatement_matches_compiled_reference():
         g = restatement.voxelize_features(feats[:3000], got[2][:3000], got[3], np.asarray([3000], np.int32), mode)
         w = reference.voxelize_features(feats[:3000], want[2][:3000], want[3], np.asarray([3000], np.int32), mode)
         assert np.allclose(g, w, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize('backend', BACKENDS, ids=IDS)
+def test_known_answer_devoxelize(backend):
+    """Point-voxel map and interpolation against the reference's own known answers."""
+    for name, mode in (('devoxelize_nearest', 'nearest'), ('devoxelize_linear', 'linear'),
+                       ('point_map_active_rows', 'nearest'), ('interpolate_linear_quarter', 'linear')):
+        kat = KATS[name]
+        coords = np.asarray(kat['coords'], np.int32)
+        rows, weights = backend.point_voxel_map(
+            np.asarray(kat['points'], np.float32), None, kat.get('point_active'), coords,
+            kat.get('voxel_active'), 1.0, 0.0, mode)
+        out = backend.interpolate_point_features(np.asarray(kat['feats'], np.float32), rows, weights)
+        assert np.allclose(out, kat['out']), name
+
+
+@pytest.mark.skipif(not reference.available(), reason='compiled reference not built')
+def test_point_voxel_map_restatement_matches_compiled_reference():
+    rng = np.random.default_rng(43)
+    voxels = np.unique(rng.integers(-6, 6, size=(3000, 4)).astype(np.int32), axis=0)
+    voxels[:, 0] = np.abs(voxels[:, 0]) % 2
+    voxels = voxels[rng.permutation(voxels.shape[0])]
+    points = (rng.uniform(-7, 7, size=(5000, 3))).astype(np.float32)
+    points[::9] = np.round(points[::9])
+    batch = rng.integers(0, 2, size=5000).astype(np.int32)
+    feats = rng.normal(size=(voxels.shape[0], 3)).astype(np.float32)
+    for mode in ('nearest', 'linear'):
+        got = restatement.point_voxel_map(points, batch, [4800], voxels, [voxels.shape[0] - 7],
+                                          (1.0, 0.5, 2.0), (0.25, 0.0, -0.5), mode)
+        want = reference.point_voxel_map(points, batch, [4800], voxels, [voxels.shape[0] - 7],
+                                         (1.0, 0.5, 2.0), (0.25, 0.0, -0.5), mode)
+        assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1]), mode
+        g = restatement.interpolate_point_features(feats, *got)
+        w = reference.interpolate_point_features(feats, *want)
+        assert np.allclose(g, w, rtol=1e-5, atol=1e-6)

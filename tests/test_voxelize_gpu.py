@@ -138,3 +138,72 @@ def test_argument_errors(cuda):
         ops.voxelize(points, torch.zeros((4, 2), device=cuda), reduction='max')
     with pytest.raises(ValueError, match='matching rows'):
         ops.voxelize(points, torch.zeros((3, 2), device=cuda))
+
+
+def test_devoxelize_known_answers(cuda):
+    from mlx_lattice_b200 import ops
+    from mlx_lattice_b200.core import SparseTensor
+
+    for name, mode in (('devoxelize_nearest', 'nearest'), ('devoxelize_linear', 'linear'),
+                       ('interpolate_linear_quarter', 'linear')):
+        kat = KATS[name]
+        voxels = SparseTensor(_dev(np.asarray(kat['coords'], np.int32), cuda),
+                              _dev(np.asarray(kat['feats'], np.float32), cuda))
+        got = ops.devoxelize(_dev(np.asarray(kat['points'], np.float32), cuda), voxels, interpolation=mode)
+        assert np.allclose(got.cpu().numpy(), kat['out']), name
+    kat = KATS['point_map_active_rows']
+    coords = _dev(np.asarray(kat['coords'], np.int32), cuda)
+    feats = _dev(np.asarray(kat['feats'], np.float32), cuda)
+    point_map = ops.build_point_voxel_map(
+        _dev(np.asarray(kat['points'], np.float32), cuda), coords,
+        _dev(np.asarray(kat['voxel_active'], np.int32), cuda),
+        point_active_rows=_dev(np.asarray(kat['point_active'], np.int32), cuda), interpolation='nearest')
+    assert point_map.point_count == 2
+    assert np.allclose(ops.interpolate_point_features(feats, point_map).cpu().numpy(), kat['out'])
+
+
+@pytest.mark.parametrize('mode', ['nearest', 'linear'])
+def test_point_voxel_map_matches_oracle(cuda, oracle, restatement, mode):
+    from mlx_lattice_b200 import _ext
+
+    rng = np.random.default_rng(51)
+    voxels = np.unique(rng.integers(-12, 12, size=(30000, 4)).astype(np.int32), axis=0)
+    voxels[:, 0] = np.abs(voxels[:, 0]) % 3
+    voxels = np.concatenate([voxels, voxels[:500]])            # duplicates: first row wins
+    voxels = voxels[rng.permutation(voxels.shape[0])]
+    points = rng.uniform(-13, 13, size=(40000, 3)).astype(np.float32)
+    points[::9] = np.round(points[::9])
+    batch = rng.integers(0, 3, size=40000).astype(np.int32)
+    p_active, v_active = [39000], [voxels.shape[0] - 100]
+    size, origin = (1.0, 0.5, 2.0), (0.25, 0.0, -0.5)
+    want_rows, want_weights = oracle.point_voxel_map(points, batch, p_active, voxels, v_active, size,
+                                                     origin, mode)
+    got_rows, got_weights = _ext.build_point_voxel_map(
+        _dev(points, cuda), _dev(batch, cuda), _dev(np.asarray(p_active, np.int32), cuda),
+        _dev(voxels, cuda), _dev(np.asarray(v_active, np.int32), cuda), size, origin, mode)
+    assert np.array_equal(got_rows.cpu().numpy(), want_rows)
+    assert np.array_equal(got_weights.cpu().numpy(), want_weights)
+    feats = rng.normal(size=(voxels.shape[0], 6)).astype(np.float32)
+    want = oracle.interpolate_point_features(feats, want_rows, want_weights)
+    got = _ext.interpolate_point_features(_dev(feats, cuda), got_rows, got_weights).cpu().numpy()
+    if oracle is restatement:
+        assert np.allclose(got, want, rtol=1e-5, atol=1e-6)
+    else:
+        assert np.array_equal(got, want)
+    _ext.check_status(cuda)
+
+
+def test_voxelize_then_devoxelize_round_trip(cuda):
+    """Nearest devoxelisation of mean-voxelised features returns, for every point, the mean of
+    its own voxel: the voxel centre convention (floor on the way in, floor(x + 0.5) on the way
+    back) differs by half a cell, so points are sampled at their voxel's integer corner."""
+    from mlx_lattice_b200 import ops
+
+    rng = np.random.default_rng(8)
+    cells = rng.integers(0, 40, size=(20000, 3))
+    points = _dev(cells.astype(np.float32), cuda)              # points on integer positions
+    feats = _dev(rng.normal(size=(20000, 3)).astype(np.float32), cuda)
+    x = ops.voxelize(points, feats, 1.0, reduction='mean')
+    back = ops.devoxelize(points, x, 1.0, interpolation='nearest')
+    quant = ops.sparse_quantize(points, 1.0)
+    assert torch.equal(back, x.feats[quant.inverse_rows.long()])

@@ -85,6 +85,21 @@ int lat_kernel_offsets_host(lat_triple kernel_size, lat_triple dilation, int32_t
  * target rows for target maps, rows*K for transposed/generative). */
 size_t lat_relation_workspace_bytes(int32_t rows, int32_t out_rows, int32_t kernel_count);
 
+/* The first-row-wins coordinate table every builder below starts from (the
+ * reference's GPU builders fill one per call: scratch of coord_hash_capacity(rows),
+ * native/features/coordinates/relations.cpp:95-105 and :555, inserted by
+ * coordinates/metal/hash.metal:7-41) as a buffer the caller may keep:
+ * lat_build_coord_table fills `table` (32-byte aligned, lat_coord_table_bytes(rows)
+ * bytes) from coords [rows, 4] and active_rows [1]. A builder that takes
+ * `source_table` accepts such a buffer made from the same (coords, rows,
+ * active_rows) and skips its own table build; NULL builds one in the workspace.
+ * One coordinate set usually feeds several builders (submanifold, strided,
+ * transposed). The buffer's layout is private to the library. */
+size_t lat_coord_table_bytes(int32_t rows);
+int lat_build_coord_table(
+    const int32_t* coords, int32_t rows, const int32_t* active_rows,
+    void* table, size_t table_bytes, int32_t* status, void* stream);
+
 /* native/bindings/coords.cpp:414-479 (`build_kernel_relation`) ->
  * make_kernel_relation, native/features/coordinates/relations.cpp:540-581;
  * algorithm native/features/coordinates/cpu/relation_build_detail.h:3-41.
@@ -99,6 +114,7 @@ int lat_build_kernel_relation(
     int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
     int32_t* out_coords, int32_t* counts,
     int32_t* row_masks, int32_t* kernel_row_offsets, int32_t* kernel_edge_ids,
+    const void* source_table /* optional, lat_build_coord_table of `coords` */,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
 /* native/bindings/coords.cpp:480-508 (`build_submanifold_kernel_relation`) ->
@@ -110,6 +126,7 @@ int lat_build_submanifold_kernel_relation(
     int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
     int32_t* out_coords, int32_t* counts,
     int32_t* row_masks, int32_t* kernel_row_offsets, int32_t* kernel_edge_ids,
+    const void* source_table /* optional, lat_build_coord_table of `coords` */,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
 /* native/bindings/coords.cpp:546-589 (`build_target_kernel_relation`) ->
@@ -160,6 +177,7 @@ int lat_build_target_transposed_relation(
     lat_triple stride,
     int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
     int32_t* counts, int32_t* row_masks /* optional [target_rows, 1] */,
+    const void* source_table /* optional, lat_build_coord_table of `coords` */,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
 /* relations.cpp:438-459 (`make_relation_grouped_view`), algorithm

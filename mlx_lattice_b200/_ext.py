@@ -202,12 +202,31 @@ def _views(in_rows, kernel_ids, counts, in_capacity: int, kernel_count: int):
     return in_offsets, in_edges, k_offsets, k_edges
 
 
+def build_coord_table(coords, active_rows):
+    """First-row-wins coordinate table of ``coords`` as an opaque device buffer that the
+    builders taking ``source_table`` accept in place of building their own (the reference's
+    GPU builders fill one per call, ``native/features/coordinates/relations.cpp:555``)."""
+    coords = _coords_arg(coords)
+    active_rows = _active_arg(active_rows)
+    rows = int(coords.shape[0])
+    device = coords.device
+    lib = _lib()
+    table = _workspace(lib.lat_coord_table_bytes(rows), device)
+    with torch.cuda.device(device):
+        check(lib.lat_build_coord_table(
+            _ptr(coords), rows, _ptr(active_rows), _ptr(table), table.numel(),
+            _ptr(status_word(device)), _stream(),
+        ))
+    return table
+
+
 def build_kernel_relation_base(
     coords, active_rows, kernel_size, stride, padding, dilation, *,
-    want_masks=False, want_kernel_lists=False,
+    want_masks=False, want_kernel_lists=False, source_table=None,
 ):
     """The six contract arrays of a forward relation plus, on request, the row
-    masks and the per-offset pair lists produced in the same pass."""
+    masks and the per-offset pair lists produced in the same pass. ``source_table``
+    is an optional ``build_coord_table(coords, active_rows)``."""
     coords = _coords_arg(coords)
     active_rows = _active_arg(active_rows)
     ks = _triple(kernel_size)
@@ -231,7 +250,8 @@ def build_kernel_relation_base(
             _ptr(coords), rows, _ptr(active_rows), ks, _triple(stride), _triple(padding),
             _triple(dilation), _ptr(in_rows), _ptr(out_rows), _ptr(kernel_ids),
             _ptr(row_offsets), _ptr(out_coords), _ptr(counts), _ptr(masks), _ptr(k_offsets),
-            _ptr(k_edges), _ptr(ws), ws.numel(), _ptr(status_word(device)), _stream(),
+            _ptr(k_edges), _ptr(source_table), _ptr(ws), ws.numel(),
+            _ptr(status_word(device)), _stream(),
         ))
     return (in_rows, out_rows, kernel_ids, row_offsets, out_coords, counts), masks, (k_offsets, k_edges)
 
@@ -363,7 +383,8 @@ def build_generative_relation(coords, active_rows, kernel_size, stride):
 
 
 def build_target_transposed_relation_base(
-    coords, active_rows, target_coords, target_active_rows, stride, *, want_masks=False
+    coords, active_rows, target_coords, target_active_rows, stride, *, want_masks=False,
+    source_table=None,
 ):
     """Transposed map of a ``kernel_size == stride`` conv restricted to a given
     fine support (one edge per target row at most); see ``include/lattice_b200.h``."""
@@ -386,8 +407,8 @@ def build_target_transposed_relation_base(
         check(lib.lat_build_target_transposed_relation(
             _ptr(coords), rows, _ptr(active_rows), _ptr(target), target_rows,
             _ptr(target_active), step, _ptr(in_rows), _ptr(out_rows),
-            _ptr(kernel_ids), _ptr(row_offsets), _ptr(counts), _ptr(masks), _ptr(ws), ws.numel(),
-            _ptr(status_word(device)), _stream(),
+            _ptr(kernel_ids), _ptr(row_offsets), _ptr(counts), _ptr(masks), _ptr(source_table),
+            _ptr(ws), ws.numel(), _ptr(status_word(device)), _stream(),
         ))
     if want_masks:
         return (in_rows, out_rows, kernel_ids, row_offsets, target, counts), masks

@@ -47,10 +47,12 @@ SIGNATURES = {
     'lat_capabilities': (I, [POINTER(c_int32), POINTER(c_int32)]),
     'lat_kernel_offsets_host': (I, [Triple, Triple, P]),
     'lat_relation_workspace_bytes': (c_size_t, [I, I, I]),
+    'lat_coord_table_bytes': (c_size_t, [I]),
+    'lat_build_coord_table': (I, [P, I, P, P, c_size_t, P, P]),
     'lat_build_kernel_relation': (
-        I, [P, I, P, Triple, Triple, Triple, Triple, P, P, P, P, P, P, P, P, P, P, c_size_t, P, P]),
+        I, [P, I, P, Triple, Triple, Triple, Triple, P, P, P, P, P, P, P, P, P, P, P, c_size_t, P, P]),
     'lat_build_submanifold_kernel_relation': (
-        I, [P, I, P, Triple, Triple, P, P, P, P, P, P, P, P, P, P, c_size_t, P, P]),
+        I, [P, I, P, Triple, Triple, P, P, P, P, P, P, P, P, P, P, P, c_size_t, P, P]),
     'lat_build_target_kernel_relation': (
         I, [P, I, P, P, I, P, Triple, Triple, Triple, Triple, P, P, P, P, P, P, P, P, P,
             c_size_t, P, P]),
@@ -59,7 +61,7 @@ SIGNATURES = {
     'lat_build_generative_relation': (
         I, [P, I, P, Triple, Triple, P, P, P, P, P, P, P, c_size_t, P, P]),
     'lat_build_target_transposed_relation': (
-        I, [P, I, P, P, I, P, Triple, P, P, P, P, P, P, P, c_size_t, P, P]),
+        I, [P, I, P, P, I, P, Triple, P, P, P, P, P, P, P, P, c_size_t, P, P]),
     'lat_grouped_view_workspace_bytes': (c_size_t, [I, I]),
     'lat_build_relation_grouped_view': (I, [P, I, P, I, P, P, P, c_size_t, P, P]),
     'lat_implicit_gemm_view_workspace_bytes': (c_size_t, [I]),

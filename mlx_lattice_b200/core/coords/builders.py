@@ -82,15 +82,18 @@ def build_kernel_relation(
     stride: int | Sequence[int] = 1,
     padding: int | Sequence[int] = 0,
     dilation: int | Sequence[int] = 1,
+    *,
+    source_table: torch.Tensor | None = None,
 ) -> KernelRelation:
-    """Forward sparse convolution / pooling relation (``builders.py:156-191``)."""
+    """Forward sparse convolution / pooling relation (``builders.py:156-191``).
+    ``source_table`` is an optional ``_ext.build_coord_table(coords, active_rows)``."""
     validate_coords(coords)
     spec = KernelSpec(size=kernel_size, stride=stride, padding=padding, dilation=dilation)
     offsets = kernel_offsets(spec.size, spec.dilation)
     source_active = _active_rows(active_rows, coords)
     base, masks, lists = _ext.build_kernel_relation_base(
         coords, source_active, spec.size, spec.stride, spec.padding, spec.dilation,
-        want_masks=True, want_kernel_lists=False,
+        want_masks=True, want_kernel_lists=False, source_table=source_table,
     )
     return _relation(
         base, masks, lists,
@@ -109,8 +112,11 @@ def build_submanifold_kernel_relation(
     active_rows: torch.Tensor | None = None,
     kernel_size: int | Sequence[int] = 3,
     dilation: int | Sequence[int] = 1,
+    *,
+    source_table: torch.Tensor | None = None,
 ) -> KernelRelation:
-    """Submanifold relation whose output support is ``coords`` (``builders.py:194-233``)."""
+    """Submanifold relation whose output support is ``coords`` (``builders.py:194-233``).
+    ``source_table`` is an optional ``_ext.build_coord_table(coords, active_rows)``."""
     validate_coords(coords)
     spec = KernelSpec(size=kernel_size, stride=1, padding=0, dilation=dilation)
     if not all(value % 2 == 1 for value in spec.size):
@@ -122,7 +128,7 @@ def build_submanifold_kernel_relation(
     source_active = _active_rows(active_rows, coords)
     base, masks, lists = _ext.build_kernel_relation_base(
         coords, source_active, spec.size, spec.stride, spec.padding, spec.dilation,
-        want_masks=True, want_kernel_lists=False,
+        want_masks=True, want_kernel_lists=False, source_table=source_table,
     )
     return _relation(
         base, masks, lists,
@@ -246,6 +252,7 @@ def build_target_transposed_relation(
     active_rows: torch.Tensor | None = None,
     target_active_rows: torch.Tensor | None = None,
     stride: int | Sequence[int] = 2,
+    source_table: torch.Tensor | None = None,
 ) -> KernelRelation:
     """Transposed relation of a ``kernel_size == stride`` conv restricted to a given
     fine support. Equals ``conv_transpose3d`` followed by a right-join alignment to
@@ -258,7 +265,8 @@ def build_target_transposed_relation(
     source_active = _active_rows(active_rows, coords)
     target_active = _active_rows(target_active_rows, target_coords)
     base, masks = _ext.build_target_transposed_relation_base(
-        coords, source_active, target_coords, target_active, step, want_masks=True
+        coords, source_active, target_coords, target_active, step, want_masks=True,
+        source_table=source_table,
     )
     return _relation(
         base, masks, None,

@@ -8,6 +8,7 @@ from itertools import count
 
 import torch
 
+from mlx_lattice_b200 import _ext
 from mlx_lattice_b200.core.coords.builders import (
     build_generative_relation,
     build_kernel_relation,
@@ -44,6 +45,7 @@ class CoordinateManager:
     _default_identity_keys: dict = field(default_factory=dict)
     _active_rows: dict = field(default_factory=dict)
     _kernel_relations: dict = field(default_factory=dict)
+    _coord_tables: dict = field(default_factory=dict)
 
     def insert_coords(
         self,
@@ -86,6 +88,15 @@ class CoordinateManager:
             raise ValueError('coordinate key does not belong to this manager.')
         return self._active_rows[key]
 
+    def coord_table(self, key: CoordinateMapKey) -> torch.Tensor:
+        """The first-row coordinate table of a key, built once and handed to every
+        builder that starts from these coordinates (submanifold, strided, transposed)."""
+        if key not in self._coord_tables:
+            self._coord_tables[key] = _ext.build_coord_table(
+                self.coords(key), self.active_rows(key)
+            )
+        return self._coord_tables[key]
+
     def _cached(self, cache_key, build) -> KernelRelation:
         if cache_key not in self._kernel_relations:
             self._kernel_relations[cache_key] = build()
@@ -104,6 +115,7 @@ class CoordinateManager:
                 stride=spec.stride,
                 padding=spec.padding,
                 dilation=spec.dilation,
+                source_table=self.coord_table(key),
             ),
         )
 
@@ -116,6 +128,7 @@ class CoordinateManager:
                 active_rows=self.active_rows(key),
                 kernel_size=spec.size,
                 dilation=spec.dilation,
+                source_table=self.coord_table(key),
             ),
         )
 
@@ -180,5 +193,6 @@ class CoordinateManager:
                 active_rows=self.active_rows(key),
                 target_active_rows=self.active_rows(target_key),
                 stride=spec.stride,
+                source_table=self.coord_table(key),
             ),
         )

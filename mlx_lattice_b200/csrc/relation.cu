@@ -1345,6 +1345,23 @@ int build_source_table(
     return LAT_OK;
 }
 
+// the first-row table of `coords`: the caller's prebuilt one (lat_build_coord_table over the
+// same coords / active_rows) or a fresh one in the workspace
+int acquire_source_table(
+    Workspace& ws, const int32_t* coords, int rows, const int32_t* active_rows, int32_t* status,
+    cudaStream_t stream, const void* prebuilt, SourceTable& table
+) {
+    if (prebuilt == nullptr) {
+        return build_source_table(ws, coords, rows, active_rows, status, false, stream, table);
+    }
+    if (reinterpret_cast<uintptr_t>(prebuilt) % 32 != 0) {
+        return fail(LAT_INVALID_ARGUMENT, "source_table must be a 32-byte aligned device buffer.");
+    }
+    table.slots = const_cast<Slot*>(static_cast<const Slot*>(prebuilt));
+    table.mask = static_cast<uint32_t>(table_slots(rows) - 1);
+    return LAT_OK;
+}
+
 struct MapOutputs {
     int32_t* in_rows;
     int32_t* out_rows;
@@ -1510,12 +1527,31 @@ static int validate_relation_args(
     return LAT_OK;
 }
 
+size_t lat_coord_table_bytes(int32_t rows) {
+    return align_up(sizeof(Slot) * static_cast<size_t>(table_slots(std::max(rows, 1))));
+}
+
+int lat_build_coord_table(
+    const int32_t* coords, int32_t rows, const int32_t* active_rows,
+    void* table, size_t table_bytes, int32_t* status, void* stream_ptr
+) {
+    LAT_REQUIRE(rows >= 0 && (coords != nullptr || rows == 0), "coords must have shape (N, 4).");
+    LAT_REQUIRE(active_rows != nullptr, "active_rows must have shape (1,) and int32 dtype.");
+    LAT_REQUIRE(table != nullptr && reinterpret_cast<uintptr_t>(table) % 32 == 0,
+                "table must be a 32-byte aligned device buffer.");
+    LAT_REQUIRE(table_bytes >= lat_coord_table_bytes(rows), "table is smaller than lat_coord_table_bytes.");
+    Workspace ws(table, table_bytes);
+    SourceTable built;
+    return build_source_table(ws, coords, rows, active_rows, status, false, as_stream(stream_ptr), built);
+}
+
 int lat_build_kernel_relation(
     const int32_t* coords, int32_t rows, const int32_t* active_rows,
     lat_triple kernel_size, lat_triple stride, lat_triple padding, lat_triple dilation,
     int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
     int32_t* out_coords, int32_t* counts,
     int32_t* row_masks, int32_t* kernel_row_offsets, int32_t* kernel_edge_ids,
+    const void* source_table,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream_ptr
 ) {
     int rc = validate_relation_args(coords, rows, active_rows, kernel_size, stride, padding, dilation);
@@ -1536,7 +1572,7 @@ int lat_build_kernel_relation(
         return LAT_OK;
     }
     SourceTable table;
-    rc = build_source_table(ws, coords, rows, active_rows, status, false, stream, table);
+    rc = acquire_source_table(ws, coords, rows, active_rows, status, stream, source_table, table);
     if (rc != LAT_OK) {
         return rc;
     }
@@ -1587,12 +1623,13 @@ int lat_build_submanifold_kernel_relation(
     int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
     int32_t* out_coords, int32_t* counts,
     int32_t* row_masks, int32_t* kernel_row_offsets, int32_t* kernel_edge_ids,
+    const void* source_table,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream
 ) {
     return lat_build_kernel_relation(
         coords, rows, active_rows, kernel_size, {1, 1, 1}, {0, 0, 0}, dilation, in_rows,
         out_rows, kernel_ids, row_offsets, out_coords, counts, row_masks, kernel_row_offsets,
-        kernel_edge_ids, workspace, workspace_bytes, status, stream);
+        kernel_edge_ids, source_table, workspace, workspace_bytes, status, stream);
 }
 
 int lat_build_target_kernel_relation(
@@ -1777,7 +1814,7 @@ int lat_build_target_transposed_relation(
     const int32_t* target_coords, int32_t target_rows, const int32_t* target_active_rows,
     lat_triple stride,
     int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
-    int32_t* counts, int32_t* row_masks,
+    int32_t* counts, int32_t* row_masks, const void* source_table,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream_ptr
 ) {
     int rc = validate_relation_args(coords, rows, active_rows, stride, stride, {0, 0, 0}, {1, 1, 1});
@@ -1794,7 +1831,7 @@ int lat_build_target_transposed_relation(
     cudaStream_t stream = as_stream(stream_ptr);
     Workspace ws(workspace, workspace_bytes);
     SourceTable table;
-    rc = build_source_table(ws, coords, rows, active_rows, status, false, stream, table);
+    rc = acquire_source_table(ws, coords, rows, active_rows, status, stream, source_table, table);
     if (rc != LAT_OK) {
         return rc;
     }

@@ -207,6 +207,49 @@ def test_target_transposed_equals_reference_composition(cuda, oracle):
     assert np.array_equal(row_offsets, np.arange(fine.shape[0] + 1))
 
 
+def test_prebuilt_coord_table_gives_the_same_relations(cuda, oracle):
+    """One coordinate table shared by the submanifold, strided and target-transposed
+    builders (what the coordinate manager does) against the oracle and against the
+    builders run with their own tables; duplicates and truncated active rows included."""
+    from mlx_lattice_b200 import _ext
+
+    cases = [('duplicates', None), ('sphere', 4000), ('lidar', None), ('negative', 1)]
+    for name, active in cases:
+        coords = CLOUDS[name]
+        n_active = coords.shape[0] if active is None else active
+        dev, act = _dev(coords, cuda), _active(n_active, cuda)
+        table = _ext.build_coord_table(dev, act)
+        for stride in (1, 2):
+            shared, masks_shared, _ = _ext.build_kernel_relation_base(
+                dev, act, 3, stride, 0, 1, want_masks=True, source_table=table)
+            own, masks_own, _ = _ext.build_kernel_relation_base(
+                dev, act, 3, stride, 0, 1, want_masks=True)
+            want = oracle.build_kernel_relation(coords, n_active, kernel_size=3, stride=stride)
+            edges, n_out = shared[5].tolist()
+            assert [edges, n_out] == want['counts'].tolist()
+            for got_arr, own_arr, key in zip(shared, own, ALL_KEYS):
+                assert torch.equal(got_arr, own_arr), key
+                assert np.array_equal(got_arr.cpu().numpy(), want[key]), key
+            assert torch.equal(masks_shared[:n_out], masks_own[:n_out])
+    _ext.check_status()
+    # the coarse level's table serves the map back onto the fine support
+    fine = CLOUDS['sphere']
+    down = _ext.build_kernel_relation_base(_dev(fine, cuda), _active(fine.shape[0], cuda), 2, 2, 0, 1)[0]
+    n_coarse = int(down[5][1])
+    coarse, coarse_act = down[4], _active(n_coarse, cuda)
+    table = _ext.build_coord_table(coarse, coarse_act)
+    args = (coarse, coarse_act, _dev(fine, cuda), _active(fine.shape[0], cuda), 2)
+    shared = _ext.build_target_transposed_relation_base(*args, source_table=table)
+    own = _ext.build_target_transposed_relation_base(*args)
+    for a, b in zip(shared, own):
+        assert torch.equal(a, b)
+    _ext.check_status()
+    with pytest.raises(ValueError):
+        _ext.build_kernel_relation_base(
+            _dev(fine, cuda), _active(fine.shape[0], cuda), 3, 1, 0, 1,
+            source_table=table[8:])
+
+
 def test_grouped_views_and_igemm_view(cuda, oracle, restatement):
     from mlx_lattice_b200 import _ext
 

@@ -16,7 +16,7 @@ __all__ = [
 ]
 
 
-def pool3d(x: SparseTensor, *, mode='sum', kernel_size=2, stride=2, padding=0, dilation=1):
+def pool3d(x: SparseTensor, *, mode='sum', kernel_size=2, stride=2, padding=0, dilation=1) -> SparseTensor:
     """Local sparse pooling over a forward kernel relation; float32 features only,
     like the reference (``ops/pool.py:27-54,155-191``)."""
     spec = KernelSpec(size=kernel_size, stride=stride, padding=padding, dilation=dilation)
@@ -42,15 +42,15 @@ def pool3d(x: SparseTensor, *, mode='sum', kernel_size=2, stride=2, padding=0, d
     )
 
 
-def sum_pool3d(x, *, kernel_size=2, stride=2, padding=0, dilation=1):
+def sum_pool3d(x: SparseTensor, *, kernel_size=2, stride=2, padding=0, dilation=1) -> SparseTensor:
     return pool3d(x, mode='sum', kernel_size=kernel_size, stride=stride, padding=padding, dilation=dilation)
 
 
-def max_pool3d(x, *, kernel_size=2, stride=2, padding=0, dilation=1):
+def max_pool3d(x: SparseTensor, *, kernel_size=2, stride=2, padding=0, dilation=1) -> SparseTensor:
     return pool3d(x, mode='max', kernel_size=kernel_size, stride=stride, padding=padding, dilation=dilation)
 
 
-def avg_pool3d(x, *, kernel_size=2, stride=2, padding=0, dilation=1):
+def avg_pool3d(x: SparseTensor, *, kernel_size=2, stride=2, padding=0, dilation=1) -> SparseTensor:
     return pool3d(x, mode='avg', kernel_size=kernel_size, stride=stride, padding=padding, dilation=dilation)
 
 

@@ -13,7 +13,9 @@ from mlx_lattice_b200.core.types import triple
 __all__ = ['sparse_cat_aligned', 'sparse_collate']
 
 
-def sparse_collate(coords: Sequence[torch.Tensor], feats: Sequence[torch.Tensor], *, stride=1):
+def sparse_collate(
+    coords: Sequence[torch.Tensor], feats: Sequence[torch.Tensor], *, stride=1
+) -> SparseTensor:
     """Collate unbatched ``(N_i, 3)`` coords / ``(N_i, C)`` feats into one tensor
     with a prepended batch column and ``batch_counts`` metadata."""
     if len(coords) != len(feats):

@@ -93,6 +93,44 @@ class MinkUNet:
         return ops.linear(cur, w['head'])
 
 
+def minkunet_artifact(quantized: dict[str, QuantizedWeight], *, target_support: bool = True):
+    """The network above as a lattice artifact: ``(manifest, weights)`` for
+    ``artifact.save_lattice_artifact`` / ``artifact.LatticeModel``. With
+    ``target_support`` the transposed convolutions name the encoder tensor they upsample
+    onto (one edge per fine voxel); without it the decoder takes the reference's form, a
+    plain transposed convolution followed by a right-join concatenation."""
+    from mlx_lattice_b200.artifact import GraphWriter
+
+    g = GraphWriter({'input': 'sparse_tensor'}, producer={'name': 'mlx-lattice-b200-workloads'})
+    k3 = {'kernel_size': (3, 3, 3)}
+    k2 = {'kernel_size': (2, 2, 2), 'stride': (2, 2, 2)}
+
+    def conv(op, name, source, attributes):
+        return g.add(f'sparse.quantized_{op}', {'input': source}, node_id=name,
+                     parameters={'weight': quantized[name]}, attributes=attributes)
+
+    cur = conv('subm_conv3d', 'stem', 'input', k3)
+    skips = [cur]
+    stages = len(ENCODER_CHANNELS)
+    for i in range(1, stages + 1):
+        cur = conv('conv3d', f'down{i}', cur, k2)
+        cur = conv('subm_conv3d', f'enc{i}a', cur, k3)
+        cur = conv('subm_conv3d', f'enc{i}b', cur, k3)
+        if i < stages:
+            skips.append(cur)
+    for i in range(stages, 0, -1):
+        skip = skips[i - 1]
+        cur = conv('conv_transpose3d', f'up{i}', cur,
+                   {**k2, 'coordinates': skip} if target_support else k2)
+        cur = g.add('ops.sparse_cat_aligned', {'lhs': cur, 'rhs': skip}, node_id=f'cat{i}',
+                    attributes={'join': 'right'})
+        cur = conv('subm_conv3d', f'dec{i}a', cur, k3)
+        cur = conv('subm_conv3d', f'dec{i}b', cur, k3)
+    g.add('feature.quantized_linear', {'input': cur}, node_id='head', output='logits',
+          parameters={'weight': quantized['head']})
+    return g.manifest({'logits': 'sparse_tensor'}), g.weights
+
+
 def minkunet_inputs(config_index: int, batch: int, per_cloud: int, first_batch: int = 0):
     """LiDAR-like coords (N, 4) int32 and xyz+intensity ~ U(0,1) fp16 features (N, 4)."""
     coords = synthetic.lidar_batch(config_index, batch, per_cloud, first_batch=first_batch)

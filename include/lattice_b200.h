@@ -416,6 +416,26 @@ int lat_batch_norm_relu(
 /* feature.py:54-56 (`relu`). */
 int lat_relu(int32_t dtype, const void* feats, int64_t elements, void* out, void* stream);
 
+/* Channel concatenation of two feature matrices read through row maps
+ * (mlx_lattice/ops/tensor.py:228-249 `sparse_cat_aligned`, which gathers each side with
+ * `gather_aligned_features`, tensor.py:89-109, and concatenates): out [rows_out,
+ * lhs_channels + rhs_channels]; row r takes lhs[lhs_rows[r]] and rhs[rhs_rows[r]], zeros
+ * where the map holds -1. A NULL map is the identity (tensors that share coordinates).
+ * element_bytes = 2 or 4. */
+int lat_concat_aligned_features(
+    int32_t element_bytes, const void* lhs, const int32_t* lhs_rows, int32_t lhs_capacity,
+    int32_t lhs_channels, const void* rhs, const int32_t* rhs_rows, int32_t rhs_capacity,
+    int32_t rhs_channels, int64_t rows_out, void* out, int32_t* status, void* stream);
+
+/* tensor.py:112-147 (`sparse_binary_op`) after the alignment is known: out[r] =
+ * op(lhs[lhs_rows[r]] or lhs_fill, rhs[rhs_rows[r]] or rhs_fill), evaluated in the
+ * element type; op: 0 add, 1 sub, 2 mul, 3 maximum, 4 minimum (tensor.py:285-296).
+ * NULL maps are the identity. */
+int lat_binary_aligned_features(
+    int32_t dtype, int32_t op, const void* lhs, const int32_t* lhs_rows, int32_t lhs_capacity,
+    float lhs_fill, const void* rhs, const int32_t* rhs_rows, int32_t rhs_capacity, float rhs_fill,
+    int64_t rows_out, int32_t channels, void* out, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -959,3 +959,62 @@ def relu(feats):
             _dtype_code(feats.dtype), _ptr(feats), feats.numel(), _ptr(out), _stream()
         ))
     return out
+
+
+# --------------------------------------------------------------------------- #
+# features through an alignment (mlx_lattice/ops/tensor.py:89-147, :228-249)
+# --------------------------------------------------------------------------- #
+
+_BINARY_OPS = {'add': 0, 'sub': 1, 'mul': 2, 'maximum': 3, 'minimum': 4}
+
+
+def _aligned_pair(lhs, lhs_rows, rhs, rhs_rows):
+    lhs, _ = _feats_arg(lhs)
+    rhs, _ = _feats_arg(rhs)
+    lhs, rhs = lhs.contiguous(), rhs.contiguous()
+    if lhs.dtype != rhs.dtype:
+        raise ValueError('sparse tensors must have matching feature dtype.')
+    if (lhs_rows is None) != (rhs_rows is None):
+        raise ValueError('row maps must be given for both sides or for neither.')
+    if lhs_rows is None:
+        if lhs.shape[0] != rhs.shape[0]:
+            raise ValueError('tensors that share coordinates must have the same number of rows.')
+        rows_out = int(lhs.shape[0])
+    else:
+        lhs_rows, rhs_rows = _i32(lhs_rows, 'lhs_rows'), _i32(rhs_rows, 'rhs_rows')
+        if lhs_rows.ndim != 1 or lhs_rows.shape != rhs_rows.shape:
+            raise ValueError('rows must have shape (N,) and int32 dtype.')
+        rows_out = int(lhs_rows.shape[0])
+    return lhs, lhs_rows, rhs, rhs_rows, rows_out
+
+
+def concat_aligned_features(lhs, lhs_rows, rhs, rhs_rows):
+    """``[lhs[lhs_rows] | rhs[rhs_rows]]`` along the channels, zero rows where a map holds
+    -1; ``None`` maps mean the two matrices already share their rows."""
+    lhs, lhs_rows, rhs, rhs_rows, rows_out = _aligned_pair(lhs, lhs_rows, rhs, rhs_rows)
+    channels = int(lhs.shape[1]) + int(rhs.shape[1])
+    out = torch.empty((rows_out, channels), dtype=lhs.dtype, device=lhs.device)
+    with torch.cuda.device(lhs.device):
+        check(_lib().lat_concat_aligned_features(
+            lhs.element_size(), _ptr(lhs), _ptr(lhs_rows), int(lhs.shape[0]), int(lhs.shape[1]),
+            _ptr(rhs), _ptr(rhs_rows), int(rhs.shape[0]), int(rhs.shape[1]), rows_out, _ptr(out),
+            _ptr(status_word(lhs.device)), _stream(),
+        ))
+    return out
+
+
+def binary_aligned_features(lhs, lhs_rows, rhs, rhs_rows, op: str, lhs_fill=0.0, rhs_fill=0.0):
+    """``op(lhs[lhs_rows] or lhs_fill, rhs[rhs_rows] or rhs_fill)`` row by row."""
+    if op not in _BINARY_OPS:
+        raise ValueError(f'unknown sparse binary op: {op}.')
+    lhs, lhs_rows, rhs, rhs_rows, rows_out = _aligned_pair(lhs, lhs_rows, rhs, rhs_rows)
+    if lhs.shape[1] != rhs.shape[1]:
+        raise ValueError('sparse binary operands must have matching channels.')
+    out = torch.empty((rows_out, int(lhs.shape[1])), dtype=lhs.dtype, device=lhs.device)
+    with torch.cuda.device(lhs.device):
+        check(_lib().lat_binary_aligned_features(
+            _dtype_code(lhs.dtype), _BINARY_OPS[op], _ptr(lhs), _ptr(lhs_rows), int(lhs.shape[0]),
+            float(lhs_fill), _ptr(rhs), _ptr(rhs_rows), int(rhs.shape[0]), float(rhs_fill),
+            rows_out, int(lhs.shape[1]), _ptr(out), _ptr(status_word(lhs.device)), _stream(),
+        ))
+    return out

@@ -18,6 +18,7 @@ import torch
 from mlx_lattice_b200 import _ext
 from mlx_lattice_b200.artifact.manifest import IRNode
 from mlx_lattice_b200.core import QuantizedWeight, SparseTensor
+from mlx_lattice_b200.core.coords.alignment import SparseAlignment
 from mlx_lattice_b200.core.coords.quantization import PointVoxelMap, SparseQuantization
 from mlx_lattice_b200.core.relations import KernelRelation
 
@@ -30,6 +31,9 @@ _VALUE_TYPES: dict[str, tuple[Any, str, dict[str, str]]] = {
     'sparse_tensor': (SparseTensor, 'SparseTensor', {}),
     'dense_tensor': (torch.Tensor, 'a dense tensor', {}),
     'relation': (KernelRelation, 'KernelRelation', {}),
+    'alignment': (SparseAlignment, 'SparseAlignment', {
+        'coords': 'dense_tensor', 'active_rows': 'dense_tensor',
+        'lhs_rows': 'dense_tensor', 'rhs_rows': 'dense_tensor'}),
     'quantization': (SparseQuantization, 'SparseQuantization', {
         'coords': 'dense_tensor', 'active_rows': 'dense_tensor',
         'inverse_rows': 'dense_tensor', 'counts': 'dense_tensor'}),

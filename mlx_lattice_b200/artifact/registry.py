@@ -29,6 +29,7 @@ from mlx_lattice_b200.artifact.manifest import IRNode
 # annotation fragment -> IR value type (annotations are strings in this package)
 _ANNOTATION_TYPES = (
     ('SparseTensor', 'sparse_tensor'),
+    ('SparseAlignment', 'alignment'),
     ('KernelRelation', 'relation'),
     ('PointVoxelMap', 'point_voxel_map'),
     ('SparseQuantization', 'quantization'),
@@ -200,6 +201,12 @@ def _register_all() -> None:
         _semantic(f'sparse.{prefix}generative_conv_transpose3d', 'generative_conv_transpose3d',
                   weight=weight, bias=True, attributes=('kernel_size', 'stride'))
         _semantic(f'feature.{prefix}linear', 'linear', weight=weight, bias=True)
+    add = public_ops()['sparse_add']
+    register(OperationBinding(
+        name='sparse.add', function=add, inputs={'lhs': 'lhs', 'rhs': 'rhs'},
+        attributes={'join': 'join'}, input_types={'lhs': 'sparse_tensor', 'rhs': 'sparse_tensor'},
+        output_type=_return_type(add),
+    ))
     _semantic('feature.relu', 'relu')
     _semantic('feature.batch_norm', 'batch_norm', optional=('weight', 'bias', 'mean', 'var'),
               attributes=('eps', 'fuse_relu'))

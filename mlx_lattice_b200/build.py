@@ -25,7 +25,7 @@ SOURCES = (
     'voxelize.cu',
     'static_scratch.cu',
     'pool.cu',
-    'feature.cu',
+    'feature.cu', 'align.cu',
     'capi.cu',
 )
 

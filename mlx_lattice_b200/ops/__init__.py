@@ -31,9 +31,21 @@ from mlx_lattice_b200.ops.quantization import (
     voxelize,
     voxelize_with_quantization,
 )
-from mlx_lattice_b200.ops.tensor import sparse_cat_aligned, sparse_collate
+from mlx_lattice_b200.ops.tensor import (
+    align_sparse,
+    sparse_add,
+    sparse_binary_op,
+    sparse_cat_aligned,
+    sparse_collate,
+    sparse_maximum,
+    sparse_minimum,
+    sparse_mul,
+    sparse_sub,
+)
 
 __all__ = [
+    'align_sparse', 'sparse_add', 'sparse_binary_op', 'sparse_maximum', 'sparse_minimum', 'sparse_mul',
+    'sparse_sub',
     'avg_pool3d', 'batch_norm', 'build_generative_relation', 'build_point_voxel_map', 'devoxelize',
     'interpolate_point_features', 'build_kernel_relation',
     'build_submanifold_kernel_relation', 'build_target_kernel_relation',

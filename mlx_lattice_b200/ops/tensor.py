@@ -7,6 +7,7 @@ from collections.abc import Sequence
 import torch
 
 from mlx_lattice_b200 import _ext
+from mlx_lattice_b200.core.coords.alignment import SparseAlignment
 from mlx_lattice_b200.core.tensor import SparseTensor
 from mlx_lattice_b200.core.types import triple
 
@@ -46,27 +47,80 @@ def sparse_collate(
     )
 
 
-def _gather_aligned(feats: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
-    gathered = feats.index_select(0, rows.clamp(min=0).long())
-    return gathered * (rows >= 0).to(feats.dtype)[:, None]
+def _require_compatible(lhs: SparseTensor, rhs: SparseTensor) -> None:
+    if lhs.stride != rhs.stride:
+        raise ValueError('sparse tensor strides must match.')
+    if lhs.coords.dtype != rhs.coords.dtype:
+        raise ValueError('sparse tensor coordinate dtypes must match.')
+
+
+def align_sparse(lhs: SparseTensor, rhs: SparseTensor, *, join: str = 'inner') -> SparseAlignment:
+    """Coordinate-value alignment of two sparse tensors (``ops/tensor.py:67-86``): the joined
+    support and, per joined row, the row of each operand (-1 where it has none)."""
+    _require_compatible(lhs, rhs)
+    coords, active, lhs_rows, rhs_rows = _ext.build_sparse_alignment(
+        lhs.coords, lhs.active_rows, rhs.coords, rhs.active_rows, join
+    )
+    return SparseAlignment(coords, active, lhs_rows, rhs_rows)
 
 
 def sparse_cat_aligned(lhs: SparseTensor, rhs: SparseTensor, *, join: str = 'inner') -> SparseTensor:
     """Concatenate the channels of two sparse tensors after coordinate-value
-    alignment; tensors that share coordinate identity are concatenated directly."""
-    if lhs.stride != rhs.stride:
-        raise ValueError('sparse tensors must have matching stride.')
-    if lhs.coords.dtype != rhs.coords.dtype:
-        raise ValueError('sparse tensors must have matching coordinate dtype.')
+    alignment; tensors that share coordinate identity are concatenated directly
+    (``ops/tensor.py:228-249``). One gather-and-concatenate kernel either way."""
+    _require_compatible(lhs, rhs)
     if lhs.same_coords(rhs):
-        return lhs.replace(feats=torch.cat([lhs.feats, rhs.feats], dim=1))
-    coords, active, lhs_rows, rhs_rows = _ext.build_sparse_alignment(
-        lhs.coords, lhs.active_rows, rhs.coords, rhs.active_rows, join
-    )
+        return lhs.replace(feats=_ext.concat_aligned_features(lhs.feats, None, rhs.feats, None))
+    alignment = align_sparse(lhs, rhs, join=join)
     return SparseTensor(
-        coords,
-        torch.cat([_gather_aligned(lhs.feats, lhs_rows), _gather_aligned(rhs.feats, rhs_rows)], dim=1),
+        alignment.coords,
+        _ext.concat_aligned_features(lhs.feats, alignment.lhs_rows, rhs.feats, alignment.rhs_rows),
         lhs.stride,
         coord_manager=lhs.coord_manager,
-        active_rows=active,
+        active_rows=alignment.active_rows,
     )
+
+
+def sparse_binary_op(
+    lhs: SparseTensor, rhs: SparseTensor, op: str, *, join: str = 'outer',
+    lhs_fill: float = 0.0, rhs_fill: float = 0.0,
+) -> SparseTensor:
+    """Elementwise ``add / sub / mul / maximum / minimum`` after coordinate-value alignment
+    (``ops/tensor.py:112-147``); rows one operand lacks take its fill value. Operands that
+    share coordinate identity are combined row by row without an alignment."""
+    _require_compatible(lhs, rhs)
+    if lhs.channels != rhs.channels:
+        raise ValueError('sparse binary operands must have matching channels.')
+    if lhs.same_coords(rhs):
+        return lhs.replace(feats=_ext.binary_aligned_features(lhs.feats, None, rhs.feats, None, op))
+    alignment = align_sparse(lhs, rhs, join=join)
+    return SparseTensor(
+        alignment.coords,
+        _ext.binary_aligned_features(
+            lhs.feats, alignment.lhs_rows, rhs.feats, alignment.rhs_rows, op, lhs_fill, rhs_fill
+        ),
+        lhs.stride,
+        coord_manager=lhs.coord_manager,
+        active_rows=alignment.active_rows,
+    )
+
+
+def sparse_add(lhs: SparseTensor, rhs: SparseTensor, *, join: str = 'outer') -> SparseTensor:
+    """``ops/tensor.py:150-157``; the residual connection of a sparse ResNet block."""
+    return sparse_binary_op(lhs, rhs, 'add', join=join)
+
+
+def sparse_sub(lhs: SparseTensor, rhs: SparseTensor, *, join: str = 'outer') -> SparseTensor:
+    return sparse_binary_op(lhs, rhs, 'sub', join=join)
+
+
+def sparse_mul(lhs: SparseTensor, rhs: SparseTensor, *, join: str = 'inner') -> SparseTensor:
+    return sparse_binary_op(lhs, rhs, 'mul', join=join)
+
+
+def sparse_maximum(lhs: SparseTensor, rhs: SparseTensor, *, join: str = 'inner') -> SparseTensor:
+    return sparse_binary_op(lhs, rhs, 'maximum', join=join)
+
+
+def sparse_minimum(lhs: SparseTensor, rhs: SparseTensor, *, join: str = 'inner') -> SparseTensor:
+    return sparse_binary_op(lhs, rhs, 'minimum', join=join)

@@ -551,6 +551,34 @@ def sparse_alignment(lhs_coords, lhs_active, rhs_coords, rhs_active, join: str):
     return out_coords, np.asarray([n], np.int32), out_l, out_r
 
 
+def gather_aligned_features(feats, rows, fill: float = 0.0) -> np.ndarray:
+    """``gather_aligned_features`` (``mlx_lattice/ops/tensor.py:89-109``): rows < 0 give
+    the fill value in every channel, in the feature dtype."""
+    feats = np.asarray(feats)
+    rows = np.asarray(rows, np.int32)
+    gathered = feats[np.maximum(rows, 0)]
+    return np.where((rows >= 0)[:, None], gathered, feats.dtype.type(fill))
+
+
+def concat_aligned_features(lhs, lhs_rows, rhs, rhs_rows) -> np.ndarray:
+    """The feature half of ``sparse_cat_aligned`` (``ops/tensor.py:228-249``)."""
+    return np.concatenate(
+        [gather_aligned_features(lhs, lhs_rows), gather_aligned_features(rhs, rhs_rows)], axis=1)
+
+
+def binary_aligned_features(lhs, lhs_rows, rhs, rhs_rows, op: str,
+                            lhs_fill: float = 0.0, rhs_fill: float = 0.0) -> np.ndarray:
+    """The feature half of ``sparse_binary_op`` (``ops/tensor.py:112-147``) with
+    ``_apply_binary_op`` (``tensor.py:285-296``), evaluated in the feature dtype."""
+    a = gather_aligned_features(lhs, lhs_rows, lhs_fill)
+    b = gather_aligned_features(rhs, rhs_rows, rhs_fill)
+    with np.errstate(all='ignore'):
+        return {
+            'add': lambda: a + b, 'sub': lambda: a - b, 'mul': lambda: a * b,
+            'maximum': lambda: np.maximum(a, b), 'minimum': lambda: np.minimum(a, b),
+        }[op]()
+
+
 # --------------------------------------------------------------------------- #
 # feature contraction
 # --------------------------------------------------------------------------- #

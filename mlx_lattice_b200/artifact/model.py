@@ -19,7 +19,7 @@ from mlx_lattice_b200.artifact.handlers import (
     infer_batch_size, quantized_payload_names, validate_value_type,
 )
 from mlx_lattice_b200.artifact.manifest import IRManifest, IRNode, value_refs
-from mlx_lattice_b200.artifact.registry import OperationBinding, validate_node
+from mlx_lattice_b200.artifact.registry import OperationBinding, node_inputs, validate_node
 
 # the version of the reference's public interface this package mirrors; a manifest's
 # ``runtime.version`` specifier is evaluated against it
@@ -110,7 +110,7 @@ def _check_manifest(manifest: IRManifest, weights: Mapping[str, torch.Tensor]) -
     for node in manifest.nodes:
         binding = validate_node(node)
         bindings.append(binding)
-        for port, ref in node.inputs.items():
+        for port, ref in node_inputs(binding, node).items():
             for value_name in value_refs(ref):
                 if value_name in types:
                     _check_types(node.id, f'inputs.{port}', value_name,
@@ -137,9 +137,10 @@ def _check_manifest(manifest: IRManifest, weights: Mapping[str, torch.Tensor]) -
 
 def _arguments(binding: OperationBinding, context: ExecutionContext, node: IRNode) -> dict[str, Any]:
     kwargs: dict[str, Any] = {}
+    inputs = node_inputs(binding, node)
     for port, argument in binding.inputs.items():
         kwargs[argument] = context.input_value(
-            node.inputs[port], sequence=port in binding.sequence_inputs
+            inputs[port], sequence=port in binding.sequence_inputs
         )
     for name, weight_name in node.parameters.items():
         item = binding.parameter(name)

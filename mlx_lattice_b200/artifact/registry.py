@@ -254,11 +254,21 @@ def _check_json(value: Any, path: str) -> None:
         raise ValueError(f'{path} must be JSON-compatible.')
 
 
+def node_inputs(binding: OperationBinding, node: IRNode) -> Mapping[str, Any]:
+    """The node's inputs by the binding's port names. A module node is written with the
+    single port ``input`` whatever its operation (``mlx_lattice/artifact/builder.py:244-251``),
+    also for the pooling modules whose operation is a generic ``ops.<function>`` route with
+    the port ``x``: ``input`` is accepted for the only port of such a route."""
+    if len(binding.inputs) == 1 and set(node.inputs) == {'input'} and 'input' not in binding.inputs:
+        return {next(iter(binding.inputs)): node.inputs['input']}
+    return node.inputs
+
+
 def validate_node(node: IRNode) -> OperationBinding:
     """Ports, parameter names and attribute names of a node against its binding
     (``mlx_lattice/artifact/registry.py:205-246``)."""
     binding = operation_binding(node.op)
-    _require_keys(node.inputs, set(binding.inputs), f'{node.id}.inputs')
+    _require_keys(node_inputs(binding, node), set(binding.inputs), f'{node.id}.inputs')
     _require_keys(node.outputs, {'output'}, f'{node.id}.outputs')
     missing = set(binding.parameters) - set(node.parameters)
     extra = set(node.parameters) - set(binding.parameters) - set(binding.optional_parameters)

@@ -170,6 +170,19 @@ def test_model_static_validation_messages():
             artifact.LatticeModel(artifact.manifest_from_dict(raw), _weights())
 
 
+def test_module_style_node_on_a_generic_route():
+    """A pooling module is exported as ``ops.max_pool3d`` with the port ``input``."""
+    manifest = _single('ops.max_pool3d', {'x0': 'sparse_tensor'}, 'pooled', node_inputs={'input': 'x0'},
+                       attributes={'kernel_size': [2, 2, 2], 'stride': [2, 2, 2]})
+    artifact.LatticeModel(manifest, {})
+    with pytest.raises(ValueError, match=r"expects 'sparse_tensor'"):
+        artifact.LatticeModel(_single('ops.max_pool3d', {'x0': 'dense_tensor'}, 'pooled',
+                                      node_inputs={'input': 'x0'}), {})
+    with pytest.raises(ValueError, match='inputs missing required keys'):
+        artifact.LatticeModel(_single('ops.sparse_cat_aligned', {'x0': 'sparse_tensor'}, 'y',
+                                      node_inputs={'input': 'x0'}), {})
+
+
 def _quantized_linear_artifact():
     dense = torch.from_numpy(np.random.default_rng(0).normal(size=(8, 64)).astype(np.float16))
     writer = artifact.GraphWriter({'input': 'sparse_tensor'})

@@ -416,6 +416,14 @@ int lat_batch_norm_relu(
 /* feature.py:54-56 (`relu`). */
 int lat_relu(int32_t dtype, const void* feats, int64_t elements, void* out, void* stream);
 
+/* mlx_lattice/ops/feature.py:59-129: op 0 sigmoid, 1 silu, 2 tanh, 3 gelu (erf form),
+ * 4 gelu (tanh approximation), 5 gelu (x * sigmoid(1.702 x)), 6 leaky_relu (p0 = negative
+ * slope), 7 softplus (p0 = beta > 0, p1 = threshold: x where beta x > threshold, else
+ * log(1 + exp(beta x)) / beta). Evaluated in float32, cast once. */
+int lat_activation(
+    int32_t dtype, int32_t op, const void* feats, int64_t elements, float p0, float p1, void* out,
+    void* stream);
+
 /* Channel concatenation of two feature matrices read through row maps
  * (mlx_lattice/ops/tensor.py:228-249 `sparse_cat_aligned`, which gathers each side with
  * `gather_aligned_features`, tensor.py:89-109, and concatenates): out [rows_out,

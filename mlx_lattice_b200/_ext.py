@@ -950,6 +950,25 @@ def batch_norm_relu(feats, weight, bias, mean, var, eps: float, apply_relu: bool
     return out
 
 
+_ACTIVATIONS = {
+    'sigmoid': 0, 'silu': 1, 'tanh': 2, 'gelu_erf': 3, 'gelu_tanh': 4, 'gelu_fast': 5,
+    'leaky_relu': 6, 'softplus': 7,
+}
+
+
+def activation(feats, name: str, p0: float = 0.0, p1: float = 0.0):
+    """Pointwise activation of a feature matrix (``mlx_lattice/ops/feature.py:59-129``)."""
+    feats, _ = _feats_arg(feats)
+    feats = feats.contiguous()
+    out = torch.empty_like(feats)
+    with torch.cuda.device(feats.device):
+        check(_lib().lat_activation(
+            _dtype_code(feats.dtype), _ACTIVATIONS[name], _ptr(feats), feats.numel(), float(p0),
+            float(p1), _ptr(out), _stream(),
+        ))
+    return out
+
+
 def relu(feats):
     feats, _ = _feats_arg(feats)
     feats = feats.contiguous()

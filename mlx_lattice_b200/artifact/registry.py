@@ -11,9 +11,9 @@ Two families, as in the reference (``mlx_lattice/artifact/ops.py:38-300``):
   defaulted graph-valued argument is a value attribute (the name of another graph
   value), every other argument is a JSON attribute; weights are parameters.
 
-Operations of the reference that lie outside this package's path (activations other
-than ReLU, layer/RMS norm, dropout, occupancy and ordering ops) are not registered and
-are rejected at load time with the reference's message, ``unsupported lattice IR op``.
+Operations of the reference that lie outside this package's path (layer/RMS norm,
+occupancy, ordering, neighbour-search and coordinate-set ops) are not registered and are
+rejected at load time with the reference's message, ``unsupported lattice IR op``.
 """
 
 from __future__ import annotations
@@ -208,6 +208,13 @@ def _register_all() -> None:
         output_type=_return_type(add),
     ))
     _semantic('feature.relu', 'relu')
+    _semantic('feature.sigmoid', 'sigmoid')
+    _semantic('feature.silu', 'silu')
+    _semantic('feature.tanh', 'tanh')
+    _semantic('feature.gelu', 'gelu', attributes=('approximate',))
+    _semantic('feature.leaky_relu', 'leaky_relu', attributes=('negative_slope',))
+    _semantic('feature.softplus', 'softplus', attributes=('beta', 'threshold'))
+    _semantic('feature.dropout', 'dropout', attributes=('p', 'training'))
     _semantic('feature.batch_norm', 'batch_norm', optional=('weight', 'bias', 'mean', 'var'),
               attributes=('eps', 'fuse_relu'))
     for mode in ('sum', 'avg', 'max'):

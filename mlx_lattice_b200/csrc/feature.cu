@@ -224,6 +224,62 @@ __global__ void relu_kernel(const T* feats, long long total, T* out) {
     }
 }
 
+// Pointwise activations of mlx_lattice/ops/feature.py:59-129, evaluated in float32 and cast
+// once. p0 / p1: negative slope (leaky ReLU); beta and threshold (softplus).
+enum Activation {
+    kSigmoid = 0, kSilu = 1, kTanh = 2, kGeluErf = 3, kGeluTanh = 4, kGeluFast = 5,
+    kLeakyRelu = 6, kSoftplus = 7,
+};
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+template <int Op> __device__ __forceinline__ float activate(float x, float p0, float p1) {
+    switch (Op) {
+        case kSigmoid: return sigmoid_f(x);
+        case kSilu: return x * sigmoid_f(x);
+        case kTanh: return tanhf(x);
+        case kGeluErf: return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
+        case kGeluTanh: return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+        case kGeluFast: return x * sigmoid_f(1.702f * x);
+        case kLeakyRelu: return x >= 0.0f ? x : x * p0;
+        default: {
+            const float scaled = x * p0;
+            return scaled > p1 ? x : log1pf(expf(scaled)) / p0;
+        }
+    }
+}
+
+template <typename T, int Op>
+__global__ void activation_kernel(const T* feats, long long total, float p0, float p1, T* out) {
+    long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (; i < total; i += stride) {
+        out[i] = from_float<T>(activate<Op>(to_float<T>(feats[i]), p0, p1));
+    }
+}
+
+template <typename T, int Op>
+void launch_activation(const void* feats, long long total, float p0, float p1, void* out,
+                       int grid, cudaStream_t stream) {
+    activation_kernel<T, Op><<<grid, 256, 0, stream>>>(
+        static_cast<const T*>(feats), total, p0, p1, static_cast<T*>(out));
+}
+
+template <typename T>
+void dispatch_activation(int op, const void* feats, long long total, float p0, float p1, void* out,
+                         int grid, cudaStream_t stream) {
+    switch (op) {
+        case kSigmoid: return launch_activation<T, kSigmoid>(feats, total, p0, p1, out, grid, stream);
+        case kSilu: return launch_activation<T, kSilu>(feats, total, p0, p1, out, grid, stream);
+        case kTanh: return launch_activation<T, kTanh>(feats, total, p0, p1, out, grid, stream);
+        case kGeluErf: return launch_activation<T, kGeluErf>(feats, total, p0, p1, out, grid, stream);
+        case kGeluTanh: return launch_activation<T, kGeluTanh>(feats, total, p0, p1, out, grid, stream);
+        case kGeluFast: return launch_activation<T, kGeluFast>(feats, total, p0, p1, out, grid, stream);
+        case kLeakyRelu: return launch_activation<T, kLeakyRelu>(feats, total, p0, p1, out, grid, stream);
+        default: return launch_activation<T, kSoftplus>(feats, total, p0, p1, out, grid, stream);
+    }
+}
+
 inline int elementwise_grid(long long total) {
     long long blocks = (total + 255) / 256;
     return static_cast<int>(std::max(1LL, std::min(blocks, 148LL * 32)));
@@ -362,6 +418,29 @@ int lat_relu(int32_t dtype, const void* feats, int64_t elements, void* out, void
     } else {
         relu_kernel<__half><<<grid, 256, 0, stream>>>(
             static_cast<const __half*>(feats), elements, static_cast<__half*>(out));
+    }
+    LAT_LAUNCH_CHECK();
+    return LAT_OK;
+}
+
+int lat_activation(
+    int32_t dtype, int32_t op, const void* feats, int64_t elements, float p0, float p1, void* out,
+    void* stream_ptr
+) {
+    LAT_REQUIRE(dtype == LAT_F32 || dtype == LAT_F16,
+                "activations support float32 and float16 tensors.");
+    LAT_REQUIRE(op >= kSigmoid && op <= kSoftplus, "unknown activation.");
+    LAT_REQUIRE(elements >= 0, "feats must have shape (N, C).");
+    LAT_REQUIRE(op != kSoftplus || p0 > 0.0f, "beta must be positive.");
+    if (elements == 0) {
+        return LAT_OK;
+    }
+    cudaStream_t stream = as_stream(stream_ptr);
+    int grid = elementwise_grid(elements);
+    if (dtype == LAT_F32) {
+        dispatch_activation<float>(op, feats, elements, p0, p1, out, grid, stream);
+    } else {
+        dispatch_activation<__half>(op, feats, elements, p0, p1, out, grid, stream);
     }
     LAT_LAUNCH_CHECK();
     return LAT_OK;

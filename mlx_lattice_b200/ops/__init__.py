@@ -13,7 +13,18 @@ from mlx_lattice_b200.ops.conv import (
     generative_conv_transpose3d,
     subm_conv3d,
 )
-from mlx_lattice_b200.ops.feature import batch_norm, linear, relu
+from mlx_lattice_b200.ops.feature import (
+    batch_norm,
+    dropout,
+    gelu,
+    leaky_relu,
+    linear,
+    relu,
+    sigmoid,
+    silu,
+    softplus,
+    tanh,
+)
 from mlx_lattice_b200.ops.pool import (
     avg_pool3d,
     global_avg_pool,
@@ -44,6 +55,7 @@ from mlx_lattice_b200.ops.tensor import (
 )
 
 __all__ = [
+    'dropout', 'gelu', 'leaky_relu', 'sigmoid', 'silu', 'softplus', 'tanh',
     'align_sparse', 'sparse_add', 'sparse_binary_op', 'sparse_maximum', 'sparse_minimum', 'sparse_mul',
     'sparse_sub',
     'avg_pool3d', 'batch_norm', 'build_generative_relation', 'build_point_voxel_map', 'devoxelize',

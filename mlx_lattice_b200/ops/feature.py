@@ -8,7 +8,10 @@ from mlx_lattice_b200 import _ext
 from mlx_lattice_b200.core import QuantizedWeight, SparseTensor
 from mlx_lattice_b200.ops._quantized import quantized_matmul
 
-__all__ = ['batch_norm', 'linear', 'relu']
+__all__ = [
+    'batch_norm', 'dropout', 'gelu', 'leaky_relu', 'linear', 'relu', 'sigmoid', 'silu', 'softplus',
+    'tanh',
+]
 
 
 def linear(x: SparseTensor, weight, bias: torch.Tensor | None = None) -> SparseTensor:
@@ -31,6 +34,50 @@ def linear(x: SparseTensor, weight, bias: torch.Tensor | None = None) -> SparseT
 
 def relu(x: SparseTensor) -> SparseTensor:
     return x.replace(feats=_ext.relu(x.feats))
+
+
+def sigmoid(x: SparseTensor) -> SparseTensor:
+    return x.replace(feats=_ext.activation(x.feats, 'sigmoid'))
+
+
+def silu(x: SparseTensor) -> SparseTensor:
+    return x.replace(feats=_ext.activation(x.feats, 'silu'))
+
+
+def tanh(x: SparseTensor) -> SparseTensor:
+    return x.replace(feats=_ext.activation(x.feats, 'tanh'))
+
+
+def gelu(x: SparseTensor, *, approximate: str = 'none') -> SparseTensor:
+    """``'none'`` / ``'precise'``: the erf formula; ``'tanh'``: the tanh approximation;
+    ``'fast'``: ``x * sigmoid(1.702 x)`` (``ops/feature.py:64-93``)."""
+    forms = {'none': 'gelu_erf', 'precise': 'gelu_erf', 'tanh': 'gelu_tanh', 'fast': 'gelu_fast'}
+    if approximate not in forms:
+        raise ValueError("approximate must be 'none', 'precise', 'tanh', or 'fast'.")
+    return x.replace(feats=_ext.activation(x.feats, forms[approximate]))
+
+
+def leaky_relu(x: SparseTensor, *, negative_slope: float = 0.01) -> SparseTensor:
+    return x.replace(feats=_ext.activation(x.feats, 'leaky_relu', float(negative_slope)))
+
+
+def softplus(x: SparseTensor, *, beta: float = 1.0, threshold: float = 20.0) -> SparseTensor:
+    """``x`` where ``beta * x > threshold``, else ``log(1 + exp(beta x)) / beta``
+    (``ops/feature.py:112-129``)."""
+    if beta <= 0:
+        raise ValueError('beta must be positive.')
+    return x.replace(feats=_ext.activation(x.feats, 'softplus', float(beta), float(threshold)))
+
+
+def dropout(x: SparseTensor, *, p: float = 0.5, training: bool = True) -> SparseTensor:
+    """Inference form of ``ops/feature.py:132-150``: the features pass unchanged when
+    ``training`` is false or ``p`` is zero. Sampling a mask is training work and is not
+    part of this package."""
+    if p < 0 or p >= 1:
+        raise ValueError('p must satisfy 0 <= p < 1.')
+    if training and p != 0:
+        raise ValueError('dropout in training mode is not available on the inference path.')
+    return x.replace(feats=x.feats)
 
 
 def batch_norm(

@@ -579,6 +579,36 @@ def binary_aligned_features(lhs, lhs_rows, rhs, rhs_rows, op: str,
         }[op]()
 
 
+def activation(feats, name: str, **params) -> np.ndarray:
+    """Pointwise activations of ``mlx_lattice/ops/feature.py:59-129`` in float64, for
+    comparison within a rounding tolerance of the feature dtype."""
+    import math
+
+    x = np.asarray(feats, np.float64)
+    sig = lambda v: 1.0 / (1.0 + np.exp(-v))  # noqa: E731
+    erf = np.vectorize(math.erf)
+    if name == 'sigmoid':
+        return sig(x)
+    if name == 'silu':
+        return x * sig(x)
+    if name == 'tanh':
+        return np.tanh(x)
+    if name == 'gelu':
+        form = params.get('approximate', 'none')
+        if form in ('none', 'precise'):
+            return 0.5 * x * (1.0 + erf(x * 0.7071067811865476))
+        if form == 'tanh':
+            return 0.5 * x * (1.0 + np.tanh(0.7978845608028654 * (x + 0.044715 * x ** 3)))
+        return x * sig(1.702 * x)
+    if name == 'leaky_relu':
+        return np.where(x >= 0, x, x * params.get('negative_slope', 0.01))
+    if name == 'softplus':
+        beta, threshold = params.get('beta', 1.0), params.get('threshold', 20.0)
+        with np.errstate(over='ignore'):
+            return np.where(x * beta > threshold, x, np.log1p(np.exp(x * beta)) / beta)
+    raise ValueError(name)
+
+
 # --------------------------------------------------------------------------- #
 # feature contraction
 # --------------------------------------------------------------------------- #

@@ -139,3 +139,48 @@ def test_argument_errors(cuda):
     c = _tensor(cuda, rhs_c, np.zeros((rhs_c.shape[0], 4), np.float16))
     with pytest.raises(ValueError, match='matching feature dtype'):
         ops.sparse_add(a, c)
+
+
+ACTIVATIONS = [
+    ('sigmoid', {}), ('silu', {}), ('tanh', {}), ('gelu', {}), ('gelu', {'approximate': 'precise'}),
+    ('gelu', {'approximate': 'tanh'}), ('gelu', {'approximate': 'fast'}),
+    ('leaky_relu', {}), ('leaky_relu', {'negative_slope': 0.2}),
+    ('softplus', {}), ('softplus', {'beta': 2.5, 'threshold': 6.0}),
+]
+
+
+@pytest.mark.parametrize('dtype', [np.float16, np.float32])
+@pytest.mark.parametrize('name, params', ACTIVATIONS)
+def test_activations(cuda, restatement, dtype, name, params):
+    """Against the float64 restatement: within 2 units in the last place of the feature
+    dtype (float32 evaluation with the device's expf / tanhf / erff, one cast)."""
+    from mlx_lattice_b200 import ops
+
+    lhs_c, _ = _clouds(9, n_lhs=1500)
+    rng = np.random.default_rng(10)
+    feats = (rng.normal(size=(lhs_c.shape[0], 24)) * 4).astype(dtype)
+    feats[:8, 0] = [0.0, -0.0, 30.0, -30.0, 7.99, 8.01, 1e-4, -1e-4]
+    x = _tensor(cuda, lhs_c, feats)
+    got = getattr(ops, name)(x, **params)
+    assert got.same_coords(x) and got.feats.dtype == x.feats.dtype
+    want = restatement.activation(feats, name, **params)
+    eps = np.finfo(dtype).eps
+    tolerance = 2 * eps * np.maximum(np.abs(want), np.finfo(dtype).tiny / eps)
+    assert np.all(np.abs(got.feats.cpu().numpy().astype(np.float64) - want) <= tolerance)
+
+
+def test_activation_arguments_and_inference_dropout(cuda):
+    from mlx_lattice_b200 import ops
+
+    lhs_c, _ = _clouds(11, n_lhs=100)
+    x = _tensor(cuda, lhs_c, np.ones((100, 4), np.float32))
+    with pytest.raises(ValueError, match="approximate must be"):
+        ops.gelu(x, approximate='quick')
+    with pytest.raises(ValueError, match='beta must be positive'):
+        ops.softplus(x, beta=0.0)
+    with pytest.raises(ValueError, match='0 <= p < 1'):
+        ops.dropout(x, p=1.0)
+    with pytest.raises(ValueError, match='training mode'):
+        ops.dropout(x, p=0.5, training=True)
+    assert torch.equal(ops.dropout(x, p=0.5, training=False).feats, x.feats)
+    assert torch.equal(ops.dropout(x, p=0.0).feats, x.feats)

@@ -416,6 +416,14 @@ int lat_batch_norm_relu(
 /* feature.py:54-56 (`relu`). */
 int lat_relu(int32_t dtype, const void* feats, int64_t elements, void* out, void* stream);
 
+/* mlx_lattice/ops/feature.py:196-225 (`layer_norm`, `rms_norm`): per row over the
+ * channels, rms = 0: (x - mean) * rsqrt(var + eps) * weight + bias with the biased
+ * variance; rms = 1: x * rsqrt(mean(x^2) + eps) * weight (bias must be NULL). weight and
+ * bias [channels] may be NULL. Statistics in float32, cast once. */
+int lat_row_norm(
+    int32_t dtype, int32_t rms, const void* feats, int64_t rows, int32_t channels,
+    const void* weight, const void* bias, float eps, void* out, void* stream);
+
 /* mlx_lattice/ops/feature.py:59-129: op 0 sigmoid, 1 silu, 2 tanh, 3 gelu (erf form),
  * 4 gelu (tanh approximation), 5 gelu (x * sigmoid(1.702 x)), 6 leaky_relu (p0 = negative
  * slope), 7 softplus (p0 = beta > 0, p1 = threshold: x where beta x > threshold, else

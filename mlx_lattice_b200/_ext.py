@@ -969,6 +969,28 @@ def activation(feats, name: str, p0: float = 0.0, p1: float = 0.0):
     return out
 
 
+def row_norm(feats, weight, bias, eps: float, rms: bool):
+    """``layer_norm`` (``rms`` false) or ``rms_norm`` over the channels of every row."""
+    feats, _ = _feats_arg(feats)
+    feats = feats.contiguous()
+    channels = int(feats.shape[1])
+    for vector, name in ((weight, 'weight'), (bias, 'bias')):
+        if vector is not None:
+            _require_cuda(vector, name)
+            if tuple(vector.shape) != (channels,):
+                raise ValueError(f'{name} must have shape ({channels},).')
+            if vector.dtype != feats.dtype:
+                raise ValueError(f'{name} must match the feature dtype.')
+    out = torch.empty_like(feats)
+    with torch.cuda.device(feats.device):
+        check(_lib().lat_row_norm(
+            _dtype_code(feats.dtype), int(bool(rms)), _ptr(feats), int(feats.shape[0]), channels,
+            _ptr(None if weight is None else weight.contiguous()),
+            _ptr(None if bias is None else bias.contiguous()), float(eps), _ptr(out), _stream(),
+        ))
+    return out
+
+
 def relu(feats):
     feats, _ = _feats_arg(feats)
     feats = feats.contiguous()

@@ -101,6 +101,7 @@ SIGNATURES = {
     'lat_batch_norm_relu': (I, [I, P, c_int64, I, P, P, P, P, c_float, I, P, P]),
     'lat_relu': (I, [I, P, c_int64, P, P]),
     'lat_activation': (I, [I, I, P, c_int64, c_float, c_float, P, P]),
+    'lat_row_norm': (I, [I, I, P, c_int64, I, P, P, c_float, P, P]),
     'lat_concat_aligned_features': (I, [I, P, P, I, I, P, P, I, I, c_int64, P, P, P]),
     'lat_binary_aligned_features': (
         I, [I, I, P, P, I, c_float, P, P, I, c_float, c_int64, I, P, P, P]),

@@ -11,8 +11,8 @@ Two families, as in the reference (``mlx_lattice/artifact/ops.py:38-300``):
   defaulted graph-valued argument is a value attribute (the name of another graph
   value), every other argument is a JSON attribute; weights are parameters.
 
-Operations of the reference that lie outside this package's path (layer/RMS norm,
-occupancy, ordering, neighbour-search and coordinate-set ops) are not registered and are
+Operations of the reference that lie outside this package's path (occupancy, ordering,
+neighbour-search and coordinate-set ops) are not registered and are
 rejected at load time with the reference's message, ``unsupported lattice IR op``.
 """
 
@@ -47,6 +47,8 @@ _PARAMETER_HINTS: dict[str, dict[str, tuple[str, str]]] = {
     'generative_conv_transpose3d': _CONV_HINTS,
     'linear': _CONV_HINTS,
     'batch_norm': {name: ('optional', 'array') for name in ('weight', 'bias', 'mean', 'var')},
+    'layer_norm': {name: ('optional', 'array') for name in ('weight', 'bias')},
+    'rms_norm': {'weight': ('optional', 'array')},
 }
 _VALUE_ATTRIBUTE_HINTS = {'conv3d': {'coordinates': 'any'}, 'conv_transpose3d': {'coordinates': 'sparse_tensor'}}
 
@@ -217,6 +219,8 @@ def _register_all() -> None:
     _semantic('feature.dropout', 'dropout', attributes=('p', 'training'))
     _semantic('feature.batch_norm', 'batch_norm', optional=('weight', 'bias', 'mean', 'var'),
               attributes=('eps', 'fuse_relu'))
+    _semantic('feature.layer_norm', 'layer_norm', optional=('weight', 'bias'), attributes=('eps',))
+    _semantic('feature.rms_norm', 'rms_norm', optional=('weight',), attributes=('eps',))
     for mode in ('sum', 'avg', 'max'):
         _semantic(f'pool.global_{mode}', f'global_{mode}_pool', handler=global_pool_handler)
     for name, function in public_ops().items():

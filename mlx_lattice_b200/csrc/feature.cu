@@ -280,6 +280,53 @@ void dispatch_activation(int op, const void* feats, long long total, float p0, f
     }
 }
 
+// Row-wise normalisations (mlx_lattice/ops/feature.py:196-225, which call the array
+// library's fused layer_norm / rms_norm): one warp per row, statistics in float32 over
+// the channels (mean, then the biased variance about it; or the mean square), then
+// (x - mean) * rsqrt(var + eps) * weight + bias, or x * rsqrt(ms + eps) * weight.
+template <typename T, bool Rms>
+__global__ void __launch_bounds__(256) row_norm_kernel(
+    const T* feats, long long rows, int channels, const T* weight, const T* bias, float eps, T* out
+) {
+    const int lane = threadIdx.x & 31;
+    const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+    for (long long row = blockIdx.x * static_cast<long long>(blockDim.x >> 5) + (threadIdx.x >> 5);
+         row < rows; row += warps) {
+        const T* x = feats + row * channels;
+        float mean = 0.0f;
+        if (!Rms) {
+            float sum = 0.0f;
+            for (int c = lane; c < channels; c += 32) {
+                sum += to_float<T>(x[c]);
+            }
+            for (int delta = 16; delta > 0; delta >>= 1) {
+                sum += __shfl_xor_sync(0xffffffffu, sum, delta);
+            }
+            mean = sum / static_cast<float>(channels);
+        }
+        float squares = 0.0f;
+        for (int c = lane; c < channels; c += 32) {
+            const float d = to_float<T>(x[c]) - mean;
+            squares = fmaf(d, d, squares);
+        }
+        for (int delta = 16; delta > 0; delta >>= 1) {
+            squares += __shfl_xor_sync(0xffffffffu, squares, delta);
+        }
+        const float scale = rsqrtf(squares / static_cast<float>(channels) + eps);
+        T* y = out + row * channels;
+        for (int c = lane; c < channels; c += 32) {
+            float v = (to_float<T>(x[c]) - mean) * scale;
+            if (weight != nullptr) {
+                v *= to_float<T>(weight[c]);
+            }
+            if (bias != nullptr) {
+                v += to_float<T>(bias[c]);
+            }
+            y[c] = from_float<T>(v);
+        }
+    }
+}
+
 inline int elementwise_grid(long long total) {
     long long blocks = (total + 255) / 256;
     return static_cast<int>(std::max(1LL, std::min(blocks, 148LL * 32)));
@@ -418,6 +465,45 @@ int lat_relu(int32_t dtype, const void* feats, int64_t elements, void* out, void
     } else {
         relu_kernel<__half><<<grid, 256, 0, stream>>>(
             static_cast<const __half*>(feats), elements, static_cast<__half*>(out));
+    }
+    LAT_LAUNCH_CHECK();
+    return LAT_OK;
+}
+
+int lat_row_norm(
+    int32_t dtype, int32_t rms, const void* feats, int64_t rows, int32_t channels,
+    const void* weight, const void* bias, float eps, void* out, void* stream_ptr
+) {
+    LAT_REQUIRE(dtype == LAT_F32 || dtype == LAT_F16,
+                "normalisation supports float32 and float16 tensors.");
+    LAT_REQUIRE(eps > 0.0f, "eps must be positive.");
+    LAT_REQUIRE(rows >= 0 && channels > 0, "feats must have shape (N, C).");
+    LAT_REQUIRE(!rms || bias == nullptr, "rms_norm has no bias.");
+    if (rows == 0) {
+        return LAT_OK;
+    }
+    cudaStream_t stream = as_stream(stream_ptr);
+    const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>((rows + 7) / 8, 148LL * 16)));
+    if (dtype == LAT_F32) {
+        auto* x = static_cast<const float*>(feats);
+        auto* w = static_cast<const float*>(weight);
+        auto* b = static_cast<const float*>(bias);
+        auto* y = static_cast<float*>(out);
+        if (rms) {
+            row_norm_kernel<float, true><<<grid, 256, 0, stream>>>(x, rows, channels, w, b, eps, y);
+        } else {
+            row_norm_kernel<float, false><<<grid, 256, 0, stream>>>(x, rows, channels, w, b, eps, y);
+        }
+    } else {
+        auto* x = static_cast<const __half*>(feats);
+        auto* w = static_cast<const __half*>(weight);
+        auto* b = static_cast<const __half*>(bias);
+        auto* y = static_cast<__half*>(out);
+        if (rms) {
+            row_norm_kernel<__half, true><<<grid, 256, 0, stream>>>(x, rows, channels, w, b, eps, y);
+        } else {
+            row_norm_kernel<__half, false><<<grid, 256, 0, stream>>>(x, rows, channels, w, b, eps, y);
+        }
     }
     LAT_LAUNCH_CHECK();
     return LAT_OK;

@@ -17,9 +17,11 @@ from mlx_lattice_b200.ops.feature import (
     batch_norm,
     dropout,
     gelu,
+    layer_norm,
     leaky_relu,
     linear,
     relu,
+    rms_norm,
     sigmoid,
     silu,
     softplus,
@@ -55,7 +57,7 @@ from mlx_lattice_b200.ops.tensor import (
 )
 
 __all__ = [
-    'dropout', 'gelu', 'leaky_relu', 'sigmoid', 'silu', 'softplus', 'tanh',
+    'dropout', 'gelu', 'layer_norm', 'leaky_relu', 'rms_norm', 'sigmoid', 'silu', 'softplus', 'tanh',
     'align_sparse', 'sparse_add', 'sparse_binary_op', 'sparse_maximum', 'sparse_minimum', 'sparse_mul',
     'sparse_sub',
     'avg_pool3d', 'batch_norm', 'build_generative_relation', 'build_point_voxel_map', 'devoxelize',

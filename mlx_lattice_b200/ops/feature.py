@@ -9,8 +9,8 @@ from mlx_lattice_b200.core import QuantizedWeight, SparseTensor
 from mlx_lattice_b200.ops._quantized import quantized_matmul
 
 __all__ = [
-    'batch_norm', 'dropout', 'gelu', 'leaky_relu', 'linear', 'relu', 'sigmoid', 'silu', 'softplus',
-    'tanh',
+    'batch_norm', 'dropout', 'gelu', 'layer_norm', 'leaky_relu', 'linear', 'relu', 'rms_norm', 'sigmoid',
+    'silu', 'softplus', 'tanh',
 ]
 
 
@@ -78,6 +78,20 @@ def dropout(x: SparseTensor, *, p: float = 0.5, training: bool = True) -> Sparse
     if training and p != 0:
         raise ValueError('dropout in training mode is not available on the inference path.')
     return x.replace(feats=x.feats)
+
+
+def layer_norm(x: SparseTensor, *, weight=None, bias=None, eps: float = 1e-5) -> SparseTensor:
+    """Layer normalisation of every sparse row over its channels (``ops/feature.py:196-210``)."""
+    if eps <= 0:
+        raise ValueError('eps must be positive.')
+    return x.replace(feats=_ext.row_norm(x.feats, weight, bias, eps, rms=False))
+
+
+def rms_norm(x: SparseTensor, *, weight=None, eps: float = 1e-5) -> SparseTensor:
+    """RMS normalisation of every sparse row (``ops/feature.py:214-225``)."""
+    if eps <= 0:
+        raise ValueError('eps must be positive.')
+    return x.replace(feats=_ext.row_norm(x.feats, weight, None, eps, rms=True))
 
 
 def batch_norm(

@@ -579,6 +579,22 @@ def binary_aligned_features(lhs, lhs_rows, rhs, rhs_rows, op: str,
         }[op]()
 
 
+def row_norm(feats, weight=None, bias=None, eps: float = 1e-5, rms: bool = False) -> np.ndarray:
+    """``layer_norm`` / ``rms_norm`` of ``mlx_lattice/ops/feature.py:196-225`` in float64:
+    biased variance over the channels of each row."""
+    x = np.asarray(feats, np.float64)
+    if rms:
+        y = x / np.sqrt(np.mean(x * x, axis=1, keepdims=True) + eps)
+    else:
+        mean = x.mean(axis=1, keepdims=True)
+        y = (x - mean) / np.sqrt(((x - mean) ** 2).mean(axis=1, keepdims=True) + eps)
+    if weight is not None:
+        y = y * np.asarray(weight, np.float64)
+    if bias is not None:
+        y = y + np.asarray(bias, np.float64)
+    return y
+
+
 def activation(feats, name: str, **params) -> np.ndarray:
     """Pointwise activations of ``mlx_lattice/ops/feature.py:59-129`` in float64, for
     comparison within a rounding tolerance of the feature dtype."""

@@ -186,3 +186,34 @@ def test_activation_arguments_and_inference_dropout(cuda):
         ops.dropout(x, p=0.5, training=True)
     assert torch.equal(ops.dropout(x, p=0.5, training=False).feats, x.feats)
     assert torch.equal(ops.dropout(x, p=0.0).feats, x.feats)
+
+
+@pytest.mark.parametrize('dtype', [np.float16, np.float32])
+@pytest.mark.parametrize('channels', [1, 20, 64, 100])
+def test_layer_norm_and_rms_norm(cuda, restatement, dtype, channels):
+    """Against the float64 restatement within 8 eps of the feature dtype times the scale of
+    the normalised row (float32 statistics, one cast)."""
+    from mlx_lattice_b200 import ops
+
+    lhs_c, _ = _clouds(12, n_lhs=700)
+    rng = np.random.default_rng(13)
+    feats = (rng.normal(size=(700, channels)) * 3 + 1.5).astype(dtype)
+    weight = rng.normal(size=channels).astype(dtype)
+    bias = rng.normal(size=channels).astype(dtype)
+    x = _tensor(cuda, lhs_c, feats)
+    w, b = torch.from_numpy(weight).to(cuda), torch.from_numpy(bias).to(cuda)
+    eps = float(np.finfo(dtype).eps)
+    cases = [
+        (ops.layer_norm(x), restatement.row_norm(feats)),
+        (ops.layer_norm(x, weight=w, bias=b, eps=1e-3), restatement.row_norm(feats, weight, bias, 1e-3)),
+        (ops.rms_norm(x), restatement.row_norm(feats, rms=True)),
+        (ops.rms_norm(x, weight=w, eps=1e-2), restatement.row_norm(feats, weight, None, 1e-2, rms=True)),
+    ]
+    for got, want in cases:
+        assert got.same_coords(x) and got.feats.dtype == x.feats.dtype
+        scale = np.abs(want).max(axis=1, keepdims=True) + 1.0
+        assert np.all(np.abs(got.feats.cpu().numpy().astype(np.float64) - want) <= 8 * eps * scale)
+    with pytest.raises(ValueError, match='eps must be positive'):
+        ops.layer_norm(x, eps=0.0)
+    with pytest.raises(ValueError, match=r'weight must have shape'):
+        ops.rms_norm(x, weight=torch.ones(channels + 1, dtype=x.feats.dtype, device=cuda))

@@ -217,3 +217,20 @@ def test_layer_norm_and_rms_norm(cuda, restatement, dtype, channels):
         ops.layer_norm(x, eps=0.0)
     with pytest.raises(ValueError, match=r'weight must have shape'):
         ops.rms_norm(x, weight=torch.ones(channels + 1, dtype=x.feats.dtype, device=cuda))
+
+
+def test_feature_modules_call_their_operators(cuda):
+    from mlx_lattice_b200 import nn, ops
+
+    lhs_c, _ = _clouds(14, n_lhs=300)
+    feats = np.random.default_rng(15).normal(size=(300, 16)).astype(np.float32)
+    x = _tensor(cuda, lhs_c, feats)
+    pairs = [
+        (nn.Sigmoid(), ops.sigmoid(x)), (nn.SiLU(), ops.silu(x)), (nn.Tanh(), ops.tanh(x)),
+        (nn.GELU('tanh'), ops.gelu(x, approximate='tanh')), (nn.LeakyReLU(0.3), ops.leaky_relu(x, negative_slope=0.3)),
+        (nn.Softplus(), ops.softplus(x)), (nn.Dropout(0.4), x),
+        (nn.LayerNorm(16).to(cuda), ops.layer_norm(x, weight=torch.ones(16, device=cuda), bias=torch.zeros(16, device=cuda))),
+        (nn.RMSNorm(16).to(cuda), ops.rms_norm(x, weight=torch.ones(16, device=cuda))),
+    ]
+    for module, want in pairs:
+        assert torch.equal(module(x).feats, want.feats), type(module).__name__

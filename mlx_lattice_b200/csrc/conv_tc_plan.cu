@@ -397,6 +397,35 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                 computed = info.x != 0;
             }
             __half* out_row = row >= 0 ? p.out + static_cast<size_t>(row) * p.c_out : nullptr;
+            if (!computed) {
+                // No row of this tile has an edge (the inactive tail of a map with a static
+                // capacity, mostly): the rows are zeros plus bias. The warp writes its 32 rows
+                // as one run of 16-byte pieces, lane after lane, instead of a row per lane.
+                const int chunks = p.c_out >> 3;
+                for (int idx = lane; idx < 32 * chunks; idx += 32) {
+                    const int r = idx / chunks;
+                    const int c = idx - r * chunks;
+                    const int target = __shfl_sync(0xffffffffu, row, r);
+                    uint4 piece = make_uint4(0u, 0u, 0u, 0u);
+                    if (p.bias != nullptr) {
+                        __half2 h[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            h[j] = __halves2half2(__ldg(p.bias + c * 8 + 2 * j),
+                                                  __ldg(p.bias + c * 8 + 2 * j + 1));
+                        }
+                        piece = *reinterpret_cast<uint4*>(h);
+                    }
+                    if (target >= 0) {
+                        reinterpret_cast<uint4*>(p.out + static_cast<size_t>(target) * p.c_out)[c] = piece;
+                    }
+                }
+                if (tile < active) {
+                    tc_fence_before();
+                    mbar_arrive(&ctl.acc_empty[a]);
+                }
+                continue;
+            }
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>((2 * a + half_tile) * p.acc_cols);
             for (int c0 = 0; c0 < p.c_out; c0 += 32) {

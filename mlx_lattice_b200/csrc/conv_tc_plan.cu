@@ -95,6 +95,43 @@ __device__ __forceinline__ int2 load_info(const PlanConvParams& p, int tile, int
     return tile < active ? __ldg(p.tile_info + tile) : make_int2(0, 0);
 }
 
+// Rows of a tile none of whose rows has an edge: zeros plus bias. Warp `w` (0-7) of a role
+// writes tile rows 32 w .. 32 w + 31 as one run of 16-byte pieces, lane after lane (the
+// inactive tail of a static-capacity map is a contiguous stretch of rows).
+__device__ __forceinline__ void fill_edgeless_rows(const PlanConvParams& p, int tile, int w, int lane) {
+    const int position = tile * kTileRows + w * 32 + lane;
+    int row = -1;
+    if (position < p.out_capacity) {
+        row = p.row_order != nullptr ? __ldg(p.row_order + position) : position;
+        if (row < 0 || row >= p.out_capacity) {
+            raise_status(p.status, LAT_STATUS_BAD_INDEX);
+            row = -1;
+        }
+    }
+    const int chunks = p.c_out >> 3;
+    for (int idx = lane; idx < 32 * chunks; idx += 32) {
+        const int r = idx / chunks;
+        const int c = idx - r * chunks;
+        const int target = __shfl_sync(0xffffffffu, row, r);
+        uint4 piece = make_uint4(0u, 0u, 0u, 0u);
+        if (p.bias != nullptr) {
+            __half2 h[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                h[j] = __halves2half2(__ldg(p.bias + c * 8 + 2 * j), __ldg(p.bias + c * 8 + 2 * j + 1));
+            }
+            piece = *reinterpret_cast<uint4*>(h);
+        }
+        if (target >= 0) {
+            reinterpret_cast<uint4*>(p.out + static_cast<size_t>(target) * p.c_out)[c] = piece;
+        }
+    }
+}
+
+// the tiles past the last one with an edge are shared between the producer warps (which
+// run out of work first) and the epilogue warps: even and odd rounds of the tile loop
+__device__ __forceinline__ bool producers_fill(int tile, int grid) { return ((tile / grid) & 1) == 0; }
+
 __global__ void __launch_bounds__(kThreads, 1)
 tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -365,6 +402,12 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
         }
         cp_async_wait<0>();
         }
+        for (int tile = blockIdx.x + ((active - blockIdx.x + grid - 1) / grid) * grid;
+             tile < p.num_tiles; tile += grid) {
+            if (producers_fill(tile, grid)) {
+                fill_edgeless_rows(p, tile, warp, lane);
+            }
+        }
     } else if (warp < 16) {
         // ======================= epilogue =======================
         const int ew = warp - 8;
@@ -398,27 +441,8 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
             }
             __half* out_row = row >= 0 ? p.out + static_cast<size_t>(row) * p.c_out : nullptr;
             if (!computed) {
-                // No row of this tile has an edge (the inactive tail of a map with a static
-                // capacity, mostly): the rows are zeros plus bias. The warp writes its 32 rows
-                // as one run of 16-byte pieces, lane after lane, instead of a row per lane.
-                const int chunks = p.c_out >> 3;
-                for (int idx = lane; idx < 32 * chunks; idx += 32) {
-                    const int r = idx / chunks;
-                    const int c = idx - r * chunks;
-                    const int target = __shfl_sync(0xffffffffu, row, r);
-                    uint4 piece = make_uint4(0u, 0u, 0u, 0u);
-                    if (p.bias != nullptr) {
-                        __half2 h[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            h[j] = __halves2half2(__ldg(p.bias + c * 8 + 2 * j),
-                                                  __ldg(p.bias + c * 8 + 2 * j + 1));
-                        }
-                        piece = *reinterpret_cast<uint4*>(h);
-                    }
-                    if (target >= 0) {
-                        reinterpret_cast<uint4*>(p.out + static_cast<size_t>(target) * p.c_out)[c] = piece;
-                    }
+                if (tile < active || !producers_fill(tile, grid)) {
+                    fill_edgeless_rows(p, tile, ew, lane);
                 }
                 if (tile < active) {
                     tc_fence_before();

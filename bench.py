@@ -594,6 +594,97 @@ def run_gpu_arm(args) -> None:
         dist.destroy_process_group()
 
 
+
+# --------------------------------------------------------------------------- #
+# single-kernel cases: python bench.py --case <name> (the commands behind profiles/)
+# --------------------------------------------------------------------------- #
+
+
+def level_tensor(device, clouds: int, level: int, channels: int, per_cloud: int = PER_CLOUD,
+                 config_index: int = CONFIG_INDEX):
+    """Sparse tensor on the coordinates of encoder level `level` of the benchmark network
+    (level 0 = input voxels, each further level one kernel-2 stride-2 downsampling) for
+    `clouds` LiDAR-like clouds, with seeded N(0,1) fp16 features of `channels` channels."""
+    import torch
+
+    from mlx_lattice_b200 import ops, workloads
+    from mlx_lattice_b200.core import SparseTensor
+
+    coords_np, _ = workloads.minkunet_inputs(config_index, clouds, per_cloud)
+    rng = np.random.default_rng(1234 + level)
+    x = SparseTensor(torch.from_numpy(coords_np).to(device),
+                     torch.zeros((coords_np.shape[0], 32), dtype=torch.float16, device=device))
+    down = torch.zeros((32, 2, 2, 2, 32), dtype=torch.float16, device=device)
+    for _ in range(level):
+        x = ops.conv3d(x, down, kernel_size=2, stride=2)
+    feats = torch.from_numpy(rng.normal(size=(x.capacity, channels)).astype(np.float16)).to(device)
+    return x.replace(feats=feats)
+
+
+def run_case(args) -> None:
+    """One kernel of the path on a small, named input, a few times over, printing the
+    event time of each repetition: `conv:<level>:<c_in>:<c_out>[:fp16]` (submanifold 3x3x3
+    int4 convolution on level `level` of `--clouds` clouds), `down:<level>:<c_in>:<c_out>`
+    (kernel-2 stride-2 int4 convolution from that level), `map[:stride]` (kernel map of
+    `--clouds` clouds of 125,000 voxels of config 2), `pool` (max_pool3d k3 s2 over one
+    config-3 cloud, 96 channels)."""
+    import torch
+
+    from mlx_lattice_b200 import _ext, _native, ops, synthetic, workloads
+    from mlx_lattice_b200.core import SparseTensor, quantize_weight
+
+    _native.load()
+    device = torch.device('cuda', 0)
+    parts = args.case.split(':')
+    kind = parts[0]
+
+    def timed(fn):
+        for _ in range(args.iters):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            out = fn()
+            end.record()
+            torch.cuda.synchronize()
+            yield out, start.elapsed_time(end)
+
+    if kind in ('conv', 'down'):
+        level, c_in, c_out = int(parts[1]), int(parts[2]), int(parts[3])
+        k = 3 if kind == 'conv' else 2
+        rng = np.random.default_rng(5)
+        dense = torch.from_numpy((rng.normal(size=(c_out, k, k, k, c_in)) * 0.05).astype(np.float16))
+        if len(parts) > 4 and parts[4] == 'fp16':
+            weight = dense.to(device)
+        else:
+            weight = workloads.quantized_to(quantize_weight(dense, group_size=32, bits=4), device)
+        x = level_tensor(device, args.clouds, level, c_in)
+        run = ((lambda: ops.subm_conv3d(x, weight, kernel_size=3)) if kind == 'conv'
+               else (lambda: ops.conv3d(x, weight, kernel_size=2, stride=2)))
+        for y, ms in timed(run):
+            rel = (x.coord_manager.submanifold_kernel_relation(x.coord_key, kernel_size=3)
+                   if kind == 'conv' else
+                   x.coord_manager.kernel_relation(x.coord_key, kernel_size=2, stride=2))
+            edges, n_out = rel.counts.tolist()
+            print(f'{args.case} clouds={args.clouds} rows_in={int(x.active_rows.item())} out_rows={n_out} '
+                  f'edges={edges} ms={ms:.3f} tflops={2.0 * edges * c_in * c_out / ms / 1e9:.1f}')
+    elif kind == 'map':
+        stride = int(parts[1]) if len(parts) > 1 else 1
+        coords = torch.from_numpy(synthetic.lidar_batch(2, args.clouds, 125000)).to(device)
+        n = coords.shape[0]
+        active = torch.tensor([n], dtype=torch.int32, device=device)
+        for (base, _, _), ms in timed(lambda: _ext.build_kernel_relation_base(coords, active, 3, stride, 0, 1)):
+            print(f'{args.case} rows={n} counts={base[5].tolist()} ms={ms:.3f} mcoords_per_s={n / ms / 1e3:.0f}')
+    elif kind == 'pool':
+        coords_np = synthetic.lidar_batch(3, args.clouds, 60000)
+        rng = np.random.default_rng(9)
+        feats = torch.from_numpy(rng.normal(size=(coords_np.shape[0], 96)).astype(np.float16)).to(device)
+        x = SparseTensor(torch.from_numpy(coords_np).to(device), feats)
+        for y, ms in timed(lambda: ops.max_pool3d(x, kernel_size=3, stride=2)):
+            print(f'{args.case} rows={x.capacity} out_rows={int(y.active_rows.item())} ms={ms:.3f}')
+    else:
+        raise SystemExit(f'unknown case {args.case}')
+    _ext.check_status(device)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument('--gpus', type=int, default=1)
@@ -602,8 +693,15 @@ def main() -> None:
     parser.add_argument('--impl', default='ours', choices=('ours', 'reference'))
     parser.add_argument('--cpu-sample', type=int, default=8000,
                         help='voxels of one cloud the CPU reference leg processes')
+    parser.add_argument('--case', default=None,
+                        help='run one kernel on a small named input instead of the benchmark '
+                             '(see run_case); used for the ncu captures under profiles/')
+    parser.add_argument('--clouds', type=int, default=1)
+    parser.add_argument('--iters', type=int, default=3)
     args = parser.parse_args()
-    if args.impl == 'reference':
+    if args.case is not None:
+        run_case(args)
+    elif args.impl == 'reference':
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

@@ -73,6 +73,14 @@ const char* lat_last_error(void);
 /* Number of CUDA kernels this library has launched in the process so far (no
  * reference counterpart; used by the benchmark to report its launch count). */
 long long lat_launch_count(void);
+/* Clock budget (SM cycles, default 4e9, about two seconds) after which a bounded wait
+ * inside a kernel (an mbarrier of the tensor-core pipeline, the look-back of the
+ * single-pass kernel map) gives up: the kernel then sets LAT_STATUS_WAIT_TIMEOUT in the
+ * status word, every role leaves its loop, tensor memory is freed and the launch
+ * returns. No reference counterpart (the reference's kernels do not wait on each
+ * other). Process-wide; takes effect for launches made after the call. */
+int lat_set_wait_budget_cycles(int64_t cycles);
+int64_t lat_wait_budget_cycles(void);
 
 /* native/features/coordinates/offsets.cpp:11-45 (`kernel_offsets`): host helper,
  * writes kernel_volume x 3 int32 to a HOST buffer, x-major / z-fastest. */
@@ -259,11 +267,17 @@ int lat_build_sparse_alignment(
  * tensor-core route uses to form its 256-row tiles (any permutation is valid),
  * optional `plan` is the gather plan built by lat_build_conv_plan over this relation
  * and this `row_order` (the tensor-core route then reads it instead of the relation
- * arrays; other routes ignore it). */
+ * arrays; other routes ignore it). Optional `feats2` [in_capacity, feats2_channels] (row
+ * stride `feats2_row_stride`, NULL = none) supplies the LAST feats2_channels of the
+ * in_channels input channels, `feats` the first in_channels - feats2_channels: the
+ * convolution then reads the channel concatenation of two tensors over the same rows
+ * (mlx_lattice/ops/tensor.py `sparse_cat_aligned` followed by a convolution) without the
+ * concatenated tensor being written. Tensor-core route with a plan only; the channel
+ * split must be a multiple of 8. */
 size_t lat_sparse_conv_workspace_bytes(int32_t n_kernels, int32_t in_channels, int32_t out_channels);
 int lat_sparse_conv_features(
     int32_t dtype, const void* feats, int32_t in_capacity, int32_t in_channels,
-    int64_t feat_row_stride,
+    int64_t feat_row_stride, const void* feats2, int32_t feats2_channels, int64_t feats2_row_stride,
     const void* weights, int32_t weight_layout, lat_triple kernel_shape, int32_t out_channels,
     const int32_t* in_rows, const int32_t* out_rows, const int32_t* kernel_ids,
     int32_t edge_capacity, const int32_t* counts, const int32_t* row_offsets,
@@ -280,6 +294,7 @@ int lat_sparse_conv_features(
  * replaced here by the optional `row_order`. `bias`/`row_order` as above. */
 int lat_sparse_quantized_conv_features(
     int32_t dtype, const void* feats, int32_t in_capacity, int64_t feat_row_stride,
+    const void* feats2, int32_t feats2_channels, int64_t feats2_row_stride,
     const uint32_t* packed, const void* scales, const void* biases,
     const int32_t* in_rows, const int32_t* out_rows, const int32_t* kernel_ids,
     int32_t edge_capacity, const int32_t* counts, const int32_t* row_offsets,

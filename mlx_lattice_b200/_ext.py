@@ -113,6 +113,18 @@ def _dtype_code(dtype: torch.dtype) -> int:
     raise ValueError('convolution supports float32 and float16 tensors.')
 
 
+def _second_source(feats: torch.Tensor, feats2) -> tuple[torch.Tensor | None, int, int]:
+    """Validated second feature source of a convolution: (tensor, row stride, channels)."""
+    if feats2 is None:
+        return None, 0, 0
+    feats2, stride2 = _feats_arg(feats2)
+    if feats2.device != feats.device or feats2.dtype != feats.dtype:
+        raise ValueError('both feature sources must share device and dtype.')
+    if feats2.shape[0] != feats.shape[0]:
+        raise ValueError('both feature sources must have the same row count.')
+    return feats2, stride2, int(feats2.shape[1])
+
+
 def _feats_arg(feats: torch.Tensor) -> tuple[torch.Tensor, int]:
     _require_cuda(feats, 'feats')
     if feats.ndim != 2:
@@ -713,12 +725,14 @@ def _weight_geometry(weights: torch.Tensor, n_kernels: int, in_channels: int):
 def sparse_conv_features(
     feats, weights, in_rows, out_rows, kernel_ids, counts, row_offsets,
     in_row_offsets=None, in_edge_ids=None, kernel_row_offsets=None, kernel_edge_ids=None,
-    out_capacity=None, n_kernels=None, *, bias=None, row_order=None, plan=None,
+    out_capacity=None, n_kernels=None, *, bias=None, row_order=None, plan=None, feats2=None,
 ):
     """``_ext.sparse_conv_features`` (``convolution.cpp:90-146``). The four grouped
     view arguments are accepted for signature compatibility; the forward pass does
-    not read them."""
+    not read them. ``feats2`` (optional, same rows) supplies the trailing input channels:
+    the convolution reads the channel concatenation ``[feats | feats2]`` in place."""
     feats, stride = _feats_arg(feats)
+    feats2, stride2, c2 = _second_source(feats, feats2)
     _require_cuda(weights, 'weights')
     if weights.dtype != feats.dtype:
         raise ValueError('convolution weights must match feature dtype.')
@@ -732,7 +746,7 @@ def sparse_conv_features(
     out_capacity, n_kernels = int(out_capacity), int(n_kernels)
     if row_offsets.shape[0] != out_capacity + 1:
         raise ValueError('row_offsets must have length out_capacity + 1.')
-    c_in = int(feats.shape[1])
+    c_in = int(feats.shape[1]) + c2
     layout, shape, c_out = _weight_geometry(weights, n_kernels, c_in)
     device = feats.device
     out = torch.empty((out_capacity, c_out), dtype=feats.dtype, device=device)
@@ -743,7 +757,8 @@ def sparse_conv_features(
             'tensor_cores': conv_uses_tensor_cores(feats.dtype, n_kernels, c_in, c_out)}
     with torch.cuda.device(device):
         _profiled('conv', info, lambda: check(lib.lat_sparse_conv_features(
-            dtype, _ptr(feats), int(feats.shape[0]), c_in, stride, _ptr(weights), layout, shape,
+            dtype, _ptr(feats), int(feats.shape[0]), c_in, stride, _ptr(feats2), c2, stride2,
+            _ptr(weights), layout, shape,
             c_out, _ptr(in_rows), _ptr(out_rows), _ptr(kernel_ids), int(in_rows.shape[0]),
             _ptr(counts), _ptr(row_offsets), out_capacity, n_kernels, _ptr(bias),
             _ptr(row_order), _ptr(plan), _ptr(out), _ptr(ws), ws.numel(),
@@ -757,12 +772,13 @@ def sparse_quantized_conv_features(
     sorted_kv_out_in_map=None, reorder_rows=None, tile_masks=None,
     out_capacity=None, n_kernels=None, in_channels=None, out_channels=None,
     storage_in_channels=None, group_size=None, bits=None, *, bias=None, row_order=None,
-    plan=None,
+    plan=None, feats2=None,
 ):
     """``_ext.sparse_quantized_conv_features`` (``convolution.cpp:12-89``). The
     three sorted-plan arrays may be empty in the reference call; here a non-empty
     ``reorder_rows`` is used as the row permutation of the tensor-core tiles."""
     feats, stride = _feats_arg(feats)
+    feats2, stride2, c2 = _second_source(feats, feats2)
     dtype = _dtype_code(feats.dtype)
     for tensor, name in ((weights, 'weights'), (scales, 'scales'), (biases, 'biases')):
         _require_cuda(tensor, name)
@@ -773,7 +789,7 @@ def sparse_quantized_conv_features(
     n_kernels, out_capacity = int(n_kernels), int(out_capacity)
     in_channels, out_channels = int(in_channels), int(out_channels)
     storage, group_size, bits = int(storage_in_channels), int(group_size), int(bits)
-    if feats.shape[1] != in_channels:
+    if feats.shape[1] + c2 != in_channels:
         raise ValueError('quantized weight input channels must match x.channels.')
     if bits not in (4, 8):
         raise ValueError('quantized convolution supports only 4 or 8 bits.')
@@ -804,8 +820,8 @@ def sparse_quantized_conv_features(
                 feats.dtype, n_kernels, in_channels, out_channels, bits, group_size)}
     with torch.cuda.device(device):
         _profiled('conv', info, lambda: check(lib.lat_sparse_quantized_conv_features(
-            dtype, _ptr(feats), int(feats.shape[0]), stride, _ptr(weights), _ptr(scales),
-            _ptr(biases), _ptr(in_rows), _ptr(out_rows), _ptr(kernel_ids),
+            dtype, _ptr(feats), int(feats.shape[0]), stride, _ptr(feats2), c2, stride2,
+            _ptr(weights), _ptr(scales), _ptr(biases), _ptr(in_rows), _ptr(out_rows), _ptr(kernel_ids),
             int(in_rows.shape[0]), _ptr(counts), _ptr(row_offsets), out_capacity, n_kernels,
             in_channels, out_channels, storage, group_size, bits, _ptr(bias), _ptr(row_order),
             _ptr(plan), _ptr(out), _ptr(ws), ws.numel(), _ptr(status_word(device)), _stream(),

@@ -44,6 +44,8 @@ SIGNATURES = {
     'lat_version': (c_char_p, []),
     'lat_last_error': (c_char_p, []),
     'lat_launch_count': (ctypes.c_longlong, []),
+    'lat_set_wait_budget_cycles': (I, [c_int64]),
+    'lat_wait_budget_cycles': (c_int64, []),
     'lat_capabilities': (I, [POINTER(c_int32), POINTER(c_int32)]),
     'lat_kernel_offsets_host': (I, [Triple, Triple, P]),
     'lat_relation_workspace_bytes': (c_size_t, [I, I, I]),
@@ -76,10 +78,10 @@ SIGNATURES = {
     'lat_build_sparse_alignment': (I, [P, I, P, P, I, P, I, P, P, P, P, P, c_size_t, P, P]),
     'lat_sparse_conv_workspace_bytes': (c_size_t, [I, I, I]),
     'lat_sparse_conv_features': (
-        I, [I, P, I, I, c_int64, P, I, Triple, I, P, P, P, I, P, P, I, I, P, P, P, P, P,
+        I, [I, P, I, I, c_int64, P, I, c_int64, P, I, Triple, I, P, P, P, I, P, P, I, I, P, P, P, P, P,
             c_size_t, P, P]),
     'lat_sparse_quantized_conv_features': (
-        I, [I, P, I, c_int64, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P, P, P, P, P,
+        I, [I, P, I, c_int64, P, I, c_int64, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P, P, P, P, P,
             c_size_t, P, P]),
     'lat_conv_plan_bytes': (c_size_t, [I, I]),
     'lat_build_conv_plan': (I, [P, P, I, P, P, I, I, I, P, P, c_size_t, P, P]),

@@ -18,10 +18,15 @@ class SparseTensor:
     on the device) records the valid prefix of the static-capacity buffers. A
     ``CoordinateManager`` owns the coordinate array and a ``CoordinateMapKey``
     names it; feature-only operations keep that identity so relations are reused.
+
+    ``feats`` may also be given as a pair of tensors over the same rows (the result of a
+    channel concatenation that has not been written yet): ``feat_parts`` then returns the
+    pair, which a tensor-core convolution reads in place, and ``feats`` writes and caches
+    the concatenated array on first access.
     """
 
     __slots__ = (
-        'coords', 'feats', 'stride', 'coord_key', 'coord_manager', 'batch_counts',
+        'coords', '_feats', '_parts', 'stride', 'coord_key', 'coord_manager', 'batch_counts',
         'active_rows',
     )
 
@@ -58,9 +63,19 @@ class SparseTensor:
                 if active_rows is None
                 else _active_rows(active_rows)
             )
-        if feats.ndim != 2:
-            raise ValueError('feats must have shape (N, C).')
-        if owned.shape[0] != feats.shape[0]:
+        parts = None
+        if isinstance(feats, (tuple, list)):
+            parts = tuple(feats)
+            if len(parts) != 2 or any(part.ndim != 2 for part in parts):
+                raise ValueError('feature parts must be two arrays of shape (N, C).')
+            if parts[0].shape[0] != parts[1].shape[0] or parts[0].dtype != parts[1].dtype:
+                raise ValueError('feature parts must share row count and dtype.')
+            rows = int(parts[0].shape[0])
+        else:
+            if feats.ndim != 2:
+                raise ValueError('feats must have shape (N, C).')
+            rows = int(feats.shape[0])
+        if owned.shape[0] != rows:
             raise ValueError('coords and feats must have the same row count.')
         counts = None
         if batch_counts is not None:
@@ -70,12 +85,32 @@ class SparseTensor:
             if sum(counts) != owned.shape[0]:
                 raise ValueError('batch_counts must cover all sparse rows.')
         self.coords = owned
-        self.feats = feats
+        self._feats = None if parts is not None else feats
+        self._parts = parts
         self.stride = normalized_stride
         self.coord_key = key
         self.coord_manager = manager
         self.batch_counts = counts
         self.active_rows = active
+
+    @property
+    def feats(self) -> torch.Tensor:
+        if self._feats is None:
+            from mlx_lattice_b200 import _ext
+
+            self._feats = _ext.concat_aligned_features(self._parts[0], None, self._parts[1], None)
+            self._parts = None
+        return self._feats
+
+    @feats.setter
+    def feats(self, value: torch.Tensor) -> None:
+        self._feats = value
+        self._parts = None
+
+    @property
+    def feat_parts(self):
+        """The two tensors whose channel concatenation is ``feats``, while it is unwritten."""
+        return self._parts
 
     @property
     def capacity(self) -> int:
@@ -87,7 +122,9 @@ class SparseTensor:
 
     @property
     def channels(self) -> int:
-        return int(self.feats.shape[1])
+        if self._parts is not None:
+            return int(self._parts[0].shape[1] + self._parts[1].shape[1])
+        return int(self._feats.shape[1])
 
     @property
     def shape(self) -> tuple[int, int]:
@@ -95,7 +132,7 @@ class SparseTensor:
 
     @property
     def dtype(self) -> torch.dtype:
-        return self.feats.dtype
+        return self._parts[0].dtype if self._parts is not None else self._feats.dtype
 
     @property
     def batch_indices(self) -> torch.Tensor:

@@ -10,7 +10,10 @@ namespace lat {
 namespace {
 thread_local std::string g_last_error;
 std::atomic<long long> g_launches{0};
+std::atomic<long long> g_wait_budget{4000000000LL};  // about two seconds of SM clocks
 }
+
+long long wait_budget_cycles() { return g_wait_budget.load(std::memory_order_relaxed); }
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
@@ -37,6 +40,7 @@ bool tc_conv_supported(int dtype, int n_kernels, int in_channels, int out_channe
 size_t tc_conv_workspace_bytes(int n_kernels, int in_channels, int out_channels);
 int run_tc_conv(
     const void* feats, int in_capacity, int in_channels, long long feat_stride,
+    const void* feats2, int feats2_channels, long long feat2_stride,
     const void* weights, int weight_layout, const uint32_t* packed, const void* scales,
     const void* biases, int storage_in_channels, int group_size, int bits, int out_channels,
     const int32_t* in_rows, const int32_t* kernel_ids, int edge_capacity, const int32_t* counts,
@@ -55,6 +59,14 @@ const char* lat_version(void) { return "0.1.0+b200"; }
 const char* lat_last_error(void) { return g_last_error.c_str(); }
 
 long long lat_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int lat_set_wait_budget_cycles(int64_t cycles) {
+    LAT_REQUIRE(cycles > 0, "the wait budget must be a positive number of clock cycles.");
+    g_wait_budget.store(cycles, std::memory_order_relaxed);
+    return LAT_OK;
+}
+
+int64_t lat_wait_budget_cycles(void) { return wait_budget_cycles(); }
 
 int lat_capabilities(int32_t* has_sm100, int32_t* device_count) {
     int count = 0;
@@ -130,7 +142,7 @@ static int validate_conv_common(
 
 int lat_sparse_conv_features(
     int32_t dtype, const void* feats, int32_t in_capacity, int32_t in_channels,
-    int64_t feat_row_stride,
+    int64_t feat_row_stride, const void* feats2, int32_t feats2_channels, int64_t feats2_row_stride,
     const void* weights, int32_t weight_layout, lat_triple kernel_shape, int32_t out_channels,
     const int32_t* in_rows, const int32_t* out_rows, const int32_t* kernel_ids,
     int32_t edge_capacity, const int32_t* counts, const int32_t* row_offsets,
@@ -155,12 +167,13 @@ int lat_sparse_conv_features(
     }
     cudaStream_t stream = as_stream(stream_ptr);
     if (tc_conv_supported(dtype, n_kernels, in_channels, out_channels, 0, 0)) {
-        return run_tc_conv(feats, in_capacity, in_channels, feat_row_stride, weights,
-                           weight_layout, nullptr, nullptr, nullptr, in_channels, 0, 0,
+        return run_tc_conv(feats, in_capacity, in_channels, feat_row_stride, feats2,
+                           feats2_channels, feats2_row_stride, weights, weight_layout, nullptr, nullptr, nullptr, in_channels, 0, 0,
                            out_channels, in_rows, kernel_ids, edge_capacity, counts, row_offsets,
                            out_capacity, n_kernels, bias, row_order, plan, out, workspace,
                            workspace_bytes, status, stream);
     }
+    LAT_REQUIRE(feats2 == nullptr, "a second feature source needs the tensor-core route and a gather plan.");
     return run_direct_conv(dtype, feats, in_capacity, in_channels, feat_row_stride, weights,
                            weight_layout, nullptr, nullptr, nullptr, in_channels, 0, 0,
                            out_channels, in_rows, kernel_ids, edge_capacity, counts, row_offsets,
@@ -170,6 +183,7 @@ int lat_sparse_conv_features(
 
 int lat_sparse_quantized_conv_features(
     int32_t dtype, const void* feats, int32_t in_capacity, int64_t feat_row_stride,
+    const void* feats2, int32_t feats2_channels, int64_t feats2_row_stride,
     const uint32_t* packed, const void* scales, const void* biases,
     const int32_t* in_rows, const int32_t* out_rows, const int32_t* kernel_ids,
     int32_t edge_capacity, const int32_t* counts, const int32_t* row_offsets,
@@ -195,12 +209,14 @@ int lat_sparse_quantized_conv_features(
                 "packed weight, scales and biases are required.");
     cudaStream_t stream = as_stream(stream_ptr);
     if (tc_conv_supported(dtype, n_kernels, in_channels, out_channels, bits, group_size)) {
-        return run_tc_conv(feats, in_capacity, in_channels, feat_row_stride, nullptr, 0, packed,
+        return run_tc_conv(feats, in_capacity, in_channels, feat_row_stride, feats2,
+                           feats2_channels, feats2_row_stride, nullptr, 0, packed,
                            scales, biases, storage_in_channels, group_size, bits, out_channels,
                            in_rows, kernel_ids, edge_capacity, counts, row_offsets, out_capacity,
                            n_kernels, bias, row_order, plan, out, workspace, workspace_bytes, status,
                            stream);
     }
+    LAT_REQUIRE(feats2 == nullptr, "a second feature source needs the tensor-core route and a gather plan.");
     return run_direct_conv(dtype, feats, in_capacity, in_channels, feat_row_stride, nullptr, 0,
                            packed, scales, biases, storage_in_channels, group_size, bits,
                            out_channels, in_rows, kernel_ids, edge_capacity, counts, row_offsets,

@@ -27,6 +27,9 @@ int fail(int code, const std::string& message);
         }                                                                           \
     } while (0)
 
+// Clock budget of the bounded in-kernel waits (lat_set_wait_budget_cycles).
+long long wait_budget_cycles();
+
 // Every kernel launch site is followed by this macro, so it also counts launches.
 void count_launch();
 #define LAT_LAUNCH_CHECK()                                                          \

@@ -716,7 +716,8 @@ int pow2_at_least(int value, int floor_value) {
 
 // conv_tc_plan.cu
 int run_tc_conv_plan(
-    const void* feats, int in_channels, long long feat_stride, const void* weights,
+    const void* feats, int in_channels, long long feat_stride, const void* feats2, int split,
+    long long feat2_stride, const void* weights,
     long long w_stride_k, long long w_stride_co, int n_kernels, int out_channels, int out_capacity,
     const void* bias, const int32_t* row_order, const void* plan, void* out, int32_t* status,
     cudaStream_t stream);
@@ -760,6 +761,7 @@ size_t tc_conv_workspace_bytes(int n_kernels, int in_channels, int out_channels)
 
 int run_tc_conv(
     const void* feats, int in_capacity, int in_channels, long long feat_stride,
+    const void* feats2, int feats2_channels, long long feat2_stride,
     const void* weights, int weight_layout, const uint32_t* packed, const void* scales,
     const void* biases, int storage_in_channels, int group_size, int bits, int out_channels,
     const int32_t* in_rows, const int32_t* kernel_ids, int edge_capacity, const int32_t* counts,
@@ -828,10 +830,12 @@ int run_tc_conv(
     }
     if (plan != nullptr && packed == nullptr) {
         // fp16 weights and a prebuilt gather plan: the plan-driven kernel
-        return run_tc_conv_plan(feats, in_channels, feat_stride, p.weights, p.w_stride_k,
+        return run_tc_conv_plan(feats, in_channels, feat_stride, feats2, in_channels - feats2_channels,
+                                feat2_stride, p.weights, p.w_stride_k,
                                 p.w_stride_co, n_kernels, out_channels, out_capacity, bias, row_order, plan,
                                 out, status, stream);
     }
+    LAT_REQUIRE(feats2 == nullptr, "a second feature source needs a gather plan (lat_build_conv_plan).");
     p.in_rows = in_rows;
     p.kernel_ids = kernel_ids;
     p.row_offsets = row_offsets;

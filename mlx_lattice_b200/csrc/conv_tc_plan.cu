@@ -24,6 +24,8 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
@@ -36,18 +38,42 @@ using namespace tcgen05;
 
 namespace {
 
+#ifdef LAT_TC_KNOBS
+__device__ long long g_dbg[148 * 16];
+#define DBG_DECL long long dbg_a = 0, dbg_b = 0; int dbg_na = 0, dbg_nb = 0
+#define DBG_T0() const long long dbg_t0 = clock64()
+#define DBG_A() do { dbg_a += clock64() - dbg_t0; ++dbg_na; } while (0)
+#define DBG_B() do { dbg_b += clock64() - dbg_t0; ++dbg_nb; } while (0)
+#define DBG_FLUSH(slot) do { long long* d = g_dbg + blockIdx.x * 16 + (slot); d[0] += dbg_a; d[1] += dbg_na; d[2] += dbg_b; d[3] += dbg_nb; } while (0)
+#else
+#define DBG_DECL
+#define DBG_T0()
+#define DBG_A()
+#define DBG_B()
+#define DBG_FLUSH(slot)
+#endif
+
 constexpr int kTileRows = kPlanTileRows;
-constexpr int kProducerThreads = 256;
-constexpr int kEpilogueThreads = 256;
-constexpr int kThreads = 544;
+constexpr int kProducerWarps = 8;
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 576;
 constexpr int kMmaWarp = 16;
+constexpr int kLoaderWarp = 17;
+constexpr int kVectorRing = 16;                   // row vectors held in shared memory
+constexpr int kVectorBytes = kPlanTileRows * 4;
 constexpr int kMaxStages = 8;
 constexpr int kMaxAccStages = 8;
 constexpr int kSlabBytesA = kTileRows * 128;
 
 struct PlanConvParams {
+    // Feature rows may come from two tensors over the same rows: channels [0, split) from
+    // `feats`, channels [split, c_in) from `feats2` (the concatenation of a decoder level
+    // read in place). split == c_in when there is one source. split is a multiple of 8.
     const __half* feats;
+    const __half* feats2;
     int feat_row_bytes;
+    int feat2_row_bytes;
+    int split;
     int c_in;
     int c_out;
     // fp16 weights addressed (in bytes) as base + k*w_k_bytes + co*w_co_bytes + 2*ci
@@ -61,6 +87,7 @@ struct PlanConvParams {
     const __half* bias;
     __half* out;
     int32_t* status;
+    long long wait_budget;
     int stages;
     int stage_bytes;     // 32 KB of A rows + the B tile
     int tmem_cols;
@@ -69,6 +96,9 @@ struct PlanConvParams {
     int num_tiles;
     int b_tma;           // 1: the B tile of a slab is one TMA box (C_in a multiple of 64)
     int b_k_outer;       // tensor-map dimension order: 1 = (C_in, C_out, K), 0 = (C_in, K, C_out)
+#ifdef LAT_TC_KNOBS
+    int knobs;
+#endif
 };
 
 struct Ring {
@@ -87,9 +117,18 @@ struct Control {
     uint64_t empty[kMaxStages];
     uint64_t acc_full[kMaxAccStages];
     uint64_t acc_empty[kMaxAccStages];
+    uint64_t vec_full[kVectorRing];
+    uint64_t vec_empty[kVectorRing];
+    int32_t vec_header[kVectorRing];
     uint32_t tmem_base;
     int abort_flag;
 };
+
+// header of a row vector in the shared-memory ring: kernel offset, position inside the
+// tile and how many vectors the tile has; negative = no more work for this CTA
+__device__ __forceinline__ int32_t make_header(int k, int present) { return k | (present << 8); }
+__device__ __forceinline__ int header_k(int32_t h) { return h & 31; }
+__device__ __forceinline__ int header_present(int32_t h) { return (h >> 8) & 63; }
 
 __device__ __forceinline__ int2 load_info(const PlanConvParams& p, int tile, int active) {
     return tile < active ? __ldg(p.tile_info + tile) : make_int2(0, 0);
@@ -137,23 +176,42 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    Control& ctl = *reinterpret_cast<Control*>(smem + p.stages * p.stage_bytes);
+    uint8_t* const vec_ring = smem + p.stages * p.stage_bytes;
+    Control& ctl = *reinterpret_cast<Control*>(vec_ring + kVectorRing * kVectorBytes);
     volatile int* abort_flag = &ctl.abort_flag;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
     const int upo = p.c_in / 32;  // units per kernel offset
+#ifdef LAT_TC_KNOBS
+    const long long dbg_kernel_t0 = clock64();
+#endif
     const int grid = gridDim.x;
+    const long long budget = p.wait_budget;
+    // Bounded wait whose verdict is the same in every lane of the (converged) warp, so that a
+    // wait that gives up takes the whole warp out of its loop and no lane is left behind at
+    // a warp-level synchronisation.
+    auto wait_warp = [&](uint64_t* bar, uint32_t parity) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, p.status, budget));
+    };
 
     if (tid == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
-            mbar_init(&ctl.full[s], kProducerThreads + (p.b_tma ? 1 : 0));
+#ifdef LAT_TC_KNOBS
+            mbar_init(&ctl.full[s], ((p.knobs & 256) ? kProducerWarps : kProducerWarps * 32) + (p.b_tma ? 1 : 0));
+#else
+            mbar_init(&ctl.full[s], kProducerWarps * 32 + (p.b_tma ? 1 : 0));
+#endif
             mbar_init(&ctl.empty[s], 1);
         }
         for (int a = 0; a < kMaxAccStages; ++a) {
             mbar_init(&ctl.acc_full[a], 1);
-            mbar_init(&ctl.acc_empty[a], kEpilogueThreads);
+            mbar_init(&ctl.acc_empty[a], kEpilogueWarps);
+        }
+        for (int v = 0; v < kVectorRing; ++v) {
+            mbar_init(&ctl.vec_full[v], 1);
+            mbar_init(&ctl.vec_empty[v], kProducerWarps);
         }
         ctl.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -182,226 +240,248 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
         // with the same swizzle term because (q + 32 j) % 8 == q % 8. The B tile uses the
         // same offsets for output channels q + 32 i.
         const uint32_t dst0 = static_cast<uint32_t>(q * 128 + ((a_chunk ^ (q & 7)) << 4));
-        const char* const feat_bytes = reinterpret_cast<const char*>(p.feats);
         const char* const weight_bytes = reinterpret_cast<const char*>(p.weights);
-        const int feat_row_bytes = p.feat_row_bytes;
         const long long w_co0 = static_cast<long long>(q) * p.w_co_bytes;
         const long long w_co_step = 32LL * p.w_co_bytes;
         const int b_copies = p.c_out >> 5;  // C_out is a multiple of 32 here, or 16 (see below)
+        // byte address and row pitch of channel `channel` of row 0 in the tensor that holds it
+        auto channel_base = [&](int channel, int& pitch) -> const char* {
+            if (channel < p.split) {
+                pitch = p.feat_row_bytes;
+                return reinterpret_cast<const char*>(p.feats) + channel * 2;
+            }
+            pitch = p.feat2_row_bytes;
+            return reinterpret_cast<const char*>(p.feats2) + (channel - p.split) * 2;
+        };
+        // this thread's eight row ids of a vector in the ring (32 contiguous bytes)
+        auto read_vector = [&](int slot, int4& d0, int4& d1) {
+            const uint32_t src = smem_u32(vec_ring + slot * kVectorBytes + q * 32);
+            d0 = lds_v4_pinned(src);
+            d1 = lds_v4_pinned(src + 16);
+        };
         Ring ring{0, 0u};
+        Ring vec{0, 0u};
         bool ok = true;
+        DBG_DECL;
+        // wait for stage `ring.index` to be free (the warp decides as one)
+        auto acquire_stage = [&]() -> bool {
+            DBG_T0();
+            const bool got = wait_warp(&ctl.empty[ring.index], ring.phase ^ 1u);
+            DBG_A();
+            return got;
+        };
+        // The slab in stage `ring.index` is issued. Every thread's copies arrive on the stage's
+        // barrier by themselves when they have landed (no thread waits for its own copies).
+        auto slab_issued = [&]() {
+#ifdef LAT_TC_KNOBS
+            if (p.knobs & 256) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ctl.full[ring.index]);
+                ring.advance(p.stages);
+                return;
+            }
+#endif
+            cp_async_arrive_noinc(&ctl.full[ring.index]);
+            ring.advance(p.stages);
+        };
 
         if ((upo & 1) == 0) {
             // ---- C_in a multiple of 64: both units of a slab belong to one kernel offset ----
-            // The loop nest is tile > offset > slab; everything that depends on the input
-            // rows (eight source addresses and their zero-fill flags) is computed once per
-            // offset, and the next offset's row vector is loaded while the current one's
-            // slabs are issued, so a slab costs its copies and little else.
+            // One ring entry = one (tile, offset) = C_in / 64 slabs. Tile boundaries do not
+            // matter here: the stream of slabs runs on until the loader's end marker.
             const int reps = upo >> 1;  // slabs per offset
-            const int unit_bytes = a_half * 64 + col8 * 2;  // this thread's 16 bytes inside a 128-byte K slab
-            int tile = blockIdx.x;
-            int2 info = load_info(p, tile, active);
-            int4 v0 = make_int4(-1, -1, -1, -1), v1 = v0;
-            auto load_vector = [&](int vector_index, int4& d0, int4& d1) {
-                const int4* src = reinterpret_cast<const int4*>(
-                    p.vectors + static_cast<size_t>(vector_index) * kTileRows + q * 8);
-                d0 = __ldg(src);
-                d1 = __ldg(src + 1);
-            };
-            if (tile < active && info.x != 0) {
-                load_vector(info.y, v0, v1);
-            }
-            while (tile < active && ok) {
-                int next_tile = tile + grid;
-                int2 next_info = load_info(p, next_tile, active);
-                uint32_t rem = static_cast<uint32_t>(info.x);
-                const int present = __popc(rem);
-                for (int o = 0; o < present && ok; ++o) {
-                    const int k = __ffs(rem) - 1;
-                    rem &= rem - 1;
-                    const int idx[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-                    const char* src[8];
-                    uint32_t valid = 0;
+            const int thread_channel = a_half * 32 + col8;
+            while (ok) {
+                {
+                DBG_T0();
+                if (!wait_warp(&ctl.vec_full[vec.index], vec.phase)) {
+                    ok = false;
+                    break;
+                }
+                DBG_B();
+                }
+                const int32_t header = ctl.vec_header[vec.index];
+                if (header < 0) {
+                    break;
+                }
+                int4 v0, v1;
+                read_vector(vec.index, v0, v1);
+                const int k = header_k(header);
+                const int idx[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                for (int r = 0; r < reps; ++r) {
+                    int pitch;
+                    const char* const base = channel_base(r * 64 + thread_channel, pitch);
+                    if (!acquire_stage()) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_addr = smem_u32(smem + ring.index * p.stage_bytes) + dst0;
+                    const uint32_t b_addr = a_addr + kSlabBytesA;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        src[j] = feat_bytes + unit_bytes +
-                                 static_cast<long long>(max(idx[j], 0)) * feat_row_bytes;
-                        valid |= idx[j] >= 0 ? (1u << j) : 0u;
+                        // absent neighbours copy zero bytes from a valid address: zero fill
+#ifdef LAT_TC_KNOBS
+                        if (p.knobs & 32) continue;
+                        cp_async_16(a_addr + 4096 * j,
+                                    base + static_cast<long long>(max(idx[j], 0)) * pitch, idx[j] >= 0 && !(p.knobs & 2));
+#else
+                        cp_async_16(a_addr + 4096 * j,
+                                    base + static_cast<long long>(max(idx[j], 0)) * pitch, idx[j] >= 0);
+#endif
                     }
-                    // the row vector of the next offset (of this tile, or the first of the
-                    // next tile that has any) travels while this offset's slabs are issued
-                    if (o + 1 < present) {
-                        load_vector(info.y + o + 1, v0, v1);
+                    if (p.b_tma) {
+                        if (tid == 0) {
+#ifdef LAT_TC_KNOBS
+                            if (p.knobs & 1) {
+                                mbar_arrive(&ctl.full[ring.index]);
+                            } else
+#endif
+                            {
+                            mbar_arrive_expect_tx(&ctl.full[ring.index],
+                                                  static_cast<uint32_t>(p.c_out) * 128u);
+                            tma_load_3d(b_addr - dst0, &b_map, r * 64, p.b_k_outer ? 0 : k,
+                                        p.b_k_outer ? k : 0, &ctl.full[ring.index]);
+                            }
+                        }
                     } else {
-                        while (next_tile < active && next_info.x == 0) {
-                            next_tile += grid;
-                            next_info = load_info(p, next_tile, active);
+                        const char* w_src = weight_bytes + static_cast<long long>(k) * p.w_k_bytes +
+                                            r * 128 + thread_channel * 2 + w_co0;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            if (i < b_copies) {
+                                cp_async_16(b_addr + 4096 * i, w_src, true);
+                                w_src += w_co_step;
+                            }
                         }
-                        if (next_tile < active) {
-                            load_vector(next_info.y, v0, v1);
+                        if ((p.c_out & 16) && q < 16) {
+                            cp_async_16(b_addr + 4096 * b_copies, w_src, true);
                         }
                     }
-                    for (int r = 0; r < reps; ++r) {
-                        if (!mbar_wait(&ctl.empty[ring.index], ring.phase ^ 1u, abort_flag, p.status)) {
+                    slab_issued();
+                    if (r == 0) {
+                        // The slot goes back to the loader only now: the copies above took
+                        // their addresses from the row ids, so every lane's reads of the slot
+                        // have returned before it can be overwritten.
+                        __syncwarp();
+                        if (lane == 0) {
+                            mbar_arrive(&ctl.vec_empty[vec.index]);
+                        }
+                        vec.advance(kVectorRing);
+                    }
+                }
+            }
+        } else {
+            // ---- general case: a slab may straddle two kernel offsets ----
+            // Unit u of a tile = (offset u / upo, 32-channel slice u % upo); slab s holds the
+            // units 2 s and 2 s + 1, this thread feeds unit 2 s + a_half. Ring entries are
+            // released in order once no later slab of any thread needs them: before slab s,
+            // everything below the entry of unit 2 s.
+            Ring released{0, 0u};   // next entry this thread has not released yet
+            auto release_until = [&](int count) -> bool {
+                for (int i = 0; i < count; ++i) {
+                    if (!wait_warp(&ctl.vec_full[released.index], released.phase)) {
+                        return false;
+                    }
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(&ctl.vec_empty[released.index]);
+                    }
+                    released.advance(kVectorRing);
+                }
+                return true;
+            };
+            while (ok) {
+                // `vec` is the first entry of the tile
+                if (!wait_warp(&ctl.vec_full[vec.index], vec.phase)) {
+                    ok = false;
+                    break;
+                }
+                const int32_t first = ctl.vec_header[vec.index];
+                if (first < 0) {
+                    break;
+                }
+                const int present = header_present(first);
+                const int units = present * upo;
+                const int slabs = (units + 1) >> 1;
+                int done = 0;        // entries of this tile already released
+                int held = -1;       // offset position whose row ids sit in v0, v1
+                int k = 0;
+                int4 v0 = make_int4(-1, -1, -1, -1), v1 = v0;
+                for (int s = 0; s < slabs && ok; ++s) {
+                    const int u = 2 * s + a_half;
+                    const bool uv = u < units;
+                    const int o = uv ? u / upo : 0;
+                    const int slice = u - o * upo;
+                    const int o_low = (2 * s) / upo;
+                    if (!release_until(o_low - done)) {
+                        ok = false;
+                        break;
+                    }
+                    done = o_low;
+                    {
+                        // The entry this lane reads (the lanes of the unused half of an odd
+                        // last slab wait on the slab's first entry, so that the whole warp
+                        // waits and decides together): up to two trips round the ring away.
+                        const int position = vec.index + (uv ? o : o_low);
+                        const int slot = position % kVectorRing;
+                        const uint32_t phase = vec.phase ^ static_cast<uint32_t>((position / kVectorRing) & 1);
+                        if (!wait_warp(&ctl.vec_full[slot], phase)) {
                             ok = false;
                             break;
                         }
-                        const uint32_t a_addr = smem_u32(smem + ring.index * p.stage_bytes) + dst0;
-                        const uint32_t b_addr = a_addr + kSlabBytesA;
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            cp_async_16(a_addr + 4096 * j, src[j] + r * 128, (valid >> j) & 1u);
+                        if (uv && o != held) {
+                            k = header_k(ctl.vec_header[slot]);
+                            read_vector(slot, v0, v1);
+                            held = o;
                         }
-                        if (p.b_tma) {
-                            if (tid == 0) {
-                                mbar_arrive_expect_tx(&ctl.full[ring.index],
-                                                      static_cast<uint32_t>(p.c_out) * 128u);
-                                tma_load_3d(b_addr - dst0, &b_map, r * 64, p.b_k_outer ? 0 : k,
-                                            p.b_k_outer ? k : 0, &ctl.full[ring.index]);
-                            }
-                        } else {
-                            const char* w_src = weight_bytes + static_cast<long long>(k) * p.w_k_bytes +
-                                                r * 128 + unit_bytes + w_co0;
+                    }
+                    const int idx[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                    const int channel = (uv ? slice : 0) * 32 + col8;
+                    int pitch;
+                    const char* const base = channel_base(channel, pitch);
+                    if (!acquire_stage()) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_addr = smem_u32(smem + ring.index * p.stage_bytes) + dst0;
+                    const uint32_t b_addr = a_addr + kSlabBytesA;
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                if (i < b_copies) {
-                                    cp_async_16(b_addr + 4096 * i, w_src, true);
-                                    w_src += w_co_step;
-                                }
-                            }
-                            if ((p.c_out & 16) && q < 16) {
-                                cp_async_16(b_addr + 4096 * b_copies, w_src, true);
-                            }
+                    for (int j = 0; j < 8; ++j) {
+                        // absent neighbours (and the unused half of an odd last slab) copy zero
+                        // bytes from a valid address: the destination is zero-filled
+                        const int in_row = uv ? idx[j] : -1;
+                        cp_async_16(a_addr + 4096 * j,
+                                    base + static_cast<long long>(max(in_row, 0)) * pitch, in_row >= 0);
+                    }
+                    const char* w_src = weight_bytes + static_cast<long long>(uv ? k : 0) * p.w_k_bytes +
+                                        channel * 2 + w_co0;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        if (i < b_copies) {
+                            cp_async_16(b_addr + 4096 * i, w_src, uv);
+                            w_src += w_co_step;
                         }
-                        cp_async_arrive_noinc(&ctl.full[ring.index]);
-                        ring.advance(p.stages);
                     }
-                }
-                tile = next_tile;
-                info = next_info;
-            }
-            cp_async_wait<0>();
-        } else {
-        // ---- general case: a slab may straddle two kernel offsets ----
-        int tile = blockIdx.x;
-        int2 info = load_info(p, tile, active);
-        int2 next_info = load_info(p, tile + grid, active);
-        int units = 0, s = 0, o = 0, slice = 0;
-        uint32_t rem = 0;
-        auto skip_empty_tiles = [&]() {
-            while (tile < active && info.x == 0) {
-                tile += grid;
-                info = next_info;
-                next_info = load_info(p, tile + grid, active);
-            }
-        };
-        auto enter_tile = [&]() {
-            units = __popc(static_cast<uint32_t>(info.x)) * upo;
-            s = 0;
-            o = 0;
-            slice = a_half;
-            rem = static_cast<uint32_t>(info.x);
-            while (slice >= upo) {
-                slice -= upo;
-                ++o;
-                rem &= rem - 1;
-            }
-        };
-        int4 i0 = make_int4(-1, -1, -1, -1), i1 = i0;
-        auto load_vector = [&](int4& v0, int4& v1) {
-            const int4* src = reinterpret_cast<const int4*>(
-                p.vectors + (static_cast<size_t>(info.y) + o) * kTileRows + q * 8);
-            v0 = __ldg(src);
-            v1 = __ldg(src + 1);
-        };
-        skip_empty_tiles();
-        if (tile < active) {
-            enter_tile();
-            if (a_half < units) {
-                load_vector(i0, i1);
-            }
-        }
-        while (tile < active) {
-            // ---- what this slab needs ----
-            const bool uv = 2 * s + a_half < units;
-            const int k = uv ? __ffs(rem) - 1 : 0;
-            const int col = (uv ? slice : 0) * 32 + col8;
-            const int idx[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
-            // ---- step the cursor and prefetch the next slab's row vector ----
-            const int prev_o = o;
-            bool moved = false;
-            ++s;
-            if (2 * s < units) {
-                slice += 2;
-                while (slice >= upo) {
-                    slice -= upo;
-                    ++o;
-                    rem &= rem - 1;
-                }
-            } else {
-                tile += grid;
-                info = next_info;
-                next_info = load_info(p, tile + grid, active);
-                skip_empty_tiles();
-                if (tile < active) {
-                    enter_tile();
-                }
-                moved = true;
-            }
-            int4 n0 = i0, n1 = i1;
-            if (tile < active && (moved || o != prev_o) && 2 * s + a_half < units) {
-                load_vector(n0, n1);
-            }
-            // ---- this slab's copies ----
-            if (!mbar_wait(&ctl.empty[ring.index], ring.phase ^ 1u, abort_flag, p.status)) {
-                ok = false;
-                break;
-            }
-            const uint32_t a_addr = smem_u32(smem + ring.index * p.stage_bytes) + dst0;
-            const uint32_t b_addr = a_addr + kSlabBytesA;
-            const char* const col_base = feat_bytes + col * 2;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                // absent neighbours (and the unused half of an odd last slab) copy zero
-                // bytes from a valid address: the destination is zero-filled
-                const int in_row = uv ? idx[j] : -1;
-                cp_async_16(a_addr + 4096 * j,
-                            col_base + static_cast<long long>(max(in_row, 0)) * feat_row_bytes,
-                            in_row >= 0);
-            }
-            if (p.b_tma) {
-                // both units of the slab share the offset k: the B tile is one box of
-                // C_out rows x 64 channels, fetched by the TMA unit (thread 0's unit is the
-                // slab's first, so its k and column are the box origin)
-                if (tid == 0) {
-                    mbar_arrive_expect_tx(&ctl.full[ring.index], static_cast<uint32_t>(p.c_out) * 128u);
-                    tma_load_3d(b_addr - dst0, &b_map, col, p.b_k_outer ? 0 : k, p.b_k_outer ? k : 0,
-                                &ctl.full[ring.index]);
-                }
-            } else {
-                const char* w_src =
-                    weight_bytes + static_cast<long long>(k) * p.w_k_bytes + col * 2 + w_co0;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    if (i < b_copies) {
-                        cp_async_16(b_addr + 4096 * i, w_src, uv);
-                        w_src += w_co_step;
+                    if (p.c_out & 16) {
+                        // C_out = 32 m + 16: the last 16 output channels
+                        if (q < 16) {
+                            cp_async_16(b_addr + 4096 * b_copies, w_src, uv);
+                        }
                     }
+                    slab_issued();
                 }
-                if (p.c_out & 16) {
-                    // C_out = 32 m + 16: the last 16 output channels
-                    if (q < 16) {
-                        cp_async_16(b_addr + 4096 * b_copies, w_src, uv);
-                    }
+                if (ok && !release_until(present - done)) {
+                    ok = false;
+                }
+                for (int i = 0; i < present; ++i) {
+                    vec.advance(kVectorRing);
                 }
             }
-            cp_async_arrive_noinc(&ctl.full[ring.index]);
-            ring.advance(p.stages);
-            i0 = n0;
-            i1 = n1;
         }
         cp_async_wait<0>();
-        }
+#ifdef LAT_TC_KNOBS
+        if (tid == 32) DBG_FLUSH(0);
+#endif
         for (int tile = blockIdx.x + ((active - blockIdx.x + grid - 1) / grid) * grid;
              tile < p.num_tiles; tile += grid) {
             if (producers_fill(tile, grid)) {
@@ -416,25 +496,38 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
         const int tile_row = half_tile * 128 + quarter * 32 + lane;
         bool ok = true;
         int local_tile = 0;
-        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += grid, ++local_tile) {
+        DBG_DECL;
+        // the output row and the offset mask of a tile are fetched one tile ahead
+        auto tile_output_row = [&](int tile) -> int {
             const int position = tile * kTileRows + tile_row;
-            int row = -1;
-            if (position < p.out_capacity) {
-                row = p.row_order != nullptr ? __ldg(p.row_order + position) : position;
-                if (row < 0 || row >= p.out_capacity) {
-                    raise_status(p.status, LAT_STATUS_BAD_INDEX);
-                    row = -1;
-                }
+            if (tile >= p.num_tiles || position >= p.out_capacity) {
+                return -1;
+            }
+            return p.row_order != nullptr ? __ldg(p.row_order + position) : position;
+        };
+        int next_row = tile_output_row(blockIdx.x);
+        int2 next_info = load_info(p, blockIdx.x, active);
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += grid, ++local_tile) {
+            int row = next_row;
+            const int2 info = next_info;
+            next_row = tile_output_row(tile + grid);
+            next_info = load_info(p, tile + grid, active);
+            if (row >= p.out_capacity || (row < 0 && tile * kTileRows + tile_row < p.out_capacity)) {
+                raise_status(p.status, LAT_STATUS_BAD_INDEX);
+                row = -1;
             }
             bool computed = false;
             int a = 0;
             if (tile < active) {
-                const int2 info = __ldg(p.tile_info + tile);
                 a = local_tile % p.acc_stages;
                 const uint32_t parity = (local_tile / p.acc_stages) & 1;
-                if (!mbar_wait(&ctl.acc_full[a], parity, abort_flag, p.status)) {
+                {
+                DBG_T0();
+                if (!wait_warp(&ctl.acc_full[a], parity)) {
                     ok = false;
                     break;
+                }
+                DBG_A();
                 }
                 tc_fence_after();
                 computed = info.x != 0;
@@ -446,7 +539,10 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                 }
                 if (tile < active) {
                     tc_fence_before();
-                    mbar_arrive(&ctl.acc_empty[a]);
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(&ctl.acc_empty[a]);
+                    }
                 }
                 continue;
             }
@@ -455,19 +551,16 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
             for (int c0 = 0; c0 < p.c_out; c0 += 32) {
                 uint32_t v[32];
                 const int width = min(32, p.c_out - c0);  // 32 or 16
-                if (computed) {
-                    if (width == 32) {
-                        tmem_load_32(taddr + c0, v);
-                    } else {
-                        tmem_load_16(taddr + c0, v);
-                    }
-                    tmem_load_wait();
+#ifdef LAT_TC_KNOBS
+                if (p.knobs & 64) break;
+                if ((p.knobs & 8) && row != 0) out_row = nullptr;
+#endif
+                if (width == 32) {
+                    tmem_load_32(taddr + c0, v);
                 } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        v[i] = 0u;
-                    }
+                    tmem_load_16(taddr + c0, v);
                 }
+                tmem_load_wait();
                 if (out_row != nullptr) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
@@ -490,65 +583,162 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                     }
                 }
             }
-            if (tile < active) {
-                tc_fence_before();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
                 mbar_arrive(&ctl.acc_empty[a]);
             }
         }
-    } else if (lane == 0) {
+#ifdef LAT_TC_KNOBS
+        if (tid == 256) DBG_FLUSH(8);
+#endif
+    } else if (warp == kMmaWarp) {
         // ======================= MMA issuer =======================
+        // Lane 0 issues; the warp as a whole fetches the offset masks of the CTA's next 32
+        // tiles in one load each, a batch ahead of their use.
         const uint32_t idesc = make_instr_desc(128, p.c_out);
+        const uint64_t desc0 = make_smem_desc(smem_u32(smem));
+        const uint32_t desc_lo0 = static_cast<uint32_t>(desc0);
+        const uint32_t desc_hi = static_cast<uint32_t>(desc0 >> 32);
+        const uint32_t stage_step = static_cast<uint32_t>(p.stage_bytes) >> 4;
         bool ok = true;
         Ring ring{0, 0u};
         int local_tile = 0;
-        int2 info = load_info(p, blockIdx.x, active);
-        for (int tile = blockIdx.x; tile < active && ok; tile += grid, ++local_tile) {
-            const int2 next_info = load_info(p, tile + grid, active);
-            const int a = local_tile % p.acc_stages;
-            const uint32_t parity = (local_tile / p.acc_stages) & 1;
-            if (!mbar_wait(&ctl.acc_empty[a], parity ^ 1, abort_flag, p.status)) {
-                ok = false;
-                break;
-            }
-            tc_fence_after();
-            const int slabs = (__popc(static_cast<uint32_t>(info.x)) * upo + 1) >> 1;
-            const uint32_t tmem_d0 = tmem_base + static_cast<uint32_t>(2 * a * p.acc_cols);
-            const uint32_t tmem_d1 = tmem_d0 + static_cast<uint32_t>(p.acc_cols);
-            for (int s = 0; s < slabs; ++s) {
-                if (!mbar_wait(&ctl.full[ring.index], ring.phase, abort_flag, p.status)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + ring.index * p.stage_bytes);
-                const uint64_t desc_a0 = make_smem_desc(a_addr);
-                const uint64_t desc_a1 = make_smem_desc(a_addr + 128 * 128);
-                const uint64_t desc_b = make_smem_desc(a_addr + kSlabBytesA);
+        DBG_DECL;
+        int2 batch = load_info(p, blockIdx.x + lane * grid, active);
+        for (int first = blockIdx.x; first < active && ok; first += 32 * grid) {
+            const int2 mine = batch;
+            batch = load_info(p, first + (32 + lane) * grid, active);
+            for (int j = 0; j < 32 && first + j * grid < active && ok; ++j, ++local_tile) {
+                const int mask = __shfl_sync(0xffffffffu, mine.x, j);
+                if (lane == 0) {
+                    const int a = local_tile % p.acc_stages;
+                    const uint32_t parity = (local_tile / p.acc_stages) & 1;
+                    {
+                    DBG_T0();
+                    if (!mbar_wait(&ctl.acc_empty[a], parity ^ 1, abort_flag, p.status, budget)) {
+                        ok = false;
+                    }
+                    DBG_A();
+                    }
+                    tc_fence_after();
+                    const int slabs = (__popc(static_cast<uint32_t>(mask)) * upo + 1) >> 1;
+                    const uint32_t tmem_d0 = tmem_base + static_cast<uint32_t>(2 * a * p.acc_cols);
+                    const uint32_t tmem_d1 = tmem_d0 + static_cast<uint32_t>(p.acc_cols);
+                    for (int s = 0; s < slabs && ok; ++s) {
+                        {
+                        DBG_T0();
+                        if (!mbar_wait(&ctl.full[ring.index], ring.phase, abort_flag, p.status, budget)) {
+                            ok = false;
+                            break;
+                        }
+                        DBG_B();
+                        }
+                        // the A rows were written by cp.async (generic proxy); the MMA reads
+                        // shared memory through the async proxy
+                        fence_proxy_async();
+                        tc_fence_after();
+                        // descriptors of the stage's operands: the address field is the low
+                        // 14 bits of the low word (16-byte units), everything else is fixed
+                        const uint32_t a_lo = desc_lo0 + static_cast<uint32_t>(ring.index) * stage_step;
+                        const uint32_t b_lo = a_lo + (kSlabBytesA >> 4);
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
-                    // 16 fp16 = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
-                    const uint32_t acc = (s | kk) != 0 ? 1u : 0u;
-                    umma_f16(tmem_d0, desc_a0 + 2 * kk, desc_b + 2 * kk, idesc, acc);
-                    umma_f16(tmem_d1, desc_a1 + 2 * kk, desc_b + 2 * kk, idesc, acc);
+                        for (int kk = 0; kk < 4; ++kk) {
+                            // 16 fp16 = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
+                            const uint32_t acc = kk != 0 ? 1u : (s != 0 ? 1u : 0u);
+#ifdef LAT_TC_KNOBS
+                            if ((p.knobs & 16) && (s | kk) != 0) continue;
+#endif
+                            umma_f16_split(tmem_d0, a_lo + 2 * kk, b_lo + 2 * kk, desc_hi, idesc, acc);
+                            umma_f16_split(tmem_d1, a_lo + (128 * 128 >> 4) + 2 * kk, b_lo + 2 * kk, desc_hi,
+                                           idesc, acc);
+                        }
+                        umma_commit(&ctl.empty[ring.index]);
+                        ring.advance(p.stages);
+                    }
+                    if (ok) {
+                        if (slabs > 0) {
+                            umma_commit(&ctl.acc_full[a]);
+                        } else {
+                            mbar_arrive(&ctl.acc_full[a]);
+                        }
+                    }
                 }
-                umma_commit(&ctl.empty[ring.index]);
-                ring.advance(p.stages);
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             }
-            if (!ok) {
-                break;
-            }
-            if (slabs > 0) {
-                umma_commit(&ctl.acc_full[a]);
-            } else {
-                mbar_arrive(&ctl.acc_full[a]);
-            }
-            info = next_info;
         }
+#ifdef LAT_TC_KNOBS
+        if (lane == 0) DBG_FLUSH(4);
+#endif
+    } else if (warp == kLoaderWarp) {
+        // ======================= row-vector loader =======================
+        // Streams the row vectors of this CTA's tiles, in the order the producers consume
+        // them, into a shared-memory ring by bulk copies, so that no producer ever waits on
+        // a global load of the plan. Lane 0 issues; the warp fetches offset masks in batches.
+        bool ok = true;
+        Ring vec{0, 0u};
+        DBG_DECL;
+        auto publish = [&](int32_t header, const int32_t* source) -> bool {
+            {
+            DBG_T0();
+            if (!mbar_wait(&ctl.vec_empty[vec.index], vec.phase ^ 1u, abort_flag, p.status, budget)) {
+                return false;
+            }
+            DBG_A();
+            }
+            ctl.vec_header[vec.index] = header;
+            if (source != nullptr) {
+                mbar_arrive_expect_tx(&ctl.vec_full[vec.index], kVectorBytes);
+                bulk_load(smem_u32(vec_ring + vec.index * kVectorBytes), source, kVectorBytes,
+                          &ctl.vec_full[vec.index]);
+            } else {
+                mbar_arrive(&ctl.vec_full[vec.index]);
+            }
+            vec.advance(kVectorRing);
+            return true;
+        };
+        int2 batch = load_info(p, blockIdx.x + lane * grid, active);
+        for (int first = blockIdx.x; first < active && ok; first += 32 * grid) {
+            const int2 mine = batch;
+            batch = load_info(p, first + (32 + lane) * grid, active);
+            for (int j = 0; j < 32 && first + j * grid < active && ok; ++j) {
+                const int mask = __shfl_sync(0xffffffffu, mine.x, j);
+                const int vector0 = __shfl_sync(0xffffffffu, mine.y, j);
+                if (lane == 0) {
+                    uint32_t rem = static_cast<uint32_t>(mask);
+                    const int present = __popc(rem);
+                    for (int o = 0; o < present && ok; ++o) {
+                        const int k = __ffs(rem) - 1;
+                        rem &= rem - 1;
+                        ok = publish(make_header(k, present),
+                                     p.vectors + (static_cast<size_t>(vector0) + o) * kTileRows);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            }
+        }
+        if (lane == 0 && ok) {
+            publish(-1, nullptr);
+        }
+#ifdef LAT_TC_KNOBS
+        if (lane == 0) DBG_FLUSH(10);
+#endif
     }
 
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+#ifdef LAT_TC_KNOBS
+    if (tid == 0) g_dbg[blockIdx.x * 16 + 12] += clock64() - dbg_kernel_t0;
+#endif
+    if (ctl.abort_flag != 0) {
+        // a role gave up: bulk copies towards this CTA's shared memory may still be in flight;
+        // they land within microseconds, and the CTA stays until they have
+        const long long start = clock64();
+        while (clock64() - start < 200000) {
+        }
+        __syncthreads();
+    }
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                      "r"(static_cast<uint32_t>(p.tmem_cols))
@@ -587,10 +777,30 @@ int pow2_at_least(int value, int floor_value) {
 
 } // namespace
 
+#ifdef LAT_TC_KNOBS
+extern "C" void lat_debug_dump(int reset) {
+    static long long host[148 * 16];
+    cudaDeviceSynchronize();
+    if (!reset) {
+        cudaMemcpyFromSymbol(host, g_dbg, sizeof(host));
+        double sum[16] = {0};
+        for (int b = 0; b < 148; ++b) for (int i = 0; i < 16; ++i) sum[i] += host[b * 16 + i];
+        const char* names[] = {"prod wait empty", "", "prod wait vec_full", "", "mma wait acc_empty", "", "mma wait full", "", "epi wait acc_full", "", "loader wait vec_empty", ""};
+        fprintf(stderr, "  kernel cycles/CTA %.0f\n", sum[12] / 148);
+        for (int i = 0; i < 12; i += 2) {
+            fprintf(stderr, "  %-22s total/CTA %10.0f  count/CTA %8.0f  avg %8.1f\n", names[i], sum[i] / 148, sum[i + 1] / 148, sum[i + 1] > 0 ? sum[i] / sum[i + 1] : 0.0);
+        }
+    }
+    memset(host, 0, sizeof(host));
+    cudaMemcpyToSymbol(g_dbg, host, sizeof(host));
+}
+#endif
+
 // fp16 weights only (packed weights are staged to fp16 by the caller); shapes as
-// tc_conv_supported allows them.
+// tc_conv_supported allows them. `feats2` (optional) holds the channels from `split` on.
 int run_tc_conv_plan(
-    const void* feats, int in_channels, long long feat_stride, const void* weights,
+    const void* feats, int in_channels, long long feat_stride, const void* feats2, int split,
+    long long feat2_stride, const void* weights,
     long long w_stride_k, long long w_stride_co, int n_kernels, int out_channels, int out_capacity,
     const void* bias, const int32_t* row_order, const void* plan, void* out, int32_t* status,
     cudaStream_t stream
@@ -603,6 +813,20 @@ int run_tc_conv_plan(
     LAT_REQUIRE(feat_stride > 0 && feat_stride * 2 < (1LL << 31),
                 "feature row stride is out of range for the tensor-core route.");
     p.feat_row_bytes = static_cast<int>(feat_stride * 2);
+    if (feats2 != nullptr) {
+        LAT_REQUIRE(split > 0 && split < in_channels && split % 8 == 0,
+                    "the channel split of a two-source convolution must be a multiple of 8 inside (0, C_in).");
+        LAT_REQUIRE(feat2_stride >= in_channels - split && feat2_stride % 8 == 0 &&
+                        feat2_stride * 2 < (1LL << 31) && reinterpret_cast<uintptr_t>(feats2) % 16 == 0,
+                    "second feature source must have 16-byte aligned rows of at least C_in - split channels.");
+        p.feats2 = static_cast<const __half*>(feats2);
+        p.feat2_row_bytes = static_cast<int>(feat2_stride * 2);
+        p.split = split;
+    } else {
+        p.feats2 = p.feats;
+        p.feat2_row_bytes = p.feat_row_bytes;
+        p.split = in_channels;
+    }
     p.c_in = in_channels;
     p.c_out = out_channels;
     p.weights = static_cast<const __half*>(weights);
@@ -611,21 +835,24 @@ int run_tc_conv_plan(
     p.num_tiles = plan_tiles(out_capacity);
     p.tile_info = static_cast<const int2*>(plan);
     p.vectors = reinterpret_cast<const int32_t*>(static_cast<const char*>(plan) + plan_info_bytes(p.num_tiles));
+    LAT_REQUIRE(reinterpret_cast<uintptr_t>(p.vectors) % 16 == 0, "plan must be a 16-byte aligned device buffer.");
     p.row_order = row_order;
     p.out_capacity = out_capacity;
     p.bias = static_cast<const __half*>(bias);
     p.out = static_cast<__half*>(out);
     p.status = status;
+    p.wait_budget = wait_budget_cycles();
     p.acc_cols = pow2_at_least(out_channels, 32);
     p.acc_stages = std::min(kMaxAccStages, 512 / (2 * p.acc_cols));
     p.tmem_cols = p.acc_stages * 2 * p.acc_cols;
     // every B tile on a 1024-byte boundary (the swizzle pattern repeats every eight rows)
     p.stage_bytes = kSlabBytesA + static_cast<int>(align_up(static_cast<size_t>(out_channels) * 128, 1024));
     const int ctl_bytes = static_cast<int>(align_up(sizeof(Control), 16));
-    const int smem_budget = 227 * 1024 - 1024 /*alignment slack*/ - ctl_bytes;
+    const int ring_bytes = kVectorRing * kVectorBytes;
+    const int smem_budget = 227 * 1024 - 1024 /*alignment slack*/ - ring_bytes - ctl_bytes;
     p.stages = std::min(kMaxStages, smem_budget / p.stage_bytes);
     LAT_REQUIRE(p.stages >= 2, "internal: shared-memory plan leaves no room for the stage ring.");
-    const size_t smem_bytes = 1024 + static_cast<size_t>(p.stages) * p.stage_bytes + ctl_bytes;
+    const size_t smem_bytes = 1024 + static_cast<size_t>(p.stages) * p.stage_bytes + ring_bytes + ctl_bytes;
 
     int device = 0;
     LAT_CUDA_CHECK(cudaGetDevice(&device));
@@ -657,6 +884,14 @@ int run_tc_conv_plan(
             p.b_k_outer = k_outer ? 1 : 0;
         }
     }
+#ifdef LAT_TC_KNOBS
+    {
+        const char* knob = getenv("LAT_TC_KNOB");
+        p.knobs = knob != nullptr ? atoi(knob) : 0;
+        const char* st = getenv("LAT_TC_STAGES");
+        if (st != nullptr) p.stages = std::min(p.stages, atoi(st));
+    }
+#endif
     tc_conv_plan_kernel<<<grid, kThreads, smem_bytes, stream>>>(p, b_map);
     LAT_LAUNCH_CHECK();
     return LAT_OK;

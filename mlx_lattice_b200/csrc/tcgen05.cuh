@@ -36,22 +36,42 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return done != 0;
 }
 
+// The same test, but the thread may sleep in it (issuing nothing) until the phase completes
+// or about `nanoseconds` have passed: a waiting warp then leaves the issue slots of its
+// scheduler to the warps that have work.
+__device__ __forceinline__ bool mbar_try_wait_sleeping(uint64_t* bar, uint32_t parity, uint32_t nanoseconds) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(nanoseconds)
+        : "memory");
+    return done != 0;
+}
+
+constexpr uint32_t kWaitSleepNs = 20000;
+
 // Bounded wait: returns false (and raises the abort flag) when the clock budget is
 // spent or another role already aborted.
 __device__ __forceinline__ bool
-mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
+mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+          long long budget = kWaitBudgetCycles) {
     if (mbar_try_wait(bar, parity)) {
         return true;
     }
     long long start = clock64();
     while (true) {
-        if (mbar_try_wait(bar, parity)) {
+        if (mbar_try_wait_sleeping(bar, parity, kWaitSleepNs)) {
             return true;
         }
         if (*abort_flag != 0) {
             return false;
         }
-        if (clock64() - start > kWaitBudgetCycles) {
+        if (clock64() - start > budget) {
             *abort_flag = 1;
             raise_status(status, LAT_STATUS_WAIT_TIMEOUT);
             return false;
@@ -90,8 +110,21 @@ __device__ __forceinline__ void tma_load_3d(
         : "memory");
 }
 
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of
+// 16 bytes); completion is counted in bytes on `bar`. No multicast.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
 __device__ __forceinline__ void prefetch_l1(const void* ptr) {
     asm volatile("prefetch.global.L1 [%0];" ::"l"(ptr));
+}
+
+__device__ __forceinline__ void cp_async_commit() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
 template <int N> __device__ __forceinline__ void cp_async_wait() {
@@ -151,6 +184,26 @@ umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint
         : "memory");
 }
 
+// The same MMA with both descriptors given as (low word, shared high word): the low word
+// holds the operand's address field, so stepping an operand is a 32-bit add.
+__device__ __forceinline__ void umma_f16_split(
+    uint32_t tmem_d, uint32_t desc_a_lo, uint32_t desc_b_lo, uint32_t desc_hi, uint32_t idesc,
+    uint32_t accumulate
+) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+        "}"
+        :
+        : "r"(tmem_d), "r"(desc_a_lo), "r"(desc_b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                      smem_u32(bar))
@@ -188,6 +241,17 @@ __device__ __forceinline__ void tmem_load_wait() {
 
 // Loads whose issue point must stay where it is written (a prefetch one pipeline step
 // ahead of its use): volatile asm is not moved across the surrounding memory operations.
+// 16 bytes of shared memory; volatile, so that neither compiler stage moves the read
+// across the barrier operations around it
+__device__ __forceinline__ int4 lds_v4_pinned(uint32_t addr) {
+    int4 v;
+    asm volatile("ld.volatile.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(addr)
+                 : "memory");
+    return v;
+}
+
 __device__ __forceinline__ uint32_t ldg_u32_pinned(const uint32_t* ptr) {
     uint32_t v;
     asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");

@@ -23,18 +23,34 @@ def _conv_plan(relation: KernelRelation, uses_tensor_cores: bool, in_rows: int):
     return relation.require_conv_plan()
 
 
+def _sources(feats, relation: KernelRelation, uses_tensor_cores: bool):
+    """``feats`` is one array or a pair over the same rows (an unwritten channel
+    concatenation). The tensor-core route with a gather plan reads a pair in place when the
+    first part's channel count is a multiple of 8; otherwise the pair is concatenated."""
+    if not isinstance(feats, tuple):
+        return feats, None
+    first, second = feats
+    in_place = (uses_tensor_cores and relation.n_in_capacity == int(first.shape[0])
+                and int(first.shape[1]) % 8 == 0)
+    if in_place:
+        return first, second
+    return _ext.concat_aligned_features(first, None, second, None), None
+
+
 def sparse_quantized_conv_features_from_relation(
-    feats: torch.Tensor, weight: QuantizedWeight, relation: KernelRelation, bias=None
+    feats, weight: QuantizedWeight, relation: KernelRelation, bias=None
 ) -> torch.Tensor:
     """Quantized sparse convolution over a prebuilt relation (``:19-61``)."""
     if relation.n_out_capacity is None or relation.n_kernels is None:
         raise ValueError('kernel relation is missing static shape metadata.')
     if relation.n_kernels != weight.weight.shape[0]:
         raise ValueError('quantized weight kernel rows must match the relation.')
+    dtype = feats[0].dtype if isinstance(feats, tuple) else feats.dtype
     tc = _ext.conv_uses_tensor_cores(
-        feats.dtype, relation.n_kernels, weight.in_channels, weight.out_channels,
+        dtype, relation.n_kernels, weight.in_channels, weight.out_channels,
         weight.bits, weight.group_size,
     )
+    feats, feats2 = _sources(feats, relation, tc)
     return _ext.sparse_quantized_conv_features(
         feats,
         weight.weight,
@@ -58,19 +74,23 @@ def sparse_quantized_conv_features_from_relation(
         bias=bias,
         row_order=_row_order(relation, tc),
         plan=_conv_plan(relation, tc, int(feats.shape[0])),
+        feats2=feats2,
     )
 
 
 def sparse_conv_features_from_relation(
-    feats: torch.Tensor, weight: torch.Tensor, relation: KernelRelation, bias=None
+    feats, weight: torch.Tensor, relation: KernelRelation, bias=None
 ) -> torch.Tensor:
     """Float sparse convolution over a prebuilt relation (``:84-116``)."""
     if relation.n_out_capacity is None or relation.n_kernels is None:
         raise ValueError('kernel relation is missing static shape metadata.')
     c_out = int(weight.shape[2] if weight.ndim == 3 else weight.shape[0])
+    pair = isinstance(feats, tuple)
     tc = _ext.conv_uses_tensor_cores(
-        feats.dtype, relation.n_kernels, int(feats.shape[1]), c_out
+        feats[0].dtype if pair else feats.dtype, relation.n_kernels,
+        int(feats[0].shape[1] + feats[1].shape[1]) if pair else int(feats.shape[1]), c_out
     )
+    feats, feats2 = _sources(feats, relation, tc)
     return _ext.sparse_conv_features(
         feats,
         weight,
@@ -84,6 +104,7 @@ def sparse_conv_features_from_relation(
         bias=bias,
         row_order=_row_order(relation, tc),
         plan=_conv_plan(relation, tc, int(feats.shape[0])),
+        feats2=feats2,
     )
 
 

@@ -151,19 +151,17 @@ def _relation_conv(
     reuse_input_coords: bool = False,
     target_key: CoordinateMapKey | None = None,
 ) -> SparseTensor:
-    _validate_feature_dtype(x.feats, weight)
+    _validate_feature_dtype(x, weight)
     if x.coords.dtype != torch.int32:
         raise ValueError('CUDA sparse convolution requires int32 coordinates.')
     _validate_weight_for_kernel(x, weight, spec.volume)
-    _validate_bias(bias, weight, x.feats.dtype)
+    _validate_bias(bias, weight, x.dtype)
     relation = _kernel_relation(x, spec, map_kind, target_key=target_key)
     if relation.n_out_capacity is None or relation.n_kernels is None:
         raise ValueError('kernel relation is missing static shape metadata.')
-    feats = (
-        sparse_quantized_conv_features_from_relation(x.feats, weight, relation, bias)
-        if isinstance(weight, QuantizedWeight)
-        else sparse_conv_features_from_relation(x.feats, weight, relation, bias)
-    )
+    run = (sparse_quantized_conv_features_from_relation if isinstance(weight, QuantizedWeight)
+           else sparse_conv_features_from_relation)
+    feats = run(x.feat_parts or x.feats, weight, relation, bias)
     if reuse_input_coords:
         return x.replace(feats=feats)
     if relation.out_coords is None:
@@ -241,7 +239,7 @@ def _target_key(x: SparseTensor, coordinates, output_stride: Triple) -> Coordina
 
 def _pointwise_features(x: SparseTensor, weight, bias) -> torch.Tensor:
     _validate_feature_dtype(x.feats, weight)
-    _validate_bias(bias, weight, x.feats.dtype)
+    _validate_bias(bias, weight, x.dtype)
     if isinstance(weight, QuantizedWeight):
         return quantized_matmul(x.feats, weight, bias)
     return _ext.linear(x.feats, _pointwise_weight_matrix(x, weight), bias)

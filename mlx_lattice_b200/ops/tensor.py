@@ -67,10 +67,12 @@ def align_sparse(lhs: SparseTensor, rhs: SparseTensor, *, join: str = 'inner') -
 def sparse_cat_aligned(lhs: SparseTensor, rhs: SparseTensor, *, join: str = 'inner') -> SparseTensor:
     """Concatenate the channels of two sparse tensors after coordinate-value
     alignment; tensors that share coordinate identity are concatenated directly
-    (``ops/tensor.py:228-249``). One gather-and-concatenate kernel either way."""
+    (``ops/tensor.py:228-249``). One gather-and-concatenate kernel either way; for tensors
+    of one coordinate identity that kernel runs only when ``feats`` of the result is read
+    (a tensor-core convolution reads the two parts in place instead)."""
     _require_compatible(lhs, rhs)
     if lhs.same_coords(rhs):
-        return lhs.replace(feats=_ext.concat_aligned_features(lhs.feats, None, rhs.feats, None))
+        return lhs.replace(feats=(lhs.feats, rhs.feats))
     alignment = align_sparse(lhs, rhs, join=join)
     return SparseTensor(
         alignment.coords,

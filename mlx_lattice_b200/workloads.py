@@ -137,80 +137,3 @@ def minkunet_inputs(config_index: int, batch: int, per_cloud: int, first_batch: 
     rng = np.random.default_rng(synthetic.cloud_seed(config_index, first_batch) + 500000)
     feats = rng.uniform(0.0, 1.0, size=(coords.shape[0], INPUT_CHANNELS)).astype(np.float16)
     return coords, feats
-
-
-# --------------------------------------------------------------------------- #
-# single-kernel cases (python -m mlx_lattice_b200.workloads ...), used for profiling
-# --------------------------------------------------------------------------- #
-
-
-def dense_cloud(rows: int, seed: int = 7) -> np.ndarray:
-    """A compact cloud (~45 % occupancy of a cube, ~12 of 27 neighbours per voxel), the
-    regime of the coarse U-Net levels."""
-    side = int(np.ceil((rows / 0.45) ** (1.0 / 3.0)))
-    rng = np.random.default_rng(seed)
-    cells = rng.permutation(side ** 3)[:rows]
-    xyz = np.stack([cells // (side * side), (cells // side) % side, cells % side], axis=1)
-    return np.concatenate([np.zeros((rows, 1), np.int64), xyz], axis=1).astype(np.int32)
-
-
-def _case_main() -> None:
-    import argparse
-
-    from mlx_lattice_b200 import _ext
-
-    parser = argparse.ArgumentParser(description='run one kernel of the hot path repeatedly')
-    parser.add_argument('case', choices=('conv', 'map'))
-    parser.add_argument('--rows', type=int, default=150000)
-    parser.add_argument('--cin', type=int, default=256)
-    parser.add_argument('--cout', type=int, default=256)
-    parser.add_argument('--bits', type=int, default=4, help='0 = fp16 weights')
-    parser.add_argument('--cloud', default='dense', choices=('dense', 'lidar'))
-    parser.add_argument('--stride', type=int, default=1)
-    parser.add_argument('--iters', type=int, default=3)
-    args = parser.parse_args()
-
-    device = torch.device('cuda', 0)
-    if args.cloud == 'dense':
-        coords_np = dense_cloud(args.rows)
-    else:
-        coords_np = synthetic.lidar_batch(2, max(1, args.rows // 125000), min(args.rows, 125000))
-    coords = torch.from_numpy(coords_np).to(device)
-    n = coords.shape[0]
-    if args.case == 'map':
-        active = torch.tensor([n], dtype=torch.int32, device=device)
-        for _ in range(args.iters):
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            base, _, _ = _ext.build_kernel_relation_base(coords, active, 3, args.stride, 0, 1)
-            end.record()
-            torch.cuda.synchronize()
-            print(f'map rows={n} stride={args.stride} counts={base[5].tolist()} '
-                  f'ms={start.elapsed_time(end):.3f}')
-        return
-    rng = np.random.default_rng(3)
-    feats = torch.from_numpy(rng.normal(size=(n, args.cin)).astype(np.float16)).to(device)
-    dense = (rng.normal(size=(args.cout, 3, 3, 3, args.cin)) * 0.05).astype(np.float16)
-    weight = torch.from_numpy(dense)
-    if args.bits:
-        weight = quantized_to(quantize_weight(weight, group_size=32, bits=args.bits), device)
-    else:
-        weight = weight.to(device)
-    x = SparseTensor(coords, feats)
-    for _ in range(args.iters):
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        y = ops.subm_conv3d(x, weight, kernel_size=3)
-        end.record()
-        torch.cuda.synchronize()
-        rel = x.coord_manager.submanifold_kernel_relation(x.coord_key, kernel_size=3)
-        edges = rel.counts.tolist()[0]
-        ms = start.elapsed_time(end)
-        print(f'conv rows={n} cin={args.cin} cout={args.cout} bits={args.bits} edges={edges} '
-              f'ms={ms:.3f} tflops={2.0 * edges * args.cin * args.cout / ms / 1e9:.1f}')
-    _ext.check_status(device)
-    del y
-
-
-if __name__ == '__main__':
-    _case_main()

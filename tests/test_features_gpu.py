@@ -361,3 +361,47 @@ def test_global_pool_linear_batchnorm(cuda, restatement):
         1e-5, True).cpu().numpy()
     assert _max_rel_err(got, want) <= FP16_TOL
     assert np.array_equal(_ext.relu(_dev(x16, cuda)).cpu().numpy(), restatement.relu(x16))
+
+
+@pytest.mark.parametrize('c_first,c_second,c_out', [(128, 128, 128), (64, 64, 64), (32, 32, 32),
+                                                   (32, 64, 32), (64, 32, 48), (8, 24, 16)])
+def test_two_source_conv_equals_conv_of_concatenation(cuda, oracle, sphere, c_first, c_second, c_out):
+    """A convolution that reads the channel concatenation of two tensors in place
+    (`feats2`) gives the bits of the same convolution over the written concatenation,
+    and stays within the fp16 tolerance of the oracle."""
+    from mlx_lattice_b200 import _ext
+
+    coords, rel = sphere
+    n = coords.shape[0]
+    rng = np.random.default_rng(c_first * 31 + c_second)
+    first = rng.normal(size=(n, c_first)).astype(np.float16)
+    second = rng.normal(size=(n, c_second)).astype(np.float16)
+    both = np.concatenate([first, second], axis=1)
+    w5 = (rng.normal(size=(c_out, 3, 3, 3, c_first + c_second)) * 0.05).astype(np.float16)
+    r = _rel_dev(rel, cuda)
+    plan = _plan(cuda, r, n, n, 27, None)
+    args = (r['in_rows'], r['out_rows'], r['kernel_ids'], r['counts'], r['row_offsets'])
+    joined = _ext.sparse_conv_features(_dev(both, cuda), _dev(w5, cuda), *args, out_capacity=n,
+                                       n_kernels=27, plan=plan).cpu().numpy()
+    # the second source as a strided view: rows of a wider array
+    wide = _dev(np.concatenate([second, second], axis=1), cuda)[:, :c_second]
+    in_place = _ext.sparse_conv_features(_dev(first, cuda), _dev(w5, cuda), *args, out_capacity=n,
+                                         n_kernels=27, plan=plan, feats2=wide).cpu().numpy()
+    assert np.array_equal(in_place, joined)
+    exact = oracle.sparse_conv(both.astype(np.float32), w5.astype(np.float32), rel, n, 27)
+    assert _max_rel_err(in_place, exact) <= FP16_TOL
+    _ext.check_status(cuda)
+
+
+def test_two_source_conv_needs_a_plan(cuda, sphere):
+    from mlx_lattice_b200 import _ext
+
+    coords, rel = sphere
+    n = coords.shape[0]
+    r = _rel_dev(rel, cuda)
+    feats = torch.zeros((n, 32), dtype=torch.float16, device=cuda)
+    weights = torch.zeros((32, 3, 3, 3, 64), dtype=torch.float16, device=cuda)
+    with pytest.raises(ValueError, match='second feature source'):
+        _ext.sparse_conv_features(feats, weights, r['in_rows'], r['out_rows'], r['kernel_ids'],
+                                  r['counts'], r['row_offsets'], out_capacity=n, n_kernels=27,
+                                  feats2=feats)

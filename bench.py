@@ -2,15 +2,19 @@
 
     python bench.py --gpus N --steps K --warmup W            # this implementation
     python bench.py --impl reference --steps K --warmup W    # reference CPU route
+    python bench.py --case conv:3:128:128 --clouds 1         # one kernel, for profiling
 
-Workload (config 4 of the baseline): MinkUNet-style int4 inference on 8 clouds of
-120,000 voxels per GPU (LiDAR-like synthetic generator, seeded), kernel maps rebuilt
-in every step ("cold"). One step = one forward pass over the batch. With N > 1 every
-rank runs its own 8-cloud batch (independent clouds shard with no data-path
-collective): weak scaling, value = voxels of all ranks / max-over-ranks time.
+Workload (config 4 of the baseline): MinkUNet-style int4 inference on ONE batch of 8
+clouds of 120,000 voxels (LiDAR-like synthetic generator, seeded), kernel maps rebuilt in
+every step ("cold"). One step = one forward pass over the batch. With N > 1 the 8 clouds
+are divided over the ranks by batch element (8/4/2/1 clouds per GPU, no data-path
+collective): strong scaling, value = 960,000 voxels * K / max-over-ranks time. The weak
+figure (every rank a full batch of its own) is the extra key `weak_scaling`.
 
-Prints ONE JSON line on rank 0 (see the keys below). Timing: CUDA events on the
-stream the kernels are launched on, L2 flushed between steps, max over ranks.
+Prints ONE JSON line on rank 0. Timing: CUDA events on the stream the kernels are launched
+on, L2 flushed between steps, max over ranks. The headline steps are CUDA-graph replays
+of the whole forward pass; the per-launch roofline figures come from a second, eager pass
+over the same steps.
 """
 
 from __future__ import annotations
@@ -107,93 +111,91 @@ class ClockSampler:
         }
 
 
-def quantized_to_numpy(q) -> dict:
-    """Package QuantizedWeight (CPU tensors) -> the dict form the oracle consumes."""
-    return {
-        'weight': q.weight.numpy().view(np.uint32),
-        'scales': q.scales.numpy(),
-        'biases': q.biases.numpy(),
-        'group_size': q.group_size,
-        'bits': q.bits,
-        'in_channels': q.in_channels,
-        'out_channels': q.out_channels,
-        'kernel_size': q.kernel_size,
-        'layout': q.layout,
-        'storage_in_channels': q.storage_in_channels,
-    }
-
-
 # --------------------------------------------------------------------------- #
 # reference CPU route (the checker, timed as a reported baseline)
 # --------------------------------------------------------------------------- #
 
 
-def cpu_reference_step(sample_voxels: int, cloud_index: int = 0) -> dict:
+def cpu_reference_step(voxels: int, cloud_index: int = 0) -> dict:
     """One forward of the same network through the reference's own CPU code
-    (oracle/_ref when it was built, else the numpy port) on a bounded sample: the
-    first `sample_voxels` voxels of one cloud of the workload."""
-    import torch
-
+    (oracle/_ref when it was built, else the numpy port) over the first `voxels` voxels
+    of cloud `cloud_index` of the workload; voxels = PER_CLOUD is one whole cloud. Clouds
+    are independent (the batch id is part of every coordinate key), so the cost per voxel
+    of one whole cloud is the cost per voxel of the batch."""
     from mlx_lattice_b200 import workloads
     from oracle import pipeline, reference, restatement
 
     backend = reference if reference.available() else restatement
     kind = 'reference' if reference.available() else 'port'
     coords, feats = workloads.minkunet_inputs(CONFIG_INDEX, 1, PER_CLOUD, first_batch=cloud_index)
-    coords, feats = coords[:sample_voxels], feats[:sample_voxels]
+    coords, feats = coords[:voxels], feats[:voxels]
     dense = workloads.minkunet_dense_weights(WEIGHT_SEED)
-    quantized = {k: quantized_to_numpy(v) for k, v in workloads.quantize_all(dense).items()}
+    quantized = {k: pipeline.quantized_to_numpy(v) for k, v in workloads.quantize_all(dense).items()}
     timings: dict = {}
     start = time.perf_counter()
     logits = pipeline.minkunet_forward(
         backend, coords, feats, quantized, workloads.minkunet_layers(), timings)
     seconds = time.perf_counter() - start
     cores = os.cpu_count() or 1
+    whole = 'one whole cloud' if voxels >= PER_CLOUD else f'the first {voxels} voxels of one cloud'
     return {
-        'value': sample_voxels / seconds,
+        'value': coords.shape[0] / seconds,
         'unit': 'voxels/s',
         'cores': cores if kind == 'reference' else 1,
         'kind': kind,
-        'sample': f'{sample_voxels} voxels of cloud {cloud_index} (1 forward, kernel maps rebuilt), '
-                  f'{seconds:.2f} s; conv {timings.get("conv", 0.0):.2f} s, '
+        'sample': f'{whole} of the workload ({coords.shape[0]} voxels, cloud {cloud_index}; 1 forward, '
+                  f'kernel maps rebuilt), {seconds:.2f} s; conv {timings.get("conv", 0.0):.2f} s, '
                   f'maps {timings.get("relation", 0.0):.2f} s',
         'seconds': seconds,
+        'voxels': int(coords.shape[0]),
         'checksum': float(np.abs(logits.astype(np.float32)).sum()),
-        'torch_threads': torch.get_num_threads(),
     }
 
 
+REFERENCE_ARM_BUDGET_S = 240.0
+
+
 def run_reference_arm(args) -> None:
+    """Rank 0 times the reference CPU route: one untimed pass over a small sample to page the
+    library in, then whole clouds of the workload (120,000 voxels each, clouds 0, 1, ..), one
+    per timed step, until `--steps` steps are done or the time budget is spent (a whole cloud
+    takes tens of seconds on the host's cores)."""
     rank = int(os.environ.get('RANK', '0'))
     if rank != 0:
         return
-    sample = args.cpu_sample
-    times = []
-    last = None
-    for i in range(args.warmup + args.steps):
-        last = cpu_reference_step(sample)
-        if i >= args.warmup:
-            times.append(last['seconds'])
-    mean = sum(times) / len(times)
-    value = sample / mean
+    cpu_reference_step(4000)
+    seconds, voxels, last = 0.0, 0, None
+    steps = 0
+    while steps < max(args.steps, 1):
+        last = cpu_reference_step(PER_CLOUD, cloud_index=steps % BATCH)
+        seconds += last['seconds']
+        voxels += last['voxels']
+        steps += 1
+        if seconds + last['seconds'] > REFERENCE_ARM_BUDGET_S:
+            break
+    value = voxels / seconds
     line = {
         'impl': 'reference',
         'metric': METRIC,
         'value': value,
         'unit': 'voxels/s',
         'n_gpus': args.gpus,
-        'steps': args.steps,
-        'warmup': args.warmup,
-        'ms_per_step': mean * 1e3,
+        'steps': steps,
+        'steps_requested': args.steps,
+        'warmup': 1,
+        'ms_per_step': seconds / steps * 1e3,
         'higher_is_better': True,
-        'scaling': 'weak',
+        'scaling': 'strong',
         'vs_baseline': None,
         'dtype': 'f16',
         'data': 'synthetic',
-        'config': {'workload': 'minkunet_int4_8x120k_lidar (bounded sample per step)',
-                   'sample_voxels': sample},
+        'config': {'workload': 'minkunet_int4_8x120k_lidar, one whole 120,000-voxel cloud per step '
+                               '(clouds are independent: voxels/s of a cloud is voxels/s of the batch)',
+                   'voxels_per_step': PER_CLOUD,
+                   'time_budget_s': REFERENCE_ARM_BUDGET_S},
         'cpu_baseline': {'value': value, 'unit': 'voxels/s', 'cores': last['cores'],
-                         'kind': last['kind'], 'sample': last['sample']},
+                         'kind': last['kind'],
+                         'sample': f'{steps} step(s) of one whole cloud each; last: ' + last['sample']},
         'e2e': {'value': value, 'unit': 'voxels/s', 'h2d_bytes_per_step': 0,
                 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
@@ -205,8 +207,25 @@ def run_reference_arm(args) -> None:
 # this implementation
 # --------------------------------------------------------------------------- #
 
+# DRAM bytes of a convolution launch over its algorithmic bytes, from ncu captures of two
+# layers of the benchmark network on LiDAR-like clouds (profiles/tc_conv_plan_kernel_lidar_*):
+# dram__bytes_read + dram__bytes_write divided by A_in*C_in*2 + N_out*C_out*2 + W + 8E.
+DRAM_OVER_ALGORITHMIC = {'wide': 1.0, 'narrow': 1.0}
 
-DRAM_READ_PER_GATHER_BYTE = 0.56  # dram__bytes_read / (E * C_in * 2), ncu, both captured cases
+
+def conv_algorithmic(info, counts) -> tuple[float, float]:
+    """(flops, bytes) of one convolution launch: 2*E*C_in*C_out over real edges; bytes =
+    active input rows * C_in * s + N_out * C_out * s + weights + 8 bytes per edge."""
+    edges, n_out = counts
+    c_in, c_out, k = info['c_in'], info['c_out'], info['n_kernels']
+    weight_bytes = (k * c_in * c_out * info['bits'] / 8 + 2 * k * (c_in / 32) * c_out * 2
+                    if info['bits'] else k * c_in * c_out * 2)
+    flops = 2.0 * edges * c_in * c_out
+    # input rows read: the output's own rows for a submanifold map; every edge's row for a
+    # kernel-2 stride-2 map (one edge per input); at most the output rows for its transpose
+    rows_in = n_out if k == 27 or edges <= n_out else min(edges, info['in_rows'])
+    bytes_ = rows_in * c_in * 2 + n_out * c_out * 2 + weight_bytes + 8 * edges
+    return flops, bytes_
 
 
 class ConvProfile:
@@ -218,83 +237,112 @@ class ConvProfile:
     def __call__(self, kind, info, start, end) -> None:
         self.records.append((info, start, end))
 
+    def layers(self, peaks: dict, steps: int) -> list[dict]:
+        """Per layer shape (kernel volume, C_in, C_out, edges): launches, mean time, and the
+        fraction of BOTH roofs, with the one that binds named."""
+        groups: dict = {}
+        for info, start, end in self.records:
+            counts = tuple(info['counts'].tolist())
+            key = (info['n_kernels'], info['c_in'], info['c_out'], counts[0], bool(info['tensor_cores']))
+            entry = groups.setdefault(key, {'ms': 0.0, 'launches': 0, 'info': info, 'counts': counts})
+            entry['ms'] += start.elapsed_time(end)
+            entry['launches'] += 1
+        out = []
+        for (k, c_in, c_out, edges, tc), entry in groups.items():
+            flops, bytes_ = conv_algorithmic(entry['info'], entry['counts'])
+            ms = entry['ms'] / entry['launches']
+            tflops = flops / ms / 1e9
+            gbs = bytes_ / ms / 1e6
+            frac_tensor = tflops / peaks['bf16_tflops_sustained']
+            frac_hbm = gbs / peaks['hbm_gbs']
+            # the roof a perfect kernel would hit first is the one with the longer minimum time
+            t_tensor = flops / (peaks['bf16_tflops_sustained'] * 1e12)
+            t_hbm = bytes_ / (peaks['hbm_gbs'] * 1e9)
+            out.append({
+                'layer': f'K{k} {c_in}->{c_out}', 'route': 'tcgen05' if tc else 'cuda cores',
+                'edges': edges, 'out_rows': entry['counts'][1],
+                'launches_per_step': entry['launches'] / steps, 'ms': ms,
+                'tflops': tflops, 'frac_tensor': frac_tensor, 'gb_s': gbs, 'frac_hbm': frac_hbm,
+                'bound': 'tensor' if t_tensor >= t_hbm else 'hbm',
+                'frac': frac_tensor if t_tensor >= t_hbm else frac_hbm,
+            })
+        out.sort(key=lambda e: -e['ms'] * e['launches_per_step'])
+        return out
+
     def summarize(self, tensor_cores: bool) -> dict:
-        """Algorithmic flops (2 * E * C_in * C_out, real edges only) and bytes of the
-        launches on one route, with their summed event durations."""
-        flops = 0.0
-        bytes_ = 0.0
-        dram = 0.0
-        ms = 0.0
+        flops = bytes_ = ms = 0.0
         launches = 0
         for info, start, end in self.records:
             if bool(info['tensor_cores']) != tensor_cores:
                 continue
-            counts = info['counts'].tolist()
-            edges, n_out = counts[0], counts[1]
-            c_in, c_out, k = info['c_in'], info['c_out'], info['n_kernels']
-            flops += 2.0 * edges * c_in * c_out
-            weight_bytes = (k * c_in * c_out * info['bits'] / 8 + 2 * k * (c_in / 32) * c_out * 2
-                            if info['bits'] else k * c_in * c_out * 2)
-            bytes_ += info['in_rows'] * c_in * 2 + n_out * c_out * 2 + weight_bytes + 8 * edges
-            # DRAM bytes of a launch, from ncu captures of this kernel on two smaller cases
-            # (profiles/tc_conv_plan_kernel_dense_256x256_and_128x128.md): reads are 0.56 x
-            # the gathered feature bytes in both (L2 absorbs the rest), writes are the output
-            dram += DRAM_READ_PER_GATHER_BYTE * edges * c_in * 2 + n_out * c_out * 2
+            f, b = conv_algorithmic(info, info['counts'].tolist())
+            flops += f
+            bytes_ += b
             ms += start.elapsed_time(end)
             launches += 1
-        return {'flops': flops, 'bytes': bytes_, 'dram': dram, 'ms': ms, 'launches': launches}
+        return {'flops': flops, 'bytes': bytes_, 'ms': ms, 'launches': launches}
 
 
-def kernel_map_benchmark(device, steps: int, peaks: dict) -> dict:
+def event_timed(fn, steps: int, flush=None) -> list[float]:
+    """CUDA-event time of `steps` calls of fn on the current stream, L2 flushed before each."""
+    import torch
+
+    times = []
+    for _ in range(steps):
+        if flush is not None:
+            flush.zero_()
+        start = torch.cuda.Event(enable_timing=True)
+        end = torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        end.synchronize()
+        times.append(start.elapsed_time(end))
+    return times
+
+
+def kernel_map_benchmark(device, steps: int, peaks: dict, flush) -> dict:
     """Config 2: kernel-map build only, 1,000,000 coords over batch 8 (125k each),
     LiDAR-like generator; kernel_size=3 submanifold map and kernel_size=3 stride=2 map."""
     import torch
 
     from mlx_lattice_b200 import _ext, synthetic
 
-    coords_host = synthetic.lidar_batch(2, 8, 125000)
-    coords = torch.from_numpy(coords_host).to(device)
+    coords = torch.from_numpy(synthetic.lidar_batch(2, 8, 125000)).to(device)
     n = coords.shape[0]
     active = torch.tensor([n], dtype=torch.int32, device=device)
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
     out = {}
     for name, stride in (('subm_k3', 1), ('k3_s2', 2)):
-        times = []
-        counts = None
-        for i in range(steps + 2):
-            flush.zero_()
-            start = torch.cuda.Event(enable_timing=True)
-            end = torch.cuda.Event(enable_timing=True)
-            start.record()
-            base, _, _ = _ext.build_kernel_relation_base(coords, active, 3, stride, 0, 1)
-            end.record()
-            torch.cuda.synchronize()
-            if i >= 2:
-                times.append(start.elapsed_time(end))
-            counts = base[5].tolist()
-            del base
-        ms = sum(times) / len(times)
-        edges, n_out = counts
-        cap = 1 << (4 * n - 1).bit_length()
-        # algorithmic bytes per build: coord read, clear + insert of the 8-byte-slot table,
-        # one 32-byte bucket per probe, edge arrays, row offsets (+ output-support pass
-        # when strided)
-        # the three edge arrays are outputs of static capacity n * 27 that the contract
-        # defines everywhere (pairs, then a zero tail): every byte of them is written
-        hbm = n * 16 + 8 * cap + 8 * n + 12 * n * 27 + 4 * (n + 1)
+        holder = {}
+
+        def build():
+            holder['base'] = _ext.build_kernel_relation_base(coords, active, 3, stride, 0, 1)[0]
+
+        build()
+        ms = sum(event_timed(build, steps, flush)) / steps
+        edges, n_out = holder['base'][5].tolist()
+        slots = 1 << (4 * n - 1).bit_length()
+        # HBM-class bytes of one build: coordinates read (16 B/row), table clear and insert
+        # (8 B/slot, 8 B/row), the pairs (12 B/edge), row offsets, output coordinates when
+        # strided; the zero tail of the three static-capacity edge arrays (27 n entries each)
+        # is counted apart; the 27 probes per output row read one 32-byte bucket each from
+        # the table, which lives in L2.
+        useful = n * 16 + 8 * slots + 8 * n + 12 * edges + 4 * (n + 1)
         if stride != 1:
-            hbm += n * 16 + 8 * cap + 8 * n + 16 * n_out
-        probes = 32 * 27 * n_out  # table reads, served by L2 (the table is 8 * cap bytes)
-        algo = hbm + probes
+            useful += n * 16 + 8 * slots + 8 * n + 16 * n_out
+        tail = 12 * (27 * n - edges)
+        probes = 32 * 27 * n_out
         out[name] = {
-            'mcoords_per_s': n / ms / 1e3,
-            'ms': ms,
-            'edges': edges,
-            'out_rows': n_out,
-            'algorithmic_gb_s': algo / ms / 1e6,
-            'hbm_algorithmic_gb_s': hbm / ms / 1e6,
-            'frac_of_hbm_peak': hbm / ms / 1e6 / peaks['hbm_gbs'],
+            'mcoords_per_s': n / ms / 1e3, 'ms': ms, 'edges': edges, 'out_rows': n_out,
+            'hbm_bytes': useful, 'hbm_gb_s': useful / ms / 1e6,
+            'frac_of_hbm_peak': useful / ms / 1e6 / peaks['hbm_gbs'],
+            'zero_tail_bytes': tail,
+            'with_zero_tail_gb_s': (useful + tail) / ms / 1e6,
+            'with_zero_tail_frac_of_hbm_peak': (useful + tail) / ms / 1e6 / peaks['hbm_gbs'],
+            'l2_probe_bytes': probes, 'l2_probe_gb_s': probes / ms / 1e6,
+            'bound': 'L2 latency of the probes (DRAM busy a few per cent: profiles/)',
         }
+        del holder
     return out
 
 
@@ -351,10 +399,126 @@ def front_end_benchmark(device, steps: int, peaks: dict) -> dict:
     }
 
 
+
+def config_figures(device, steps: int, peaks: dict, flush) -> dict:
+    """Event-timed figures of the other BASELINE configurations (the headline is config 4):
+    config 0 (fp32 submanifold conv, 50,000 voxels, 32->32), config 1 (int4 kernel-2 stride-2
+    conv 64->128 over 4 x 200,000 voxels) and config 3 (int8 block over 16 x 60,000 voxels),
+    kernel maps prebuilt (the map build is config 2's figure)."""
+    import torch
+
+    from mlx_lattice_b200 import nn, ops, synthetic, workloads
+    from mlx_lattice_b200.core import SparseTensor, quantize_weight
+
+    out = {}
+    rng = np.random.default_rng(99)
+
+    def dev(array):
+        return torch.from_numpy(np.ascontiguousarray(array)).to(device)
+
+    # ---- config 0 ----
+    coords = synthetic.sphere_plane_batch(0, 1, 50000, 256)
+    x = SparseTensor(dev(coords), dev(rng.normal(size=(coords.shape[0], 32)).astype(np.float32)))
+    w = dev((rng.normal(size=(32, 3, 3, 3, 32)) * 0.05).astype(np.float32))
+    ops.subm_conv3d(x, w, kernel_size=3)
+    ms = sum(event_timed(lambda: ops.subm_conv3d(x, w, kernel_size=3), steps, flush)) / steps
+    rel = x.coord_manager.submanifold_kernel_relation(x.coord_key, kernel_size=3)
+    edges, n_out = rel.counts.tolist()
+    bytes_ = coords.shape[0] * 32 * 4 * 2 + 27 * 32 * 32 * 4 + 8 * edges
+    out['config0_subm_fp32_50k_32x32'] = {
+        'ms': ms, 'edges': edges, 'mvoxels_per_s': coords.shape[0] / ms / 1e3,
+        'gflops': 2.0 * edges * 32 * 32 / ms / 1e6, 'gb_s': bytes_ / ms / 1e6,
+        'frac_of_hbm_peak': bytes_ / ms / 1e6 / peaks['hbm_gbs'], 'bound': 'hbm',
+        'route': 'cuda cores (fp32 FMA in the reference summation order)'}
+
+    # ---- config 1 ----
+    coords = synthetic.sphere_plane_batch(1, 4, 200000, 512)
+    x = SparseTensor(dev(coords), dev(rng.normal(size=(coords.shape[0], 64)).astype(np.float16)))
+    dense = torch.from_numpy((rng.normal(size=(128, 2, 2, 2, 64)) * 0.05).astype(np.float16))
+    q = workloads.quantized_to(quantize_weight(dense, group_size=32, bits=4), device)
+    ops.conv3d(x, q, kernel_size=2, stride=2)
+    ms = sum(event_timed(lambda: ops.conv3d(x, q, kernel_size=2, stride=2), steps, flush)) / steps
+    rel = x.coord_manager.kernel_relation(x.coord_key, kernel_size=2, stride=2)
+    edges, n_out = rel.counts.tolist()
+    flops = 2.0 * edges * 64 * 128
+    bytes_ = coords.shape[0] * 64 * 2 + n_out * 128 * 2 + 8 * 64 * 128 / 2 + 8 * edges
+    t_tensor, t_hbm = flops / (peaks['bf16_tflops_sustained'] * 1e12), bytes_ / (peaks['hbm_gbs'] * 1e9)
+    out['config1_strided_int4_4x200k_64x128'] = {
+        'ms': ms, 'edges': edges, 'out_rows': n_out, 'mvoxels_per_s': coords.shape[0] / ms / 1e3,
+        'tflops': flops / ms / 1e9, 'frac_tensor': flops / ms / 1e9 / peaks['bf16_tflops_sustained'],
+        'gb_s': bytes_ / ms / 1e6, 'frac_of_hbm_peak': bytes_ / ms / 1e6 / peaks['hbm_gbs'],
+        'bound': 'tensor' if t_tensor >= t_hbm else 'hbm'}
+
+    # ---- config 3 ----
+    coords = synthetic.lidar_batch(3, 16, 60000)
+    n = coords.shape[0]
+    x = SparseTensor(dev(coords), dev(rng.normal(size=(n, 96)).astype(np.float16)),
+                     batch_counts=(60000,) * 16)
+    dense = torch.from_numpy((rng.normal(size=(96, 3, 3, 3, 96)) * 0.05).astype(np.float16))
+    qc = workloads.quantized_to(quantize_weight(dense, group_size=32, bits=8), device)
+    ql = workloads.quantized_to(quantize_weight(
+        torch.from_numpy((rng.normal(size=(192, 96)) * 0.1).astype(np.float16)), group_size=32, bits=8), device)
+    gamma, beta = dev(rng.uniform(0.5, 1.5, 96).astype(np.float16)), dev(rng.normal(size=96).astype(np.float16))
+    mean, var = dev(rng.normal(size=96).astype(np.float16) * 0.1), dev(rng.uniform(0.5, 1.5, 96).astype(np.float16))
+    parts: dict = {}
+
+    def block():
+        # pooling runs in float32 (as in the reference), the linear layer in float16 again
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        marks[0].record()
+        y = ops.subm_conv3d(x, qc, kernel_size=3)
+        marks[1].record()
+        y = ops.batch_norm(y, weight=gamma, bias=beta, mean=mean, var=var, fuse_relu=True)
+        marks[2].record()
+        pooled = ops.max_pool3d(y.astype(torch.float32), kernel_size=3, stride=2)
+        marks[3].record()
+        z = ops.linear(pooled.astype(torch.float16), ql)
+        marks[4].record()
+        parts['marks'] = marks
+        return pooled, z
+
+    pooled, z = block()
+    n_out = int(pooled.active_rows.item())
+    batch_of = pooled.coords[:n_out, 0].cpu().numpy()
+    per_cloud = tuple(int(v) for v in np.bincount(batch_of, minlength=16))
+    pooled_coords = pooled.coords[:n_out].contiguous()
+
+    def whole():
+        _, z = block()
+        head = SparseTensor(pooled_coords, z.feats[:n_out].float(), stride=2, batch_counts=per_cloud)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        out_rows = ops.global_avg_pool(head)
+        end.record()
+        parts['pool'] = (start, end)
+        return out_rows
+
+    whole()
+    ms = sum(event_timed(whole, steps, flush)) / steps
+    torch.cuda.synchronize()
+    names = ('subm_conv_int8_96x96', 'batch_norm_relu', 'max_pool_k3_s2_fp32', 'quantized_linear_96x192')
+    marks = parts['marks']
+    rel = x.coord_manager.submanifold_kernel_relation(x.coord_key, kernel_size=3)
+    edges, _ = rel.counts.tolist()
+    stage_ms = {name: marks[i].elapsed_time(marks[i + 1]) for i, name in enumerate(names)}
+    stage_ms['global_avg_pool'] = parts['pool'][0].elapsed_time(parts['pool'][1])
+    pool_bytes = n * 96 * 4 + n_out * 96 * 4 + 4 * 27 * n_out
+    out['config3_int8_block_16x60k'] = {
+        'ms': ms, 'mvoxels_per_s': n / ms / 1e3, 'conv_edges': edges, 'pooled_rows': n_out,
+        'conv_tflops': 2.0 * edges * 96 * 96 / stage_ms['subm_conv_int8_96x96'] / 1e9,
+        'max_pool_gb_s': pool_bytes / stage_ms['max_pool_k3_s2_fp32'] / 1e6,
+        'max_pool_frac_of_hbm_peak': pool_bytes / stage_ms['max_pool_k3_s2_fp32'] / 1e6 / peaks['hbm_gbs'],
+        'linear_tflops': 2.0 * n_out * 96 * 192 / stage_ms['quantized_linear_96x192'] / 1e9,
+        'stage_ms': stage_ms,
+        'note': 'kernel maps prebuilt and cached by the coordinate manager; stage times include the '
+                'dtype casts beside them'}
+    return out
+
+
 def run_gpu_arm(args) -> None:
     import torch
 
-    from mlx_lattice_b200 import _ext, _native, workloads
+    from mlx_lattice_b200 import _ext, _native, sharding, workloads
     from mlx_lattice_b200.core import SparseTensor
 
     _native.load()  # no CPU fallback: fail loudly when the extension is missing
@@ -371,25 +535,10 @@ def run_gpu_arm(args) -> None:
 
         dist.init_process_group('nccl', device_id=device)
     peaks = load_peaks()
-
-    # ---- workload: this rank's 8 clouds (global batch ids rank*8 .. rank*8+7) ----
-    coords_np, feats_np = workloads.minkunet_inputs(
-        CONFIG_INDEX, BATCH, PER_CLOUD, first_batch=rank * BATCH)
-    voxels = coords_np.shape[0]
-    coords_host = torch.from_numpy(coords_np).pin_memory()
-    feats_host = torch.from_numpy(feats_np).pin_memory()
+    steps, warmup = args.steps, max(args.warmup, 3)
     quantized = workloads.quantize_all(workloads.minkunet_dense_weights(WEIGHT_SEED))
     model = workloads.MinkUNet(quantized, device)
-    coords_dev = coords_host.to(device)
-    feats_dev = feats_host.to(device)
-    logits_host = torch.empty((voxels, workloads.HEAD_CHANNELS), dtype=torch.float16).pin_memory()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
-    batch_counts = (PER_CLOUD,) * BATCH
-
-    def forward(coords, feats):
-        # a fresh SparseTensor gets a fresh coordinate manager: every kernel map is
-        # rebuilt in every step, like the reference does for a new input
-        return model(SparseTensor(coords, feats, batch_counts=batch_counts)).feats
 
     def barrier():
         torch.cuda.synchronize()
@@ -397,202 +546,266 @@ def run_gpu_arm(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed_steps(step_fn, steps):
-        times = []
-        for _ in range(steps):
-            flush.zero_()
-            start = torch.cuda.Event(enable_timing=True)
-            end = torch.cuda.Event(enable_timing=True)
-            start.record()
-            step_fn()
-            end.record()
-            end.synchronize()
-            times.append(start.elapsed_time(end))
-        return times
+    def max_over_ranks(value: float) -> float:
+        if not distributed:
+            return value
+        t = torch.tensor([value], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
-    def resident_step():
-        return forward(coords_dev, feats_dev)
+    class Shard:
+        """The clouds [first, first + count) of the workload on this GPU, their forward pass
+        captured in a CUDA graph over fixed input buffers (kernel maps are rebuilt inside)."""
 
-    def e2e_step():
-        c = coords_host.to(device, non_blocking=True)
-        f = feats_host.to(device, non_blocking=True)
-        logits_host.copy_(forward(c, f), non_blocking=True)
+        def __init__(self, first: int, count: int, slots: int = 1) -> None:
+            coords_np, feats_np = workloads.minkunet_inputs(CONFIG_INDEX, count, PER_CLOUD, first_batch=first)
+            self.voxels = coords_np.shape[0]
+            self.batch_counts = (PER_CLOUD,) * count
+            self.coords_host = torch.from_numpy(coords_np).pin_memory()
+            self.feats_host = torch.from_numpy(feats_np).pin_memory()
+            self.inputs = [(self.coords_host.to(device), self.feats_host.to(device)) for _ in range(slots)]
+            self.logits_host = [torch.empty((self.voxels, workloads.HEAD_CHANNELS), dtype=torch.float16).pin_memory()
+                                for _ in range(slots)]
+            self.graphs, self.outputs, self.graph_launches = [], [], 0
 
-    for _ in range(max(args.warmup, 3)):
-        resident_step()
+        def forward(self, slot: int = 0):
+            # a fresh SparseTensor gets a fresh coordinate manager: every kernel map is
+            # rebuilt in every step, like the reference does for a new input
+            coords, feats = self.inputs[slot]
+            return model(SparseTensor(coords, feats, batch_counts=self.batch_counts)).feats
+
+        def capture(self) -> bool:
+            try:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    for slot in range(len(self.inputs)):
+                        self.forward(slot)
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                for slot in range(len(self.inputs)):
+                    graph = torch.cuda.CUDAGraph()
+                    before = _ext.launch_count()
+                    with torch.cuda.graph(graph):
+                        out = self.forward(slot)
+                    self.graph_launches = _ext.launch_count() - before
+                    self.graphs.append(graph)
+                    self.outputs.append(out)
+                    graph.replay()
+                torch.cuda.synchronize()
+                return True
+            except Exception as error:  # noqa: BLE001 - fall back to eager launches, and say so
+                self.graphs, self.outputs = [], []
+                self.capture_error = f'{type(error).__name__}: {error}'
+                return False
+
+        def step(self, slot: int = 0):
+            if self.graphs:
+                self.graphs[slot].replay()
+                return self.outputs[slot]
+            return self.forward(slot)
+
+    # ---- strong split: ONE 8-cloud batch, clouds divided over the ranks ----
+    first, end = sharding.shard_range(BATCH, world, rank)
+    shard = Shard(first, end - first, slots=2)
+    for _ in range(warmup):
+        shard.forward(0)
     torch.cuda.synchronize()
     _ext.check_status(device)
-
-    # ---- timed region: K resident steps, convolution launches bracketed by events ----
-    profile = ConvProfile()
-    sampler = ClockSampler(local_rank)
+    graphed = shard.capture()
+    for _ in range(warmup):
+        shard.step(0)
     barrier()
+
+    # ---- timed region 1 (the headline): K steps, inputs resident, L2 flushed between steps ----
+    sampler = ClockSampler(local_rank)
     sampler.start()
-    launches_before = _ext.launch_count()
-    _ext.profile_hook = profile
     wall_start = time.perf_counter()
-    step_ms = timed_steps(resident_step, args.steps)
+    launches_before = _ext.launch_count()
+    step_ms = event_timed(lambda: shard.step(0), steps, flush)
     barrier()
     wall = time.perf_counter() - wall_start
+    launches = (shard.graph_launches * steps) if graphed else _ext.launch_count() - launches_before
+    total_ms = max_over_ranks(sum(step_ms))
+    value = BATCH * PER_CLOUD * steps / (total_ms / 1e3)
+
+    # ---- timed region 2: the same K steps as eager launches with an event pair around every
+    # convolution launch (the roofline figures; the events cannot sit inside a graph) ----
+    profile = ConvProfile()
+    _ext.profile_hook = profile
+    eager_ms = event_timed(lambda: shard.forward(0), steps, flush)
     _ext.profile_hook = None
-    launches = _ext.launch_count() - launches_before
-    total_ms = sum(step_ms)
-
-    # ---- the same step captured once in a CUDA graph and replayed (informational) ----
-    graph_ms = None
-    try:
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            resident_step()
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            resident_step()
-        graph.replay()
-        torch.cuda.synchronize()
-        graph_ms = sum(timed_steps(graph.replay, args.steps)) / args.steps
-        del graph
-    except Exception:  # noqa: BLE001 - capture support is optional for the headline number
-        graph_ms = None
     barrier()
+    eager_total_ms = max_over_ranks(sum(eager_ms))
 
-    # ---- end to end: pinned host buffers in, logits back to the host, every step ----
-    for _ in range(2):
-        e2e_step()
-    barrier()
-    e2e_serial_ms = sum(timed_steps(e2e_step, args.steps))
-    barrier()
-
-    # The same K end-to-end steps as a software pipeline, timed as one region: the inputs
-    # of step i+1 travel on a copy stream while step i computes, the logits of step i
-    # travel back while step i+1 computes. Every step's H2D and D2H is inside the region.
-    def e2e_pipelined(steps: int) -> float:
+    # ---- end to end: pinned host buffers in, logits back to the host, every step. The K
+    # steps run as a two-slot software pipeline in ONE timed region: the inputs of step i+1
+    # travel while step i computes, the logits of step i travel back while step i+1 computes.
+    def e2e_pipelined(count: int) -> float:
         main = torch.cuda.current_stream()
         copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
-        dev_in = [(torch.empty_like(coords_dev), torch.empty_like(feats_dev)) for _ in range(2)]
-        host_out = [torch.empty_like(logits_host).pin_memory() for _ in range(2)]
         in_ready = [torch.cuda.Event() for _ in range(2)]
         consumed = [torch.cuda.Event() for _ in range(2)]
+        drained = [torch.cuda.Event() for _ in range(2)]
 
         def prefetch(i: int) -> None:
             slot = i % 2
             with torch.cuda.stream(copy_in):
                 copy_in.wait_event(consumed[slot])
-                dev_in[slot][0].copy_(coords_host, non_blocking=True)
-                dev_in[slot][1].copy_(feats_host, non_blocking=True)
+                shard.inputs[slot][0].copy_(shard.coords_host, non_blocking=True)
+                shard.inputs[slot][1].copy_(shard.feats_host, non_blocking=True)
                 in_ready[slot].record(copy_in)
 
-        flush.zero_()
         torch.cuda.synchronize()
         start = torch.cuda.Event(enable_timing=True)
-        end = torch.cuda.Event(enable_timing=True)
+        stop = torch.cuda.Event(enable_timing=True)
         start.record(main)
         copy_in.wait_stream(main)
         copy_out.wait_stream(main)
         prefetch(0)
-        for i in range(steps):
+        for i in range(count):
             slot = i % 2
-            if i + 1 < steps:
+            if i + 1 < count:
                 prefetch(i + 1)
             main.wait_event(in_ready[slot])
-            out = forward(dev_in[slot][0], dev_in[slot][1])
+            main.wait_event(drained[slot])      # the slot's previous logits have left
+            out = shard.step(slot)
             consumed[slot].record(main)
-            step_done = torch.cuda.Event()
-            step_done.record(main)
+            done = torch.cuda.Event()
+            done.record(main)
             with torch.cuda.stream(copy_out):
-                copy_out.wait_event(step_done)
-                host_out[slot].copy_(out, non_blocking=True)
-                out.record_stream(copy_out)
+                copy_out.wait_event(done)
+                shard.logits_host[slot].copy_(out, non_blocking=True)
+                drained[slot].record(copy_out)
         main.wait_stream(copy_out)
-        end.record(main)
-        end.synchronize()
-        return start.elapsed_time(end)
+        stop.record(main)
+        stop.synchronize()
+        return start.elapsed_time(stop)
+
+    def e2e_serial(count: int) -> float:
+        def one():
+            shard.inputs[0][0].copy_(shard.coords_host, non_blocking=True)
+            shard.inputs[0][1].copy_(shard.feats_host, non_blocking=True)
+            shard.logits_host[0].copy_(shard.step(0), non_blocking=True)
+        return sum(event_timed(one, count))
 
     e2e_pipelined(2)
     barrier()
-    e2e_ms = e2e_pipelined(args.steps)
+    e2e_ms = max_over_ranks(e2e_pipelined(steps))
+    barrier()
+    e2e_serial_ms = max_over_ranks(e2e_serial(steps))
     barrier()
     clocks = sampler.stop()
     _ext.check_status(device)
 
+    # ---- weak scaling (extra key, N > 1): every rank runs a full 8-cloud batch of its own ----
+    weak = None
     if distributed:
-        stats = torch.tensor([total_ms, e2e_ms, e2e_serial_ms], dtype=torch.float64, device=device)
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        total_ms, e2e_ms, e2e_serial_ms = stats.tolist()
-    value = voxels * world * args.steps / (total_ms / 1e3)
-    e2e_value = voxels * world * args.steps / (e2e_ms / 1e3)
+        del shard.graphs, shard.outputs
+        full = Shard(rank * BATCH, BATCH)
+        for _ in range(3):
+            full.forward(0)
+        full.capture()
+        for _ in range(3):
+            full.step(0)
+        barrier()
+        weak_ms = max_over_ranks(sum(event_timed(lambda: full.step(0), steps, flush)))
+        weak = {'value': BATCH * PER_CLOUD * world * steps / (weak_ms / 1e3), 'unit': 'voxels/s',
+                'ms_per_step': weak_ms / steps, 'voxels_per_gpu': BATCH * PER_CLOUD,
+                'note': 'every rank steps its own 8-cloud batch (clouds 8*rank .. 8*rank+7)'}
+        del full
+        barrier()
 
     if rank == 0:
         tc = profile.summarize(tensor_cores=True)
+        layers = profile.layers(peaks, steps)
         peak_tf = peaks['bf16_tflops_sustained']
         achieved_tf = tc['flops'] / (tc['ms'] / 1e3) / 1e12 if tc['ms'] > 0 else 0.0
+        dram = sum(
+            (DRAM_OVER_ALGORITHMIC['wide' if e['layer'].split('->')[1] in ('128', '256') else 'narrow'])
+            * e['gb_s'] * e['ms'] * 1e6 * e['launches_per_step'] for e in layers if e['route'] == 'tcgen05')
+        per_step_launches = tc['launches'] / steps
         roofline = {
             'bound': 'tensor',
-            'kernel': 'tc_conv_plan_kernel (tcgen05 implicit GEMM, all conv layers of the step)',
+            'kernel': 'tc_conv_plan_kernel (tcgen05 implicit GEMM, all tensor-core conv launches of the step)',
             'achieved': achieved_tf,
             'peak': peak_tf,
             'unit': 'TFLOP/s',
             'frac': achieved_tf / peak_tf,
             'peak_source': peaks['source'] + ' (dense bf16, sustained)',
-            'traffic': tc['dram'] / tc['launches'] if tc['launches'] else None,
-            'traffic_note': 'DRAM bytes per launch (mean over the conv launches), scaled from ncu '
-                            'captures of two smaller cases by gathered bytes',
+            'frac_of_burst_peak': achieved_tf / peaks['bf16_tflops'],
+            'traffic': dram / per_step_launches if per_step_launches else None,
+            'traffic_note': 'DRAM bytes per launch, mean over the conv launches of a step: each '
+                            "layer's algorithmic bytes times the dram/algorithmic ratio ncu measured "
+                            'on that layer class of one LiDAR cloud (profiles/)',
             'algorithmic_gb_s': tc['bytes'] / (tc['ms'] / 1e3) / 1e9 if tc['ms'] > 0 else 0.0,
             'launches': tc['launches'],
-            'ms_per_step_in_kernel': tc['ms'] / args.steps,
+            'ms_per_step_in_kernel': tc['ms'] / steps,
+            'timed_in': 'the eager pass over the same K steps (an event pair per launch)',
+            'layers': layers,
         }
-        kernel_map = kernel_map_benchmark(device, max(args.steps, 3), peaks)
-        front_end = front_end_benchmark(device, max(args.steps, 3), peaks)
-        cpu = cpu_reference_step(args.cpu_sample)
+        extra_steps = max(min(steps, 10), 3)
+        kernel_map = kernel_map_benchmark(device, extra_steps, peaks, flush)
+        front_end = front_end_benchmark(device, extra_steps, peaks)
+        configs = config_figures(device, extra_steps, peaks, flush)
         line = {
             'metric': METRIC,
             'value': value,
             'unit': 'voxels/s',
             'n_gpus': world,
-            'steps': args.steps,
-            'warmup': max(args.warmup, 3),
-            'ms_per_step': total_ms / args.steps,
+            'steps': steps,
+            'warmup': warmup,
+            'ms_per_step': total_ms / steps,
             'higher_is_better': True,
-            'scaling': 'weak',
+            'scaling': 'strong',
             'vs_baseline': None,
             'dtype': 'f16',
             'data': 'synthetic',
             'config': {
                 'workload': 'minkunet_int4_8x120k_lidar',
-                'voxels_per_gpu': voxels,
+                'global_batch': f'{BATCH} clouds x {PER_CLOUD} voxels = {BATCH * PER_CLOUD} voxels per step',
+                'voxels_per_gpu': shard.voxels,
                 'weights': 'int4 affine, group_size 32, N(0, 2/fan_in)',
                 'kernel_maps': 'rebuilt every step (cold)',
                 'l2': 'flushed between steps (256 MiB write); working set exceeds L2',
-                'parallelism': f'batch-sharded x{world}, no data-path collective',
+                'launch': ('one CUDA graph replay per step (the whole forward incl. kernel-map builds)'
+                           if graphed else 'eager launches (graph capture failed: ' +
+                           getattr(shard, 'capture_error', '?') + ')'),
+                'parallelism': f'the 8 clouds sharded over {world} GPU(s) by batch element, '
+                               'no data-path collective',
             },
+            'eager': {'ms_per_step': eager_total_ms / steps,
+                      'value': BATCH * PER_CLOUD * steps / (eager_total_ms / 1e3), 'unit': 'voxels/s',
+                      'note': 'the same steps as individual launches from Python, an event pair '
+                              'around every convolution'},
             'e2e': {
-                'value': e2e_value,
+                'value': BATCH * PER_CLOUD * steps / (e2e_ms / 1e3),
                 'unit': 'voxels/s',
-                'h2d_bytes_per_step': coords_host.numel() * 4 + feats_host.numel() * 2,
-                'd2h_bytes_per_step': logits_host.numel() * 2,
-                'ms_per_step': e2e_ms / args.steps,
-                'pipeline': 'K steps in one timed region: H2D of step i+1 and D2H of step i '
-                            'overlap the compute of their neighbour step; no L2 flush inside the region '
-                            '(the working set of a step exceeds L2)',
-                'serial_ms_per_step': e2e_serial_ms / args.steps,
+                'h2d_bytes_per_step': shard.coords_host.numel() * 4 + shard.feats_host.numel() * 2,
+                'd2h_bytes_per_step': shard.logits_host[0].numel() * 2,
+                'ms_per_step': e2e_ms / steps,
+                'pipeline': 'K steps in one timed region: H2D of step i+1 and D2H of step i overlap the '
+                            'compute of their neighbour step (two input/output slots); no L2 flush inside '
+                            'the region (the working set of a step exceeds L2); bytes are per rank',
+                'serial_ms_per_step': e2e_serial_ms / steps,
             },
             'gpu_launches': launches,
+            'gpu_launches_per_step': launches / steps,
             'roofline': roofline,
             'kernel_map': kernel_map,
             'front_end': front_end,
-            'cuda_graph_replay': None if graph_ms is None else {
-                'ms_per_step': graph_ms, 'value': voxels * world / (graph_ms / 1e3), 'unit': 'voxels/s'},
-            'cpu_baseline': {k: cpu[k] for k in ('value', 'unit', 'cores', 'kind', 'sample')},
+            'configs': configs,
+            'weak_scaling': weak,
             'clocks': clocks,
             'wall_s_timed_region': wall,
         }
+        if world == 1:
+            cpu = cpu_reference_step(PER_CLOUD)
+            line['cpu_baseline'] = {k: cpu[k] for k in ('value', 'unit', 'cores', 'kind', 'sample')}
         print(json.dumps(line))
     if distributed:
         dist.barrier()
         dist.destroy_process_group()
-
 
 
 # --------------------------------------------------------------------------- #
@@ -691,8 +904,6 @@ def main() -> None:
     parser.add_argument('--steps', type=int, default=10)
     parser.add_argument('--warmup', type=int, default=3)
     parser.add_argument('--impl', default='ours', choices=('ours', 'reference'))
-    parser.add_argument('--cpu-sample', type=int, default=8000,
-                        help='voxels of one cloud the CPU reference leg processes')
     parser.add_argument('--case', default=None,
                         help='run one kernel on a small named input instead of the benchmark '
                              '(see run_case); used for the ncu captures under profiles/')

@@ -63,7 +63,9 @@ enum {
 
 enum { LAT_F32 = 0, LAT_F16 = 1 };
 enum { LAT_REDUCE_SUM = 0, LAT_REDUCE_MAX = 1, LAT_REDUCE_AVG = 2 };
-enum { LAT_WEIGHT_KERNEL_MAJOR = 0, LAT_WEIGHT_DENSE_5D = 1 };
+/* weight layouts of lat_sparse_conv_features: (K, C_in, C_out); (C_out, Kx, Ky, Kz, C_in);
+ * (K, C_out, C_in) as lat_dequantize_conv_weights writes it (tensor-core route only) */
+enum { LAT_WEIGHT_KERNEL_MAJOR = 0, LAT_WEIGHT_DENSE_5D = 1, LAT_WEIGHT_OUT_MAJOR = 2 };
 enum { LAT_JOIN_INNER = 0, LAT_JOIN_LEFT = 1, LAT_JOIN_RIGHT = 2, LAT_JOIN_OUTER = 3 };
 
 /* native/bindings/runtime.cpp:27-38 (`version`, `capabilities`). */
@@ -258,7 +260,7 @@ int lat_build_sparse_alignment(
  * native/features/convolution/cpu/algorithms.cpp:180-302.
  * feats [in_capacity, in_channels] with row stride `feat_row_stride` (elements),
  * weights either (K, C_in, C_out) or (C_out, Kx, Ky, Kz, C_in) contiguous, out
- * [out_capacity, out_channels]; rows >= counts[1] are zero. dtype LAT_F32 or
+ * [out_capacity, out_channels]; rows >= counts[1] are zero (plus `bias` when given). dtype LAT_F32 or
  * LAT_F16 for feats, weights and out alike; accumulation is float32. The
  * grouped-view arguments of the reference call are not read by the forward pass
  * and are therefore not part of this signature. Optional `bias` [out_channels]
@@ -302,6 +304,18 @@ int lat_sparse_quantized_conv_features(
     int32_t storage_in_channels, int32_t group_size, int32_t bits,
     const void* bias, const int32_t* row_order, const void* plan, void* out,
     void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* The fp16 weights a packed convolution weight stands for, as (K, C_out, C_in): w =
+ * code*scale + bias evaluated in float32 and rounded once (the decode rule of
+ * native/features/convolution/cpu/quantized.cpp:54-62, 107-131). The tensor-core route
+ * of lat_sparse_quantized_conv_features makes this array in its workspace on every call;
+ * a caller that keeps it (weights are constants of an inference network) passes it to
+ * lat_sparse_conv_features with LAT_WEIGHT_OUT_MAJOR instead and gets the same bits
+ * without the per-call conversion. fp16 scales/biases only. */
+int lat_dequantize_conv_weights(
+    const uint32_t* packed, const void* scales, const void* biases, int32_t n_kernels,
+    int32_t in_channels, int32_t out_channels, int32_t storage_in_channels, int32_t group_size,
+    int32_t bits, void* out, void* stream);
 
 /* Gather plan of the tensor-core route for one relation (no reference counterpart;
  * it takes the place of the per-call walk over the relation that the reference's

@@ -113,6 +113,24 @@ def _dtype_code(dtype: torch.dtype) -> int:
     raise ValueError('convolution supports float32 and float16 tensors.')
 
 
+def _vec_arg(vector, name: str, length: int, like: torch.Tensor, dtype=None):
+    """Optional per-channel vector handed to a kernel as a bare pointer: CUDA tensor on the
+    device of ``like``, exact length and dtype, contiguous. Returns the (contiguous) tensor
+    or None; raises ValueError before anything is launched."""
+    if vector is None:
+        return None
+    if not isinstance(vector, torch.Tensor) or not vector.is_cuda:
+        raise ValueError(f'{name} must be a CUDA tensor.')
+    if vector.device != like.device:
+        raise ValueError(f'{name} must be on the same device as the features.')
+    want = like.dtype if dtype is None else dtype
+    if vector.dtype != want:
+        raise ValueError(f'{name} dtype must be {want}.')
+    if tuple(vector.shape) != (int(length),):
+        raise ValueError(f'{name} must have shape ({int(length)},).')
+    return vector.contiguous()
+
+
 def _second_source(feats: torch.Tensor, feats2) -> tuple[torch.Tensor | None, int, int]:
     """Validated second feature source of a convolution: (tensor, row stride, channels)."""
     if feats2 is None:
@@ -519,8 +537,12 @@ def lookup_coords_static(coords, queries, out: torch.Tensor | None = None):
     device = coords.device
     if out is None:
         out = torch.empty(queries.shape[0], dtype=torch.int32, device=device)
-    elif out.dtype != torch.int32 or out.numel() != queries.shape[0] or not out.is_contiguous():
-        raise ValueError('out must be a contiguous int32 tensor with one entry per query.')
+    elif (not isinstance(out, torch.Tensor) or not out.is_cuda or out.device != device
+          or out.dtype != torch.int32 or out.numel() != queries.shape[0] or not out.is_contiguous()):
+        raise ValueError('out must be a contiguous int32 CUDA tensor on the device of coords with one '
+                         'entry per query.')
+    if queries.device != device:
+        raise ValueError('queries must be on the same device as coords.')
     with torch.cuda.device(device):
         check(_lib().lat_lookup_coords_static(
             _ptr(coords), int(coords.shape[0]), _ptr(queries), int(queries.shape[0]), _ptr(out),
@@ -702,7 +724,11 @@ def interpolate_point_features(voxel_feats, rows, weights):
 # --------------------------------------------------------------------------- #
 
 
-def _weight_geometry(weights: torch.Tensor, n_kernels: int, in_channels: int):
+def _weight_geometry(weights: torch.Tensor, n_kernels: int, in_channels: int, out_major: bool = False):
+    if out_major:
+        if weights.ndim != 3 or weights.shape[0] != n_kernels or weights.shape[2] != in_channels:
+            raise ValueError('dequantised convolution weights must have shape (K, C_out, C_in).')
+        return 2, Triple(n_kernels, 1, 1), int(weights.shape[1])
     if weights.ndim == 3:
         if weights.shape[0] != n_kernels:
             raise ValueError('weight kernel rows must match the convolution kernel.')
@@ -726,11 +752,14 @@ def sparse_conv_features(
     feats, weights, in_rows, out_rows, kernel_ids, counts, row_offsets,
     in_row_offsets=None, in_edge_ids=None, kernel_row_offsets=None, kernel_edge_ids=None,
     out_capacity=None, n_kernels=None, *, bias=None, row_order=None, plan=None, feats2=None,
+    out_major=False,
 ):
     """``_ext.sparse_conv_features`` (``convolution.cpp:90-146``). The four grouped
     view arguments are accepted for signature compatibility; the forward pass does
     not read them. ``feats2`` (optional, same rows) supplies the trailing input channels:
-    the convolution reads the channel concatenation ``[feats | feats2]`` in place."""
+    the convolution reads the channel concatenation ``[feats | feats2]`` in place.
+    ``out_major`` marks ``weights`` as the ``(K, C_out, C_in)`` array of
+    ``dequantize_conv_weights`` (tensor-core route only)."""
     feats, stride = _feats_arg(feats)
     feats2, stride2, c2 = _second_source(feats, feats2)
     _require_cuda(weights, 'weights')
@@ -747,8 +776,10 @@ def sparse_conv_features(
     if row_offsets.shape[0] != out_capacity + 1:
         raise ValueError('row_offsets must have length out_capacity + 1.')
     c_in = int(feats.shape[1]) + c2
-    layout, shape, c_out = _weight_geometry(weights, n_kernels, c_in)
+    layout, shape, c_out = _weight_geometry(weights, n_kernels, c_in, out_major)
     device = feats.device
+    bias = _vec_arg(bias, 'bias', c_out, feats)
+    row_order, plan = _order_and_plan(row_order, plan, out_capacity, n_kernels, device)
     out = torch.empty((out_capacity, c_out), dtype=feats.dtype, device=device)
     lib = _lib()
     ws = _workspace(lib.lat_sparse_conv_workspace_bytes(n_kernels, c_in, c_out), device)
@@ -811,6 +842,8 @@ def sparse_quantized_conv_features(
     if row_order is None and reorder_rows is not None and reorder_rows.numel() == out_capacity:
         row_order = _i32(reorder_rows, 'reorder_rows')
     device = feats.device
+    bias = _vec_arg(bias, 'bias', out_channels, feats)
+    row_order, plan = _order_and_plan(row_order, plan, out_capacity, n_kernels, device)
     out = torch.empty((out_capacity, out_channels), dtype=feats.dtype, device=device)
     lib = _lib()
     ws = _workspace(lib.lat_sparse_conv_workspace_bytes(n_kernels, in_channels, out_channels), device)
@@ -827,6 +860,45 @@ def sparse_quantized_conv_features(
             _ptr(plan), _ptr(out), _ptr(ws), ws.numel(), _ptr(status_word(device)), _stream(),
         )))
     return out
+
+
+def dequantize_conv_weights(weights, scales, biases, in_channels: int, out_channels: int,
+                            storage_in_channels: int, group_size: int, bits: int) -> torch.Tensor:
+    """The fp16 ``(K, C_out, C_in)`` weights a packed convolution weight stands for
+    (``lat_dequantize_conv_weights``): what the tensor-core route of the quantized
+    convolution would make in its workspace on every call."""
+    for tensor, name in ((weights, 'weights'), (scales, 'scales'), (biases, 'biases')):
+        _require_cuda(tensor, name)
+    if scales.dtype != torch.float16 or biases.dtype != torch.float16:
+        raise ValueError('dequantised convolution weights need float16 scales and biases.')
+    n_kernels = int(weights.shape[0])
+    words, groups = storage_in_channels * bits // 32, storage_in_channels // group_size
+    if tuple(weights.shape) != (n_kernels, words, out_channels):
+        raise ValueError('packed weight must have shape (K, S * bits / 32, C_out).')
+    if tuple(scales.shape) != (n_kernels, groups, out_channels) or scales.shape != biases.shape:
+        raise ValueError('scales and biases must have shape (K, C_out, G).')
+    weights, scales, biases = weights.contiguous(), scales.contiguous(), biases.contiguous()
+    out = torch.empty((n_kernels, out_channels, in_channels), dtype=torch.float16, device=weights.device)
+    with torch.cuda.device(weights.device):
+        check(_lib().lat_dequantize_conv_weights(
+            _ptr(weights), _ptr(scales), _ptr(biases), n_kernels, int(in_channels), int(out_channels),
+            int(storage_in_channels), int(group_size), int(bits), _ptr(out), _stream()))
+    return out
+
+
+def _order_and_plan(row_order, plan, out_capacity: int, n_kernels: int, device):
+    """Validated optional row permutation and gather plan of a convolution call."""
+    if row_order is not None:
+        row_order = _i32(row_order, 'row_order')
+        if row_order.device != device or row_order.numel() != out_capacity:
+            raise ValueError('row_order must hold one int32 entry per output row, on the feature device.')
+    if plan is not None:
+        _require_cuda(plan, 'plan')
+        need = int(_lib().lat_conv_plan_bytes(out_capacity, n_kernels)) if n_kernels <= 32 else 0
+        if (plan.device != device or plan.dtype != torch.uint8 or not plan.is_contiguous()
+                or plan.numel() < need):
+            raise ValueError('plan must be the uint8 buffer build_conv_plan returned for this relation.')
+    return row_order, plan
 
 
 def conv_uses_tensor_cores(dtype, n_kernels, in_channels, out_channels, bits=0, group_size=0) -> bool:
@@ -927,7 +999,10 @@ def linear(feats, weight, bias=None):
     _require_cuda(weight, 'weight')
     if weight.dtype != feats.dtype:
         raise ValueError('convolution weights must match feature dtype.')
+    if weight.ndim != 2 or weight.shape[1] != feats.shape[1] or weight.device != feats.device:
+        raise ValueError('linear weight must have shape (C_out, C_in) on the feature device.')
     weight = weight.contiguous()
+    bias = _vec_arg(bias, 'bias', weight.shape[0], feats)
     out = torch.empty((feats.shape[0], weight.shape[0]), dtype=feats.dtype, device=feats.device)
     with torch.cuda.device(feats.device):
         check(_lib().lat_linear(
@@ -942,6 +1017,23 @@ def quantized_linear(
 ):
     feats, _ = _feats_arg(feats)
     feats = feats.contiguous()
+    out_channels, storage, group_size, bits = (int(out_channels), int(storage_in_channels),
+                                               int(group_size), int(bits))
+    if bits not in (4, 8) or group_size not in (32, 64, 128):
+        raise ValueError('quantized linear supports 4 or 8 bits and group_size 32, 64, or 128.')
+    if storage % group_size != 0 or storage < feats.shape[1]:
+        raise ValueError('packed storage channels must be divisible by group_size.')
+    for tensor, name in ((packed, 'packed'), (scales, 'scales'), (biases, 'biases')):
+        _require_cuda(tensor, name)
+        if tensor.device != feats.device:
+            raise ValueError(f'{name} must be on the same device as the features.')
+    if packed.dtype not in (torch.uint32, torch.int32) or tuple(packed.shape) != (out_channels, storage * bits // 32):
+        raise ValueError('packed weight must have shape (C_out, S * bits / 32) and uint32 dtype.')
+    if scales.dtype != feats.dtype or biases.dtype != feats.dtype:
+        raise ValueError('features must match quantized scale dtype.')
+    if tuple(scales.shape) != (out_channels, storage // group_size) or scales.shape != biases.shape:
+        raise ValueError('scales and biases must have shape (C_out, S / group_size).')
+    bias = _vec_arg(bias, 'bias', out_channels, feats)
     out = torch.empty((feats.shape[0], out_channels), dtype=feats.dtype, device=feats.device)
     with torch.cuda.device(feats.device):
         check(_lib().lat_quantized_linear(
@@ -956,6 +1048,11 @@ def quantized_linear(
 def batch_norm_relu(feats, weight, bias, mean, var, eps: float, apply_relu: bool):
     feats, _ = _feats_arg(feats)
     feats = feats.contiguous()
+    channels = int(feats.shape[1])
+    weight, bias = _vec_arg(weight, 'weight', channels, feats), _vec_arg(bias, 'bias', channels, feats)
+    mean, var = _vec_arg(mean, 'mean', channels, feats), _vec_arg(var, 'var', channels, feats)
+    if mean is None or var is None:
+        raise ValueError('batch_norm needs mean and var.')
     out = torch.empty_like(feats)
     with torch.cuda.device(feats.device):
         check(_lib().lat_batch_norm_relu(

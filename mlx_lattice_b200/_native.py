@@ -83,6 +83,7 @@ SIGNATURES = {
     'lat_sparse_quantized_conv_features': (
         I, [I, P, I, c_int64, P, I, c_int64, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P, P, P, P, P,
             c_size_t, P, P]),
+    'lat_dequantize_conv_weights': (I, [P, P, P, I, I, I, I, I, I, P, P]),
     'lat_conv_plan_bytes': (c_size_t, [I, I]),
     'lat_build_conv_plan': (I, [P, P, I, P, P, I, I, I, P, P, c_size_t, P, P]),
     'lat_conv_uses_tensor_cores': (I, [I, I, I, I, I, I]),

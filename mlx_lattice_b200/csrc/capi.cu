@@ -48,6 +48,10 @@ int run_tc_conv(
     const int32_t* row_order, const void* plan, void* out, void* workspace,
     size_t workspace_bytes, int32_t* status, cudaStream_t stream);
 
+int run_stage_quantized_weights(
+    const uint32_t* packed, const void* scales, const void* biases, int n_kernels, int in_channels,
+    int out_channels, int storage_in_channels, int group_size, int bits, void* out, cudaStream_t stream);
+
 } // namespace lat
 
 using namespace lat;
@@ -158,9 +162,13 @@ int lat_sparse_conv_features(
         return rc;
     }
     LAT_REQUIRE(weights != nullptr, "weights are required.");
-    LAT_REQUIRE(weight_layout == LAT_WEIGHT_KERNEL_MAJOR || weight_layout == LAT_WEIGHT_DENSE_5D,
+    LAT_REQUIRE(weight_layout == LAT_WEIGHT_KERNEL_MAJOR || weight_layout == LAT_WEIGHT_DENSE_5D ||
+                    weight_layout == LAT_WEIGHT_OUT_MAJOR,
                 "mapped convolution weight must have shape (K, C_in, C_out) or "
                 "(C_out, Kx, Ky, Kz, C_in).");
+    LAT_REQUIRE(weight_layout != LAT_WEIGHT_OUT_MAJOR ||
+                    tc_conv_supported(dtype, n_kernels, in_channels, out_channels, 0, 0),
+                "(K, C_out, C_in) weights are taken by the tensor-core route only.");
     if (weight_layout == LAT_WEIGHT_DENSE_5D) {
         LAT_REQUIRE(kernel_shape.x * kernel_shape.y * kernel_shape.z == n_kernels,
                     "weight kernel rows must match the convolution kernel.");
@@ -179,6 +187,23 @@ int lat_sparse_conv_features(
                            out_channels, in_rows, kernel_ids, edge_capacity, counts, row_offsets,
                            out_capacity, n_kernels, bias, out, workspace, workspace_bytes, status,
                            stream);
+}
+
+int lat_dequantize_conv_weights(
+    const uint32_t* packed, const void* scales, const void* biases, int32_t n_kernels,
+    int32_t in_channels, int32_t out_channels, int32_t storage_in_channels, int32_t group_size,
+    int32_t bits, void* out, void* stream_ptr
+) {
+    LAT_REQUIRE(bits == 4 || bits == 8, "quantized convolution supports only 4 or 8 bits.");
+    LAT_REQUIRE(group_size == 32 || group_size == 64 || group_size == 128,
+                "quantized convolution group_size must be 32, 64, or 128.");
+    LAT_REQUIRE(n_kernels > 0 && in_channels > 0 && out_channels > 0, "weight shape must be positive.");
+    LAT_REQUIRE(storage_in_channels >= in_channels && storage_in_channels % group_size == 0,
+                "packed storage channels must be divisible by group_size.");
+    LAT_REQUIRE(packed != nullptr && scales != nullptr && biases != nullptr && out != nullptr,
+                "packed weight, scales, biases and the output buffer are required.");
+    return run_stage_quantized_weights(packed, scales, biases, n_kernels, in_channels, out_channels,
+                                       storage_in_channels, group_size, bits, out, as_stream(stream_ptr));
 }
 
 int lat_sparse_quantized_conv_features(

@@ -729,6 +729,22 @@ static bool dequant_in_registers() {
     return mode != nullptr && mode[0] == 'r';
 }
 
+int run_stage_quantized_weights(
+    const uint32_t* packed, const void* scales, const void* biases, int n_kernels, int in_channels,
+    int out_channels, int storage_in_channels, int group_size, int bits, void* out, cudaStream_t stream
+) {
+    const size_t total = static_cast<size_t>(n_kernels) * in_channels * out_channels;
+    if (total == 0) {
+        return LAT_OK;
+    }
+    stage_quantized_weights_kernel<<<static_cast<int>((total + 255) / 256), 256, 0, stream>>>(
+        packed, static_cast<const __half*>(scales), static_cast<const __half*>(biases), n_kernels,
+        in_channels, out_channels, storage_in_channels * bits / 32, storage_in_channels / group_size,
+        group_size, bits, static_cast<__half*>(out));
+    LAT_LAUNCH_CHECK();
+    return LAT_OK;
+}
+
 bool tc_conv_supported(int dtype, int n_kernels, int in_channels, int out_channels,
                        int quantized_bits, int group_size) {
     if (dtype != LAT_F16) {
@@ -782,7 +798,12 @@ int run_tc_conv(
     p.c_out = out_channels;
     p.n_kernels = n_kernels;
     if (packed == nullptr) {
-        if (weight_layout == LAT_WEIGHT_DENSE_5D) {
+        if (weight_layout == LAT_WEIGHT_OUT_MAJOR) {
+            // (K, C_out, C_in): the form lat_dequantize_conv_weights writes
+            p.weights = static_cast<const __half*>(weights);
+            p.w_stride_k = static_cast<long long>(out_channels) * in_channels;
+            p.w_stride_co = in_channels;
+        } else if (weight_layout == LAT_WEIGHT_DENSE_5D) {
             // (C_out, K, C_in): rows already K-major
             p.weights = static_cast<const __half*>(weights);
             p.w_stride_k = in_channels;

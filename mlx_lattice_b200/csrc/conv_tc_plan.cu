@@ -1,31 +1,33 @@
-// Tensor-core sparse convolution driven by a gather plan (conv_plan.cu): the same
-// output-stationary implicit GEMM on tcgen05 as conv_tc.cu -- 256-row tiles, a unit =
-// (kernel offset used by the tile, 32-channel slice of C_in), two units per 64-wide K
-// slab, fp32 accumulators in TMEM, one deterministic store per output row -- but no role
-// ever touches the relation's CSR arrays and the producers never synchronise with each
-// other:
+// Tensor-core sparse convolution driven by a gather plan (conv_plan.cu): an output-stationary
+// implicit GEMM on tcgen05 -- 256-row tiles of output rows in the plan's row order, a unit =
+// (kernel offset used by the tile, 32-channel slice of C_in), two units per 64-wide K slab,
+// fp32 accumulators in TMEM, one deterministic store per output row. No role touches the
+// relation's CSR arrays and no thread waits for a copy of its own:
+//   warp 17    row-vector loader: streams the plan's row vectors of the CTA's tiles (one
+//              per tile and used kernel offset, 1 KB each) into a 16-slot shared-memory
+//              ring by bulk copies, in the order the producers consume them, so that no
+//              producer waits on a global load of the plan.
 //   warps 0-7  producers. A thread owns one 16-byte chunk column (so one unit of each
-//              slab) and the eight tile rows q, q+32, ..; the input rows of those eight
-//              are 32 contiguous bytes of the plan's row vector, fetched one slab ahead
-//              into registers. Per slab: wait for a free stage, 8 cp.async for A (zero
-//              fill where the row has no neighbour), C_out/32 cp.async for the fp16 B
-//              tile, then cp.async.mbarrier.arrive.noinc so that the stage's barrier
+//              slab) and the eight tile rows q, q+32, ..; their input rows are 32
+//              contiguous bytes of a row vector in the ring. Per slab: wait for a free
+//              stage, 8 cp.async for A (zero fill where the row has no neighbour; the
+//              channels may come from two feature tensors over the same rows), the fp16
+//              B tile, then cp.async.mbarrier.arrive.noinc so that the stage's barrier
 //              completes when the copies land. The stream of slabs runs across tile
-//              boundaries; tile headers are prefetched a tile ahead. When C_in is a
-//              multiple of 64 both units of a slab share their kernel offset: the loop
-//              nest is tile > offset > slab with the row addresses computed once per
-//              offset, and the weight tile of a slab is one TMA box
-//              (cp.async.bulk.tensor.3d, 128-byte swizzle) issued by one thread.
+//              boundaries. When C_in is a multiple of 64 both units of a slab share
+//              their kernel offset: one ring entry feeds C_in / 64 slabs and the weight
+//              tile of a slab is one TMA box (cp.async.bulk.tensor.3d, 128-byte swizzle,
+//              no multicast) issued by one thread.
 //   warp 16    one thread issues the MMAs (8 per slab), commits the stage back to the
 //              producers and, per tile, the accumulator to the epilogue.
 //   warps 8-15 epilogue: tcgen05.ld, optional bias, one cast to fp16, 16-byte stores.
-// Every mbarrier wait is bounded by a clock budget; on expiry the kernel records
-// LAT_STATUS_WAIT_TIMEOUT, every role leaves its loop and the CTA frees its TMEM.
+// Every mbarrier wait is bounded by a clock budget (lat_set_wait_budget_cycles) and its
+// verdict is made uniform across the warp; on expiry the kernel records
+// LAT_STATUS_WAIT_TIMEOUT, every role leaves its loop, the CTA lets copies in flight land
+// and frees its TMEM.
 #include <cuda.h>
 
 #include <algorithm>
-#include <cstdlib>
-#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
@@ -37,21 +39,6 @@ namespace lat {
 using namespace tcgen05;
 
 namespace {
-
-#ifdef LAT_TC_KNOBS
-__device__ long long g_dbg[148 * 16];
-#define DBG_DECL long long dbg_a = 0, dbg_b = 0; int dbg_na = 0, dbg_nb = 0
-#define DBG_T0() const long long dbg_t0 = clock64()
-#define DBG_A() do { dbg_a += clock64() - dbg_t0; ++dbg_na; } while (0)
-#define DBG_B() do { dbg_b += clock64() - dbg_t0; ++dbg_nb; } while (0)
-#define DBG_FLUSH(slot) do { long long* d = g_dbg + blockIdx.x * 16 + (slot); d[0] += dbg_a; d[1] += dbg_na; d[2] += dbg_b; d[3] += dbg_nb; } while (0)
-#else
-#define DBG_DECL
-#define DBG_T0()
-#define DBG_A()
-#define DBG_B()
-#define DBG_FLUSH(slot)
-#endif
 
 constexpr int kTileRows = kPlanTileRows;
 constexpr int kProducerWarps = 8;
@@ -96,9 +83,6 @@ struct PlanConvParams {
     int num_tiles;
     int b_tma;           // 1: the B tile of a slab is one TMA box (C_in a multiple of 64)
     int b_k_outer;       // tensor-map dimension order: 1 = (C_in, C_out, K), 0 = (C_in, K, C_out)
-#ifdef LAT_TC_KNOBS
-    int knobs;
-#endif
 };
 
 struct Ring {
@@ -184,9 +168,6 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
     const int warp = tid >> 5;
     const int lane = tid & 31;
     const int upo = p.c_in / 32;  // units per kernel offset
-#ifdef LAT_TC_KNOBS
-    const long long dbg_kernel_t0 = clock64();
-#endif
     const int grid = gridDim.x;
     const long long budget = p.wait_budget;
     // Bounded wait whose verdict is the same in every lane of the (converged) warp, so that a
@@ -198,11 +179,7 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
 
     if (tid == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
-#ifdef LAT_TC_KNOBS
-            mbar_init(&ctl.full[s], ((p.knobs & 256) ? kProducerWarps : kProducerWarps * 32) + (p.b_tma ? 1 : 0));
-#else
             mbar_init(&ctl.full[s], kProducerWarps * 32 + (p.b_tma ? 1 : 0));
-#endif
             mbar_init(&ctl.empty[s], 1);
         }
         for (int a = 0; a < kMaxAccStages; ++a) {
@@ -262,25 +239,14 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
         Ring ring{0, 0u};
         Ring vec{0, 0u};
         bool ok = true;
-        DBG_DECL;
         // wait for stage `ring.index` to be free (the warp decides as one)
         auto acquire_stage = [&]() -> bool {
-            DBG_T0();
             const bool got = wait_warp(&ctl.empty[ring.index], ring.phase ^ 1u);
-            DBG_A();
             return got;
         };
         // The slab in stage `ring.index` is issued. Every thread's copies arrive on the stage's
         // barrier by themselves when they have landed (no thread waits for its own copies).
         auto slab_issued = [&]() {
-#ifdef LAT_TC_KNOBS
-            if (p.knobs & 256) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&ctl.full[ring.index]);
-                ring.advance(p.stages);
-                return;
-            }
-#endif
             cp_async_arrive_noinc(&ctl.full[ring.index]);
             ring.advance(p.stages);
         };
@@ -292,13 +258,9 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
             const int reps = upo >> 1;  // slabs per offset
             const int thread_channel = a_half * 32 + col8;
             while (ok) {
-                {
-                DBG_T0();
                 if (!wait_warp(&ctl.vec_full[vec.index], vec.phase)) {
                     ok = false;
                     break;
-                }
-                DBG_B();
                 }
                 const int32_t header = ctl.vec_header[vec.index];
                 if (header < 0) {
@@ -320,28 +282,15 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         // absent neighbours copy zero bytes from a valid address: zero fill
-#ifdef LAT_TC_KNOBS
-                        if (p.knobs & 32) continue;
-                        cp_async_16(a_addr + 4096 * j,
-                                    base + static_cast<long long>(max(idx[j], 0)) * pitch, idx[j] >= 0 && !(p.knobs & 2));
-#else
                         cp_async_16(a_addr + 4096 * j,
                                     base + static_cast<long long>(max(idx[j], 0)) * pitch, idx[j] >= 0);
-#endif
                     }
                     if (p.b_tma) {
                         if (tid == 0) {
-#ifdef LAT_TC_KNOBS
-                            if (p.knobs & 1) {
-                                mbar_arrive(&ctl.full[ring.index]);
-                            } else
-#endif
-                            {
                             mbar_arrive_expect_tx(&ctl.full[ring.index],
                                                   static_cast<uint32_t>(p.c_out) * 128u);
                             tma_load_3d(b_addr - dst0, &b_map, r * 64, p.b_k_outer ? 0 : k,
                                         p.b_k_outer ? k : 0, &ctl.full[ring.index]);
-                            }
                         }
                     } else {
                         const char* w_src = weight_bytes + static_cast<long long>(k) * p.w_k_bytes +
@@ -479,9 +428,6 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
             }
         }
         cp_async_wait<0>();
-#ifdef LAT_TC_KNOBS
-        if (tid == 32) DBG_FLUSH(0);
-#endif
         for (int tile = blockIdx.x + ((active - blockIdx.x + grid - 1) / grid) * grid;
              tile < p.num_tiles; tile += grid) {
             if (producers_fill(tile, grid)) {
@@ -496,7 +442,6 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
         const int tile_row = half_tile * 128 + quarter * 32 + lane;
         bool ok = true;
         int local_tile = 0;
-        DBG_DECL;
         // the output row and the offset mask of a tile are fetched one tile ahead
         auto tile_output_row = [&](int tile) -> int {
             const int position = tile * kTileRows + tile_row;
@@ -521,13 +466,9 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
             if (tile < active) {
                 a = local_tile % p.acc_stages;
                 const uint32_t parity = (local_tile / p.acc_stages) & 1;
-                {
-                DBG_T0();
                 if (!wait_warp(&ctl.acc_full[a], parity)) {
                     ok = false;
                     break;
-                }
-                DBG_A();
                 }
                 tc_fence_after();
                 computed = info.x != 0;
@@ -551,10 +492,6 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
             for (int c0 = 0; c0 < p.c_out; c0 += 32) {
                 uint32_t v[32];
                 const int width = min(32, p.c_out - c0);  // 32 or 16
-#ifdef LAT_TC_KNOBS
-                if (p.knobs & 64) break;
-                if ((p.knobs & 8) && row != 0) out_row = nullptr;
-#endif
                 if (width == 32) {
                     tmem_load_32(taddr + c0, v);
                 } else {
@@ -589,9 +526,6 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                 mbar_arrive(&ctl.acc_empty[a]);
             }
         }
-#ifdef LAT_TC_KNOBS
-        if (tid == 256) DBG_FLUSH(8);
-#endif
     } else if (warp == kMmaWarp) {
         // ======================= MMA issuer =======================
         // Lane 0 issues; the warp as a whole fetches the offset masks of the CTA's next 32
@@ -604,7 +538,6 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
         bool ok = true;
         Ring ring{0, 0u};
         int local_tile = 0;
-        DBG_DECL;
         int2 batch = load_info(p, blockIdx.x + lane * grid, active);
         for (int first = blockIdx.x; first < active && ok; first += 32 * grid) {
             const int2 mine = batch;
@@ -614,25 +547,17 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                 if (lane == 0) {
                     const int a = local_tile % p.acc_stages;
                     const uint32_t parity = (local_tile / p.acc_stages) & 1;
-                    {
-                    DBG_T0();
                     if (!mbar_wait(&ctl.acc_empty[a], parity ^ 1, abort_flag, p.status, budget)) {
                         ok = false;
-                    }
-                    DBG_A();
                     }
                     tc_fence_after();
                     const int slabs = (__popc(static_cast<uint32_t>(mask)) * upo + 1) >> 1;
                     const uint32_t tmem_d0 = tmem_base + static_cast<uint32_t>(2 * a * p.acc_cols);
                     const uint32_t tmem_d1 = tmem_d0 + static_cast<uint32_t>(p.acc_cols);
                     for (int s = 0; s < slabs && ok; ++s) {
-                        {
-                        DBG_T0();
                         if (!mbar_wait(&ctl.full[ring.index], ring.phase, abort_flag, p.status, budget)) {
                             ok = false;
                             break;
-                        }
-                        DBG_B();
                         }
                         // the A rows were written by cp.async (generic proxy); the MMA reads
                         // shared memory through the async proxy
@@ -646,9 +571,6 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                         for (int kk = 0; kk < 4; ++kk) {
                             // 16 fp16 = 32 bytes along K inside the swizzle atom: +2 in 16-byte units
                             const uint32_t acc = kk != 0 ? 1u : (s != 0 ? 1u : 0u);
-#ifdef LAT_TC_KNOBS
-                            if ((p.knobs & 16) && (s | kk) != 0) continue;
-#endif
                             umma_f16_split(tmem_d0, a_lo + 2 * kk, b_lo + 2 * kk, desc_hi, idesc, acc);
                             umma_f16_split(tmem_d1, a_lo + (128 * 128 >> 4) + 2 * kk, b_lo + 2 * kk, desc_hi,
                                            idesc, acc);
@@ -667,9 +589,6 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             }
         }
-#ifdef LAT_TC_KNOBS
-        if (lane == 0) DBG_FLUSH(4);
-#endif
     } else if (warp == kLoaderWarp) {
         // ======================= row-vector loader =======================
         // Streams the row vectors of this CTA's tiles, in the order the producers consume
@@ -677,14 +596,9 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
         // a global load of the plan. Lane 0 issues; the warp fetches offset masks in batches.
         bool ok = true;
         Ring vec{0, 0u};
-        DBG_DECL;
         auto publish = [&](int32_t header, const int32_t* source) -> bool {
-            {
-            DBG_T0();
             if (!mbar_wait(&ctl.vec_empty[vec.index], vec.phase ^ 1u, abort_flag, p.status, budget)) {
                 return false;
-            }
-            DBG_A();
             }
             ctl.vec_header[vec.index] = header;
             if (source != nullptr) {
@@ -720,17 +634,11 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
         if (lane == 0 && ok) {
             publish(-1, nullptr);
         }
-#ifdef LAT_TC_KNOBS
-        if (lane == 0) DBG_FLUSH(10);
-#endif
     }
 
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-#ifdef LAT_TC_KNOBS
-    if (tid == 0) g_dbg[blockIdx.x * 16 + 12] += clock64() - dbg_kernel_t0;
-#endif
     if (ctl.abort_flag != 0) {
         // a role gave up: bulk copies towards this CTA's shared memory may still be in flight;
         // they land within microseconds, and the CTA stays until they have
@@ -777,24 +685,6 @@ int pow2_at_least(int value, int floor_value) {
 
 } // namespace
 
-#ifdef LAT_TC_KNOBS
-extern "C" void lat_debug_dump(int reset) {
-    static long long host[148 * 16];
-    cudaDeviceSynchronize();
-    if (!reset) {
-        cudaMemcpyFromSymbol(host, g_dbg, sizeof(host));
-        double sum[16] = {0};
-        for (int b = 0; b < 148; ++b) for (int i = 0; i < 16; ++i) sum[i] += host[b * 16 + i];
-        const char* names[] = {"prod wait empty", "", "prod wait vec_full", "", "mma wait acc_empty", "", "mma wait full", "", "epi wait acc_full", "", "loader wait vec_empty", ""};
-        fprintf(stderr, "  kernel cycles/CTA %.0f\n", sum[12] / 148);
-        for (int i = 0; i < 12; i += 2) {
-            fprintf(stderr, "  %-22s total/CTA %10.0f  count/CTA %8.0f  avg %8.1f\n", names[i], sum[i] / 148, sum[i + 1] / 148, sum[i + 1] > 0 ? sum[i] / sum[i + 1] : 0.0);
-        }
-    }
-    memset(host, 0, sizeof(host));
-    cudaMemcpyToSymbol(g_dbg, host, sizeof(host));
-}
-#endif
 
 // fp16 weights only (packed weights are staged to fp16 by the caller); shapes as
 // tc_conv_supported allows them. `feats2` (optional) holds the channels from `split` on.
@@ -884,14 +774,6 @@ int run_tc_conv_plan(
             p.b_k_outer = k_outer ? 1 : 0;
         }
     }
-#ifdef LAT_TC_KNOBS
-    {
-        const char* knob = getenv("LAT_TC_KNOB");
-        p.knobs = knob != nullptr ? atoi(knob) : 0;
-        const char* st = getenv("LAT_TC_STAGES");
-        if (st != nullptr) p.stages = std::min(p.stages, atoi(st));
-    }
-#endif
     tc_conv_plan_kernel<<<grid, kThreads, smem_bytes, stream>>>(p, b_map);
     LAT_LAUNCH_CHECK();
     return LAT_OK;

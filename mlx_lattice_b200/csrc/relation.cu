@@ -60,6 +60,7 @@ struct MapParams {
     int tail_is_total;            // rows >= n_out get E (target maps) instead of 0
     int edge_capacity;
     int32_t* status;
+    long long wait_budget;        // clock budget of the look-back wait
 };
 
 __global__ void fill_i32_kernel(int32_t* data, size_t count, int value) {
@@ -485,7 +486,6 @@ __global__ void __launch_bounds__(kBlockThreads) map_fill_kernel(MapParams p) {
 constexpr unsigned long long kTileAggregate = 1ull << 62;
 constexpr unsigned long long kTilePrefix = 2ull << 62;
 constexpr unsigned long long kTileValueMask = (1ull << 62) - 1;
-constexpr long long kLookbackBudgetCycles = 4000000000LL;  // about two seconds
 
 __global__ void __launch_bounds__(kBlockThreads, 5) map_single_pass_kernel(
     MapParams p, unsigned long long* tile_status, int* ticket, int num_tiles
@@ -640,7 +640,8 @@ __global__ void __launch_bounds__(kBlockThreads, 5) map_single_pass_kernel(
                 const int nearest = prefix != 0 ? __ffs(prefix) - 1 : 31;
                 const unsigned need = nearest >= 31 ? 0xffffffffu : ((2u << nearest) - 1u);
                 if ((ready & need) != need) {
-                    if (clock64() - start > kLookbackBudgetCycles) {
+                    // the warp gives up as one (a lane left behind would hang the next ballot)
+                    if (__any_sync(0xffffffffu, clock64() - start > p.wait_budget)) {
                         failed = true;
                         break;
                     }
@@ -1418,6 +1419,7 @@ int run_map(
     }
 
     MapParams p{};
+    p.wait_budget = wait_budget_cycles();
     p.coords = coords;
     p.table = table.slots;
     p.table_mask = table.mask;
@@ -1754,6 +1756,7 @@ int lat_build_transposed_kernel_relation(
         LAT_CUDA_CHECK(fill_i32(kernel_ids, capacity, 0, stream));
         LAT_CUDA_CHECK(fill_i32(row_offsets, capacity + 1, 0, stream));
         MapParams p{};
+        p.wait_budget = wait_budget_cycles();
         p.coords = coords;
         p.table = table.slots;
         p.table_mask = table.mask;

@@ -37,6 +37,21 @@ def _sources(feats, relation: KernelRelation, uses_tensor_cores: bool):
     return _ext.concat_aligned_features(first, None, second, None), None
 
 
+def _kept_fp16_weights(weight: QuantizedWeight) -> torch.Tensor:
+    """The dequantised ``(K, C_out, C_in)`` fp16 form of a packed weight, made once and kept on
+    the packed array (weights are constants of an inference network; a later in-place change
+    of the packed array, its scales or its biases makes a new one)."""
+    versions = (weight.weight._version, weight.scales._version, weight.biases._version,
+                weight.scales.data_ptr(), weight.biases.data_ptr())
+    kept = getattr(weight.weight, '_lattice_fp16', None)
+    if kept is None or kept[0] != versions:
+        kept = (versions, _ext.dequantize_conv_weights(
+            weight.weight, weight.scales, weight.biases, weight.in_channels, weight.out_channels,
+            weight.storage_in_channels, weight.group_size, weight.bits))
+        weight.weight._lattice_fp16 = kept
+    return kept[1]
+
+
 def sparse_quantized_conv_features_from_relation(
     feats, weight: QuantizedWeight, relation: KernelRelation, bias=None
 ) -> torch.Tensor:
@@ -51,6 +66,15 @@ def sparse_quantized_conv_features_from_relation(
         weight.bits, weight.group_size,
     )
     feats, feats2 = _sources(feats, relation, tc)
+    if tc and weight.scales.dtype == torch.float16:
+        # the tensor cores take fp16 operands: the packed codes are converted once, not per call
+        return _ext.sparse_conv_features(
+            feats, _kept_fp16_weights(weight), relation.edges.in_rows, relation.edges.out_rows,
+            relation.edges.kernel_ids, relation.counts, relation.output_csr.row_offsets,
+            out_capacity=relation.n_out_capacity, n_kernels=relation.n_kernels, bias=bias,
+            row_order=_row_order(relation, tc), plan=_conv_plan(relation, tc, int(feats.shape[0])),
+            feats2=feats2, out_major=True,
+        )
     return _ext.sparse_quantized_conv_features(
         feats,
         weight.weight,

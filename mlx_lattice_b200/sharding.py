@@ -49,12 +49,28 @@ def merge_relations(shards: list[dict], row_starts: list[int], out_starts: list[
 
 
 def gather_global_pool(local_rows: torch.Tensor, group=None) -> torch.Tensor:
-    """All-gather of the (B_local, C) global-pool rows into (B, C) on every rank; every
-    rank must hold the same B_local. NCCL on GPUs, gloo on the CPU."""
+    """All-gather of the (B_local, C) global-pool rows into (B, C) on every rank, in rank
+    order. Ranks may hold different B_local (``shard_range`` gives the earlier ranks one
+    cloud more when the clouds do not divide evenly): the row counts are exchanged first
+    and every rank pads its block to the largest one, because an all-gather of unequal
+    blocks is undefined. NCCL on GPUs, gloo on the CPU."""
     import torch.distributed as dist
 
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return local_rows
-    parts = [torch.empty_like(local_rows) for _ in range(dist.get_world_size(group))]
-    dist.all_gather(parts, local_rows.contiguous(), group=group)
-    return torch.cat(parts, dim=0)
+    world = dist.get_world_size(group)
+    if local_rows.ndim != 2:
+        raise ValueError('global-pool rows must have shape (B_local, C).')
+    counts = [torch.zeros(2, dtype=torch.int64, device=local_rows.device) for _ in range(world)]
+    mine = torch.tensor([local_rows.shape[0], local_rows.shape[1]], dtype=torch.int64,
+                        device=local_rows.device)
+    dist.all_gather(counts, mine, group=group)
+    sizes = [tuple(int(v) for v in c.tolist()) for c in counts]
+    if any(channels != sizes[0][1] for _, channels in sizes):
+        raise ValueError('every rank must hold global-pool rows of the same channel count.')
+    largest = max(rows for rows, _ in sizes)
+    block = local_rows.new_zeros((largest, local_rows.shape[1]))
+    block[: local_rows.shape[0]] = local_rows
+    parts = [torch.empty_like(block) for _ in range(world)]
+    dist.all_gather(parts, block, group=group)
+    return torch.cat([part[:rows] for part, (rows, _) in zip(parts, sizes)], dim=0)

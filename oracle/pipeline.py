@@ -15,6 +15,23 @@ import numpy as np
 from oracle import restatement
 
 
+def quantized_to_numpy(q) -> dict:
+    """A packed weight of the package under test (CPU tensors with ``.numpy()``) as the
+    dict of numpy arrays the oracle consumes."""
+    return {
+        'weight': q.weight.numpy().view(np.uint32),
+        'scales': q.scales.numpy(),
+        'biases': q.biases.numpy(),
+        'group_size': q.group_size,
+        'bits': q.bits,
+        'in_channels': q.in_channels,
+        'out_channels': q.out_channels,
+        'kernel_size': q.kernel_size,
+        'layout': q.layout,
+        'storage_in_channels': q.storage_in_channels,
+    }
+
+
 def _qconv(backend, feats, q, rel, out_capacity, n_kernels):
     return backend.sparse_quantized_conv(
         feats, q['weight'], q['scales'], q['biases'], rel, out_capacity, n_kernels,

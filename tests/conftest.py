@@ -71,3 +71,30 @@ def canonical_pair_lists(rel, n_kernels):
         pairs = np.stack([rel['in_rows'][ids], rel['out_rows'][ids]], axis=1)
         lists.append(pairs[np.lexsort((pairs[:, 1], pairs[:, 0]))])
     return lists
+
+
+def run_ranks(target, world: int, args: tuple, timeout: float):
+    """Start `world` spawned processes running target(rank, world, *args, results) and wait for
+    them; a rank that is still alive after `timeout` seconds (stuck in a collective) is
+    terminated, then killed, so that no worker outlives the test holding a device. Returns
+    (exit codes, results queue)."""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context('spawn')
+    results = ctx.Queue()
+    procs = [ctx.Process(target=target, args=(rank, world, *args, results), daemon=True)
+             for rank in range(world)]
+    try:
+        for proc in procs:
+            proc.start()
+        for proc in procs:
+            proc.join(timeout=timeout)
+    finally:
+        for proc in procs:
+            if proc.is_alive():
+                proc.terminate()
+                proc.join(timeout=10)
+            if proc.is_alive():
+                proc.kill()
+                proc.join()
+    return [proc.exitcode for proc in procs], results

@@ -59,3 +59,19 @@ def test_host_only_entry_points():
         _ext.kernel_offsets((0, 1, 1))
     caps = _ext.capabilities()
     assert set(caps) == {'cpu', 'metal', 'cuda'} and caps['cpu'] is False
+
+
+def test_vector_arguments_are_checked_on_the_host():
+    """`_vec_arg` guards every optional per-channel pointer of `_ext`: a host tensor is
+    refused with a ValueError (no launch is possible without a device anyway)."""
+    import pytest
+    import torch
+
+    from mlx_lattice_b200 import _ext
+
+    like = torch.zeros((4, 8), dtype=torch.float16)
+    assert _ext._vec_arg(None, 'bias', 8, like) is None
+    with pytest.raises(ValueError, match='bias must be a CUDA tensor'):
+        _ext._vec_arg(torch.zeros(8, dtype=torch.float16), 'bias', 8, like)
+    with pytest.raises(ValueError, match='bias must be a CUDA tensor'):
+        _ext._vec_arg([0.0] * 8, 'bias', 8, like)

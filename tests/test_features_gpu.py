@@ -405,3 +405,69 @@ def test_two_source_conv_needs_a_plan(cuda, sphere):
         _ext.sparse_conv_features(feats, weights, r['in_rows'], r['out_rows'], r['kernel_ids'],
                                   r['counts'], r['row_offsets'], out_capacity=n, n_kernels=27,
                                   feats2=feats)
+
+
+def test_kept_fp16_weights_give_the_bits_of_the_packed_call(cuda, restatement, sphere):
+    """ops.subm_conv3d converts a packed weight to fp16 once and keeps the result; the bits
+    equal those of lat_sparse_quantized_conv_features, which converts on every call."""
+    from mlx_lattice_b200 import _ext, ops
+    from mlx_lattice_b200.core import QuantizedWeight, SparseTensor
+
+    coords, rel = sphere
+    n = coords.shape[0]
+    rng = np.random.default_rng(77)
+    feats = rng.normal(size=(n, 64)).astype(np.float16)
+    q = restatement.quantize_weight((rng.normal(size=(128, 3, 3, 3, 64)) * 0.05).astype(np.float16), 32, 4)
+    direct = _qconv(cuda, feats, q, rel, n, 27, with_plan=True)
+    weight = QuantizedWeight(_dev(q['weight'].view(np.int32), cuda), _dev(q['scales'], cuda),
+                             _dev(q['biases'], cuda), 32, 4, 64, 128, (3, 3, 3), 'dense_5d')
+    x = SparseTensor(_dev(coords, cuda), _dev(feats, cuda))
+    first = ops.subm_conv3d(x, weight, kernel_size=3).feats
+    kept = weight.weight._lattice_fp16[1]
+    second = ops.subm_conv3d(x, weight, kernel_size=3).feats
+    assert weight.weight._lattice_fp16[1] is kept          # converted once
+    assert np.array_equal(first.cpu().numpy(), direct) and torch.equal(first, second)
+    weight.scales.mul_(2)                                  # an in-place change makes a new copy
+    third = ops.subm_conv3d(x, weight, kernel_size=3).feats
+    assert weight.weight._lattice_fp16[1] is not kept and not torch.equal(third, first)
+    _ext.check_status(cuda)
+
+
+def test_bad_vector_arguments_raise_before_any_launch(cuda, sphere):
+    """Optional per-channel vectors reach the kernels as bare pointers; wrong device, dtype,
+    length or layout is a ValueError in the wrapper, never a device fault."""
+    from mlx_lattice_b200 import _ext
+
+    coords, rel = sphere
+    n = coords.shape[0]
+    r = _rel_dev(rel, cuda)
+    feats = torch.zeros((n, 32), dtype=torch.float16, device=cuda)
+    weights = torch.zeros((32, 3, 3, 3, 32), dtype=torch.float16, device=cuda)
+    args = (r['in_rows'], r['out_rows'], r['kernel_ids'], r['counts'], r['row_offsets'])
+    before = _ext.launch_count()
+    for bias in (torch.zeros(32, dtype=torch.float16),                       # host memory
+                 torch.zeros(32, dtype=torch.float32, device=cuda),          # dtype
+                 torch.zeros(31, dtype=torch.float16, device=cuda),          # too short
+                 torch.zeros((32, 1), dtype=torch.float16, device=cuda)):    # shape
+        with pytest.raises(ValueError, match='bias'):
+            _ext.sparse_conv_features(feats, weights, *args, out_capacity=n, n_kernels=27, bias=bias)
+        with pytest.raises(ValueError, match='bias'):
+            _ext.linear(feats, torch.zeros((32, 32), dtype=torch.float16, device=cuda), bias)
+    with pytest.raises(ValueError, match='row_order'):
+        _ext.sparse_conv_features(feats, weights, *args, out_capacity=n, n_kernels=27,
+                                  row_order=torch.zeros(n - 1, dtype=torch.int32, device=cuda))
+    with pytest.raises(ValueError, match='plan'):
+        _ext.sparse_conv_features(feats, weights, *args, out_capacity=n, n_kernels=27,
+                                  plan=torch.zeros(64, dtype=torch.uint8, device=cuda))
+    good = torch.ones(32, dtype=torch.float16, device=cuda)
+    for name in ('weight', 'bias', 'mean', 'var'):
+        vectors = {'weight': good, 'bias': good, 'mean': good, 'var': good}
+        vectors[name] = torch.ones(64, dtype=torch.float16, device=cuda)[::2]   # strided view: made contiguous
+        _ext.batch_norm_relu(feats, vectors['weight'], vectors['bias'], vectors['mean'], vectors['var'], 1e-5, False)
+        vectors[name] = torch.ones(33, dtype=torch.float16, device=cuda)
+        with pytest.raises(ValueError, match=name):
+            _ext.batch_norm_relu(feats, vectors['weight'], vectors['bias'], vectors['mean'], vectors['var'], 1e-5, False)
+    with pytest.raises(ValueError, match='linear weight'):
+        _ext.linear(feats, torch.zeros((32, 16), dtype=torch.float16, device=cuda))
+    assert _ext.launch_count() == before + 4      # only the four valid batch_norm calls launched
+    _ext.check_status(cuda)

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from bench import quantized_to_numpy
+from oracle.pipeline import quantized_to_numpy
 from mlx_lattice_b200 import synthetic
 
 pytestmark = pytest.mark.gpu
@@ -17,16 +17,21 @@ def _max_rel_err(got, want):
     return np.abs(np.asarray(got, np.float64) - want).max() / max(np.abs(want).max(), 1e-30)
 
 
-def test_minkunet_int4_matches_reference_composition(cuda, oracle):
+@pytest.mark.parametrize('clouds,per', [(2, 5000), (1, 120000)],
+                         ids=['two_small_clouds', 'config4_one_whole_cloud'])
+def test_minkunet_int4_matches_reference_composition(cuda, oracle, clouds, per):
+    """BASELINE config 4: the MinkUNet-style int4 network against the reference composition
+    evaluated by the oracle; the second case is one cloud of the benchmark batch at its
+    full size (120,000 voxels; the clouds of a batch are independent)."""
     from mlx_lattice_b200 import _ext, workloads
     from mlx_lattice_b200.core import SparseTensor
     from oracle import pipeline
 
-    coords, feats = workloads.minkunet_inputs(4, 2, 5000)
+    coords, feats = workloads.minkunet_inputs(4, clouds, per)
     quantized = workloads.quantize_all(workloads.minkunet_dense_weights(20264))
     model = workloads.MinkUNet(quantized, cuda)
     x = SparseTensor(torch.from_numpy(coords).to(cuda), torch.from_numpy(feats).to(cuda),
-                     batch_counts=(5000, 5000))
+                     batch_counts=(per,) * clouds)
     out = model(x)
     assert out.same_coords(x)
     logits = out.feats.cpu().numpy()
@@ -34,22 +39,23 @@ def test_minkunet_int4_matches_reference_composition(cuda, oracle):
     want = pipeline.minkunet_forward(
         oracle, coords, feats, {k: quantized_to_numpy(v) for k, v in quantized.items()},
         workloads.minkunet_layers())
-    assert logits.shape == want.shape == (10000, 20)
+    assert logits.shape == want.shape == (clouds * per, 20)
     assert _max_rel_err(logits, want) <= 2e-3
     # deterministic: a second forward (fresh maps) is bitwise identical
     again = model(SparseTensor(torch.from_numpy(coords).to(cuda), torch.from_numpy(feats).to(cuda)))
     assert np.array_equal(again.feats.cpu().numpy(), logits)
 
 
-def test_mixed_int8_block_config3_shape(cuda, oracle, restatement):
-    """SubmConv3d int8 96->96, BatchNorm, ReLU, max_pool3d(k3, s2), QuantizedLinear int8
-    96->192, global_avg_pool, with the dtype plumbing the reference allows (pooling in
-    float32)."""
+@pytest.mark.parametrize('clouds,per', [(3, 4000), (1, 60000)],
+                         ids=['three_small_clouds', 'config3_one_whole_cloud'])
+def test_mixed_int8_block_config3_shape(cuda, oracle, restatement, clouds, per):
+    """BASELINE config 3: SubmConv3d int8 96->96, BatchNorm, ReLU, max_pool3d(k3, s2),
+    QuantizedLinear int8 96->192, global_avg_pool, with the dtype plumbing the reference
+    allows (pooling in float32); the second case is one cloud at its full size."""
     from mlx_lattice_b200 import _ext, nn, ops
     from mlx_lattice_b200.core import SparseTensor
 
     rng = np.random.default_rng(20263)
-    clouds, per = 3, 4000
     coords = synthetic.lidar_batch(3, clouds, per)
     n = coords.shape[0]
     feats = rng.normal(size=(n, 96)).astype(np.float16)

@@ -4,12 +4,14 @@ unsharded map bit-exactly, and the global-pool all-gather assembles the (B, C) r
 import os
 import socket
 
+from datetime import timedelta
+
 import numpy as np
 import pytest
 import torch
 import torch.distributed as dist
-import torch.multiprocessing as mp
 
+from conftest import run_ranks
 from mlx_lattice_b200 import sharding, synthetic
 from oracle import restatement
 
@@ -25,7 +27,7 @@ def _free_port() -> int:
 def _worker(rank: int, world: int, port: int, results) -> None:
     os.environ['MASTER_ADDR'] = '127.0.0.1'
     os.environ['MASTER_PORT'] = str(port)
-    dist.init_process_group('gloo', rank=rank, world_size=world)
+    dist.init_process_group('gloo', rank=rank, world_size=world, timeout=timedelta(seconds=120))
     try:
         coords = synthetic.lidar_batch(2, CLOUDS, PER_CLOUD)
         counts = (PER_CLOUD,) * CLOUDS
@@ -73,13 +75,32 @@ def test_shard_ranges_cover_all_clouds():
 
 
 def test_two_rank_sharding_reproduces_unsharded_maps():
-    ctx = mp.get_context('spawn')
-    results = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, results)) for r in range(2)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=180)
-        assert p.exitcode == 0
+    codes, results = run_ranks(_worker, 2, (_free_port(),), timeout=180)
+    assert codes == [0, 0]
     assert results.get(timeout=10) is True
+
+
+def _uneven_worker(rank: int, world: int, port: int, clouds: int, results) -> None:
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world, timeout=timedelta(seconds=120))
+    try:
+        begin, end = sharding.shard_range(clouds, world, rank)
+        # row b of the joint result is (b, 10 b, 100 b)
+        local = torch.tensor([[b, 10.0 * b, 100.0 * b] for b in range(begin, end)],
+                             dtype=torch.float32).reshape(end - begin, 3)
+        gathered = sharding.gather_global_pool(local)
+        want = torch.tensor([[b, 10.0 * b, 100.0 * b] for b in range(clouds)], dtype=torch.float32)
+        results.put((rank, bool(torch.equal(gathered, want.reshape(clouds, 3)))))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('clouds,world', [(5, 2), (7, 3), (2, 3)])
+def test_global_pool_gather_with_an_uneven_split(clouds, world):
+    """CLOUDS % world != 0: the earlier ranks hold one cloud more (one rank may hold none);
+    the gather still returns the (CLOUDS, C) rows in cloud order on every rank."""
+    codes, results = run_ranks(_uneven_worker, world, (_free_port(), clouds), timeout=180)
+    assert codes == [0] * world
+    seen = sorted(results.get(timeout=10) for _ in range(world))
+    assert seen == [(rank, True) for rank in range(world)]

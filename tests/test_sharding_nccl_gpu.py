@@ -5,9 +5,13 @@ one GPU. Skipped on a single-GPU box."""
 import os
 import socket
 
+from datetime import timedelta
+
 import numpy as np
 import pytest
 import torch
+
+from conftest import run_ranks
 
 pytestmark = pytest.mark.gpu
 
@@ -50,7 +54,8 @@ def _worker(rank: int, world: int, port: int, results) -> None:
     os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
     torch.cuda.set_device(rank)
     device = torch.device('cuda', rank)
-    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=device)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=device,
+                            timeout=timedelta(seconds=120))
     try:
         coords, feats, weight = _inputs()
         counts = (PER_CLOUD,) * CLOUDS
@@ -69,15 +74,6 @@ def _worker(rank: int, world: int, port: int, results) -> None:
 def test_two_gpu_shards_gather_the_joint_global_pool():
     if torch.cuda.device_count() < 2:
         pytest.skip('needs two GPUs')
-    import torch.multiprocessing as mp
-
-    ctx = mp.get_context('spawn')
-    results = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, results)) for r in range(2)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=300)
-    assert all(p.exitcode == 0 for p in procs)
+    codes, results = run_ranks(_worker, 2, (_free_port(),), timeout=300)
+    assert codes == [0, 0]
     assert results.get(timeout=10) is True

@@ -207,10 +207,17 @@ def run_reference_arm(args) -> None:
 # this implementation
 # --------------------------------------------------------------------------- #
 
-# DRAM bytes of a convolution launch over its algorithmic bytes, from ncu captures of two
-# layers of the benchmark network on LiDAR-like clouds (profiles/tc_conv_plan_kernel_lidar_*):
-# dram__bytes_read + dram__bytes_write divided by A_in*C_in*2 + N_out*C_out*2 + W + 8E.
-DRAM_OVER_ALGORITHMIC = {'wide': 1.0, 'narrow': 1.0}
+# DRAM bytes of a convolution launch over its algorithmic bytes, by input width: ncu captures
+# (dram__bytes_read + dram__bytes_write) of the 256->256, 128->128 and 64->64 layers of the
+# benchmark network at the benchmark's own size (8 LiDAR-like clouds), summarised in
+# profiles/tc_conv_plan_kernel_lidar_layers.md. The excess is the repeated gather of input
+# rows that fall out of L2 (each row is read once per edge) and the zero tail of the
+# static-capacity output.
+DRAM_OVER_ALGORITHMIC = ((256, 4.29), (128, 2.16), (0, 1.05))
+
+
+def dram_over_algorithmic(c_in: int) -> float:
+    return next(ratio for width, ratio in DRAM_OVER_ALGORITHMIC if c_in >= width)
 
 
 def conv_algorithmic(info, counts) -> tuple[float, float]:
@@ -612,7 +619,7 @@ def run_gpu_arm(args) -> None:
         shard.forward(0)
     torch.cuda.synchronize()
     _ext.check_status(device)
-    graphed = shard.capture()
+    graphed = False if args.no_graph else shard.capture()
     for _ in range(warmup):
         shard.step(0)
     barrier()
@@ -705,7 +712,8 @@ def run_gpu_arm(args) -> None:
         full = Shard(rank * BATCH, BATCH)
         for _ in range(3):
             full.forward(0)
-        full.capture()
+        if not args.no_graph:
+            full.capture()
         for _ in range(3):
             full.step(0)
         barrier()
@@ -721,9 +729,8 @@ def run_gpu_arm(args) -> None:
         layers = profile.layers(peaks, steps)
         peak_tf = peaks['bf16_tflops_sustained']
         achieved_tf = tc['flops'] / (tc['ms'] / 1e3) / 1e12 if tc['ms'] > 0 else 0.0
-        dram = sum(
-            (DRAM_OVER_ALGORITHMIC['wide' if e['layer'].split('->')[1] in ('128', '256') else 'narrow'])
-            * e['gb_s'] * e['ms'] * 1e6 * e['launches_per_step'] for e in layers if e['route'] == 'tcgen05')
+        dram = sum(dram_over_algorithmic(int(e['layer'].split()[1].split('->')[0])) * e['gb_s'] * e['ms'] * 1e6
+                   * e['launches_per_step'] for e in layers if e['route'] == 'tcgen05')
         per_step_launches = tc['launches'] / steps
         roofline = {
             'bound': 'tensor',
@@ -736,8 +743,8 @@ def run_gpu_arm(args) -> None:
             'frac_of_burst_peak': achieved_tf / peaks['bf16_tflops'],
             'traffic': dram / per_step_launches if per_step_launches else None,
             'traffic_note': 'DRAM bytes per launch, mean over the conv launches of a step: each '
-                            "layer's algorithmic bytes times the dram/algorithmic ratio ncu measured "
-                            'on that layer class of one LiDAR cloud (profiles/)',
+                            "layer's algorithmic bytes times the dram/algorithmic ratio that ncu measured "
+                            'on the 256-, 128- and 64-channel layers at this size (profiles/)',
             'algorithmic_gb_s': tc['bytes'] / (tc['ms'] / 1e3) / 1e9 if tc['ms'] > 0 else 0.0,
             'launches': tc['launches'],
             'ms_per_step_in_kernel': tc['ms'] / steps,
@@ -769,8 +776,8 @@ def run_gpu_arm(args) -> None:
                 'kernel_maps': 'rebuilt every step (cold)',
                 'l2': 'flushed between steps (256 MiB write); working set exceeds L2',
                 'launch': ('one CUDA graph replay per step (the whole forward incl. kernel-map builds)'
-                           if graphed else 'eager launches (graph capture failed: ' +
-                           getattr(shard, 'capture_error', '?') + ')'),
+                           if graphed else 'eager launches (' + ('--no-graph' if args.no_graph else
+                           'graph capture failed: ' + getattr(shard, 'capture_error', '?')) + ')'),
                 'parallelism': f'the 8 clouds sharded over {world} GPU(s) by batch element, '
                                'no data-path collective',
             },
@@ -839,8 +846,8 @@ def run_case(args) -> None:
     event time of each repetition: `conv:<level>:<c_in>:<c_out>[:fp16]` (submanifold 3x3x3
     int4 convolution on level `level` of `--clouds` clouds), `down:<level>:<c_in>:<c_out>`
     (kernel-2 stride-2 int4 convolution from that level), `map[:stride]` (kernel map of
-    `--clouds` clouds of 125,000 voxels of config 2), `pool` (max_pool3d k3 s2 over one
-    config-3 cloud, 96 channels)."""
+    `--clouds` clouds of 125,000 voxels of config 2), `pool` (max_pool3d k3 s2 over
+    `--clouds` config-3 clouds of 60,000 voxels, 96 float32 channels)."""
     import torch
 
     from mlx_lattice_b200 import _ext, _native, ops, synthetic, workloads
@@ -889,7 +896,7 @@ def run_case(args) -> None:
     elif kind == 'pool':
         coords_np = synthetic.lidar_batch(3, args.clouds, 60000)
         rng = np.random.default_rng(9)
-        feats = torch.from_numpy(rng.normal(size=(coords_np.shape[0], 96)).astype(np.float16)).to(device)
+        feats = torch.from_numpy(rng.normal(size=(coords_np.shape[0], 96)).astype(np.float32)).to(device)
         x = SparseTensor(torch.from_numpy(coords_np).to(device), feats)
         for y, ms in timed(lambda: ops.max_pool3d(x, kernel_size=3, stride=2)):
             print(f'{args.case} rows={x.capacity} out_rows={int(y.active_rows.item())} ms={ms:.3f}')
@@ -904,6 +911,9 @@ def main() -> None:
     parser.add_argument('--steps', type=int, default=10)
     parser.add_argument('--warmup', type=int, default=3)
     parser.add_argument('--impl', default='ours', choices=('ours', 'reference'))
+    parser.add_argument('--no-graph', action='store_true',
+                        help='step with individual launches instead of CUDA-graph replays (the form '
+                             'the ncu launch list under profiles/ is taken on)')
     parser.add_argument('--case', default=None,
                         help='run one kernel on a small named input instead of the benchmark '
                              '(see run_case); used for the ncu captures under profiles/')

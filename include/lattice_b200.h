@@ -420,6 +420,20 @@ int lat_global_pool(
     const float* feats, int32_t rows, int32_t channels, const int32_t* batch_offsets,
     int32_t batches, int32_t reduce, float* out, void* stream);
 
+/* The same `linear` (mlx_lattice/ops/feature.py:33-51) on the tensor cores, for float16
+ * rows with C_in a multiple of 32 and C_out a multiple of 16 up to 256
+ * (lat_linear_uses_tensor_cores): x @ W.T is the tcgen05 convolution over the identity
+ * relation with one kernel offset. `plan` is lat_build_identity_conv_plan(rows) in a
+ * buffer of lat_conv_plan_bytes(rows, 1) bytes; it depends on `rows` only and can be
+ * kept. weight (C_out, C_in) float16, 16-byte aligned; float32 accumulation, one cast,
+ * optional bias [C_out] added after it. */
+int lat_linear_uses_tensor_cores(int32_t dtype, int32_t in_channels, int32_t out_channels);
+int lat_build_identity_conv_plan(int32_t rows, void* plan, size_t plan_bytes, void* stream);
+int lat_linear_tensor_cores(
+    const void* feats, int32_t rows, int32_t in_channels, int64_t feat_row_stride,
+    const void* weight, int32_t out_channels, const void* bias, const void* plan, void* out,
+    int32_t* status, void* stream);
+
 /* mlx_lattice/ops/feature.py:33-51 (`linear`, x @ W.T + b) and the pointwise
  * branch of conv3d (mlx_lattice/ops/conv.py:79-82,347-355). weight (C_out, C_in). */
 int lat_linear(

@@ -993,10 +993,47 @@ def global_pool(feats, batch_offsets, reduce: str):
     return out
 
 
+# identity gather plans of the tensor-core linear, by (device index, rows): they depend on the
+# row count only, so the few most recent ones are kept
+_identity_plans: dict = {}
+_TC_LINEAR_MIN_ROWS = 4096
+
+
+def _identity_plan(rows: int, device: torch.device) -> torch.Tensor:
+    key = (device.index, rows)
+    plan = _identity_plans.get(key)
+    if plan is None:
+        lib = _lib()
+        plan = torch.empty(max(int(lib.lat_conv_plan_bytes(rows, 1)), 256), dtype=torch.uint8, device=device)
+        with torch.cuda.device(device):
+            check(lib.lat_build_identity_conv_plan(rows, _ptr(plan), plan.numel(), _stream()))
+        while len(_identity_plans) >= 8:
+            _identity_plans.pop(next(iter(_identity_plans)))
+        _identity_plans[key] = plan
+    return plan
+
+
 def linear(feats, weight, bias=None):
-    feats, _ = _feats_arg(feats)
-    feats = feats.contiguous()
+    """``feats @ weight.T + bias`` (``mlx_lattice/ops/feature.py:33-51``). float16 matrices
+    whose shapes the tcgen05 tiles cover run on the tensor cores (the convolution kernel
+    over the identity relation); everything else on the CUDA-core kernel."""
+    feats, stride = _feats_arg(feats)
     _require_cuda(weight, 'weight')
+    if (feats.dtype == torch.float16 and weight.dtype == torch.float16 and weight.ndim == 2
+            and weight.shape[1] == feats.shape[1] and weight.device == feats.device
+            and feats.shape[0] >= _TC_LINEAR_MIN_ROWS and stride % 8 == 0 and feats.data_ptr() % 16 == 0
+            and _lib().lat_linear_uses_tensor_cores(1, int(feats.shape[1]), int(weight.shape[0]))):
+        weight = weight.contiguous()
+        bias = _vec_arg(bias, 'bias', weight.shape[0], feats)
+        rows = int(feats.shape[0])
+        out = torch.empty((rows, weight.shape[0]), dtype=feats.dtype, device=feats.device)
+        plan = _identity_plan(rows, feats.device)
+        with torch.cuda.device(feats.device):
+            check(_lib().lat_linear_tensor_cores(
+                _ptr(feats), rows, int(feats.shape[1]), stride, _ptr(weight), int(weight.shape[0]),
+                _ptr(bias), _ptr(plan), _ptr(out), _ptr(status_word(feats.device)), _stream()))
+        return out
+    feats = feats.contiguous()
     if weight.dtype != feats.dtype:
         raise ValueError('convolution weights must match feature dtype.')
     if weight.ndim != 2 or weight.shape[1] != feats.shape[1] or weight.device != feats.device:

@@ -100,6 +100,9 @@ SIGNATURES = {
         I, [P, I, I, c_int64, P, P, P, I, P, P, I, I, I, I, P, P, P]),
     'lat_global_pool': (I, [P, I, I, P, I, I, P, P]),
     'lat_linear': (I, [I, P, I, I, P, I, P, P, P]),
+    'lat_linear_uses_tensor_cores': (I, [I, I, I]),
+    'lat_build_identity_conv_plan': (I, [I, P, c_size_t, P]),
+    'lat_linear_tensor_cores': (I, [P, I, I, c_int64, P, I, P, P, P, P, P]),
     'lat_quantized_linear': (I, [I, P, I, I, P, P, P, I, I, I, I, P, P, P]),
     'lat_batch_norm_relu': (I, [I, P, c_int64, I, P, P, P, P, c_float, I, P, P]),
     'lat_relu': (I, [I, P, c_int64, P, P]),

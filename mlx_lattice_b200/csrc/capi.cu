@@ -48,6 +48,13 @@ int run_tc_conv(
     const int32_t* row_order, const void* plan, void* out, void* workspace,
     size_t workspace_bytes, int32_t* status, cudaStream_t stream);
 
+int run_tc_conv_plan(
+    const void* feats, int in_channels, long long feat_stride, const void* feats2, int split,
+    long long feat2_stride, const void* weights,
+    long long w_stride_k, long long w_stride_co, int n_kernels, int out_channels, int out_capacity,
+    const void* bias, const int32_t* row_order, const void* plan, void* out, int32_t* status,
+    cudaStream_t stream);
+
 int run_stage_quantized_weights(
     const uint32_t* packed, const void* scales, const void* biases, int n_kernels, int in_channels,
     int out_channels, int storage_in_channels, int group_size, int bits, void* out, cudaStream_t stream);
@@ -187,6 +194,31 @@ int lat_sparse_conv_features(
                            out_channels, in_rows, kernel_ids, edge_capacity, counts, row_offsets,
                            out_capacity, n_kernels, bias, out, workspace, workspace_bytes, status,
                            stream);
+}
+
+int lat_linear_uses_tensor_cores(int32_t dtype, int32_t in_channels, int32_t out_channels) {
+    return tc_conv_supported(dtype, 1, in_channels, out_channels, 0, 0) ? 1 : 0;
+}
+
+int lat_linear_tensor_cores(
+    const void* feats, int32_t rows, int32_t in_channels, int64_t feat_row_stride,
+    const void* weight, int32_t out_channels, const void* bias, const void* plan, void* out,
+    int32_t* status, void* stream_ptr
+) {
+    LAT_REQUIRE(rows >= 0 && (feats != nullptr || rows == 0), "feats must have shape (N, C).");
+    LAT_REQUIRE(tc_conv_supported(LAT_F16, 1, in_channels, out_channels, 0, 0),
+                "the tensor-core linear needs float16, C_in a multiple of 32 and C_out a multiple of "
+                "16 up to 256.");
+    LAT_REQUIRE(weight != nullptr && reinterpret_cast<uintptr_t>(weight) % 16 == 0,
+                "weight (C_out, C_in) must be a 16-byte aligned device array.");
+    LAT_REQUIRE(feat_row_stride >= in_channels && feat_row_stride % 8 == 0 &&
+                    reinterpret_cast<uintptr_t>(feats) % 16 == 0,
+                "feature rows must be 16-byte aligned for the tensor-core route.");
+    LAT_REQUIRE(plan != nullptr && (out != nullptr || rows == 0), "plan and output buffer are required.");
+    // x @ W.T is the convolution over the identity relation with a single kernel offset
+    return run_tc_conv_plan(feats, in_channels, feat_row_stride, nullptr, in_channels, 0, weight,
+                            static_cast<long long>(out_channels) * in_channels, in_channels, 1,
+                            out_channels, rows, bias, nullptr, plan, out, status, as_stream(stream_ptr));
 }
 
 int lat_dequantize_conv_weights(

@@ -176,6 +176,21 @@ __global__ void __launch_bounds__(kPlanTileRows) plan_fill_kernel(PlanBuildParam
     }
 }
 
+// the plan of the identity relation (output row i reads input row i at the only offset):
+// every tile uses offset 0 and its row vector is the tile's own rows
+__global__ void __launch_bounds__(kPlanTileRows) identity_plan_kernel(int rows, int num_tiles, int2* tile_info,
+                                                                    int32_t* vectors) {
+    const int tile = blockIdx.x;
+    const int row = tile * kPlanTileRows + threadIdx.x;
+    vectors[static_cast<size_t>(tile) * kPlanTileRows + plan_slot(threadIdx.x)] = row < rows ? row : -1;
+    if (threadIdx.x == 0) {
+        tile_info[tile] = make_int2(1, tile);
+        if (tile == 0) {
+            tile_info[num_tiles] = make_int2(num_tiles, num_tiles);
+        }
+    }
+}
+
 } // namespace
 
 } // namespace lat
@@ -188,6 +203,22 @@ size_t lat_conv_plan_bytes(int32_t out_capacity, int32_t kernel_count) {
     const size_t tiles = static_cast<size_t>(plan_tiles(out_capacity));
     return plan_info_bytes(static_cast<int>(tiles)) +
            tiles * static_cast<size_t>(std::max(kernel_count, 1)) * kPlanTileRows * sizeof(int32_t);
+}
+
+int lat_build_identity_conv_plan(int32_t rows, void* plan, size_t plan_bytes, void* stream_ptr) {
+    LAT_REQUIRE(rows >= 0, "rows must be non-negative.");
+    LAT_REQUIRE(plan != nullptr && reinterpret_cast<uintptr_t>(plan) % 16 == 0,
+                "plan must be a 16-byte aligned device buffer.");
+    LAT_REQUIRE(plan_bytes >= lat_conv_plan_bytes(rows, 1), "plan buffer is smaller than lat_conv_plan_bytes.");
+    if (rows == 0) {
+        return LAT_OK;
+    }
+    const int tiles = plan_tiles(rows);
+    identity_plan_kernel<<<tiles, kPlanTileRows, 0, as_stream(stream_ptr)>>>(
+        rows, tiles, static_cast<int2*>(plan),
+        reinterpret_cast<int32_t*>(static_cast<char*>(plan) + plan_info_bytes(tiles)));
+    LAT_LAUNCH_CHECK();
+    return LAT_OK;
 }
 
 int lat_build_conv_plan(

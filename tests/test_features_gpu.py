@@ -471,3 +471,36 @@ def test_bad_vector_arguments_raise_before_any_launch(cuda, sphere):
         _ext.linear(feats, torch.zeros((32, 16), dtype=torch.float16, device=cuda))
     assert _ext.launch_count() == before + 4      # only the four valid batch_norm calls launched
     _ext.check_status(cuda)
+
+
+@pytest.mark.parametrize('c_in,c_out', [(96, 192), (32, 16), (256, 256), (64, 48)])
+def test_linear_on_the_tensor_cores(cuda, restatement, c_in, c_out):
+    """float16 matrices of at least 4096 rows whose shapes the tcgen05 tiles cover run as the
+    convolution over the identity relation; same tolerance as every fp16 contraction, also
+    for rows of a wider array, a bias, and a packed weight converted once."""
+    from mlx_lattice_b200 import _ext, ops
+    from mlx_lattice_b200.core import QuantizedWeight, SparseTensor
+
+    assert _ext._lib().lat_linear_uses_tensor_cores(1, c_in, c_out) == 1
+    rng = np.random.default_rng(c_in + c_out)
+    rows = 4096 + 777
+    x = rng.normal(size=(rows, c_in)).astype(np.float16)
+    w = (rng.normal(size=(c_out, c_in)) * 0.1).astype(np.float16)
+    b = rng.normal(size=c_out).astype(np.float16)
+    before = _ext.launch_count()
+    got = _ext.linear(_dev(x, cuda), _dev(w, cuda), _dev(b, cuda)).cpu().numpy()
+    assert _max_rel_err(got, restatement.linear(x, w, b)) <= FP16_TOL
+    wide = _dev(np.concatenate([x, x], axis=1), cuda)[:, :c_in]
+    assert np.array_equal(_ext.linear(wide, _dev(w, cuda), _dev(b, cuda)).cpu().numpy(), got)
+    small = _ext.linear(_dev(x[:4000], cuda), _dev(w, cuda), _dev(b, cuda)).cpu().numpy()   # CUDA cores
+    assert _max_rel_err(small, got[:4000]) <= FP16_TOL
+    q = restatement.quantize_weight(w, 32, 8)
+    weight = QuantizedWeight(_dev(q['weight'].view(np.int32), cuda), _dev(q['scales'], cuda),
+                             _dev(q['biases'], cuda), 32, 8, c_in, c_out, (1, 1, 1), 'linear')
+    coords = np.zeros((rows, 4), np.int32)
+    coords[:, 1] = np.arange(rows)
+    y = ops.linear(SparseTensor(_dev(coords, cuda), _dev(x, cuda)), weight).feats.cpu().numpy()
+    assert _max_rel_err(y, restatement.quantized_matmul(x, q)) <= FP16_TOL
+    assert hasattr(weight.weight, '_lattice_fp16_matrix')
+    assert _ext.launch_count() > before
+    _ext.check_status(cuda)

@@ -42,11 +42,8 @@ namespace {
 
 constexpr int kTileRows = kPlanTileRows;
 constexpr int kProducerWarps = 8;
-constexpr int kEpilogueWarps = 8;
-constexpr int kThreads = 576;
-constexpr int kMmaWarp = 16;
-constexpr int kLoaderWarp = 17;
-constexpr int kVectorRing = 16;                   // row vectors held in shared memory
+
+constexpr int kVectorRing = 16;                   // most row vectors held in shared memory
 constexpr int kVectorBytes = kPlanTileRows * 4;
 constexpr int kMaxStages = 8;
 constexpr int kMaxAccStages = 8;
@@ -76,6 +73,7 @@ struct PlanConvParams {
     int32_t* status;
     long long wait_budget;
     int stages;
+    int vec_slots;       // row vectors in the shared-memory ring (at most kVectorRing)
     int stage_bytes;     // 32 KB of A rows + the B tile
     int tmem_cols;
     int acc_cols;
@@ -155,13 +153,22 @@ __device__ __forceinline__ void fill_edgeless_rows(const PlanConvParams& p, int 
 // run out of work first) and the epilogue warps: even and odd rounds of the tile loop
 __device__ __forceinline__ bool producers_fill(int tile, int grid) { return ((tile / grid) & 1) == 0; }
 
-__global__ void __launch_bounds__(kThreads, 1)
+// kEpilogueWarps = 8: one CTA per SM, a warp per 32-row quarter of each 128-row half (C_out
+// above 128, where one tile's accumulators fill the tensor memory). kEpilogueWarps = 4: TWO
+// CTAs per SM, each with half the stages, half the tensor memory and four epilogue warps
+// that take both halves in turn; while one CTA's MMA thread is between slabs (barrier
+// test, proxy fence, commit) the other's MMAs keep the pipe busy.
+template <int kEpilogueWarps>
+__global__ void __launch_bounds__((kProducerWarps + kEpilogueWarps + 2) * 32, kEpilogueWarps == 4 ? 2 : 1)
 tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map) {
+    constexpr int kMmaWarp = kProducerWarps + kEpilogueWarps;
+    constexpr int kLoaderWarp = kMmaWarp + 1;
+    constexpr int kHalves = 8 / kEpilogueWarps;    // 128-row halves of a tile per epilogue warp
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* const vec_ring = smem + p.stages * p.stage_bytes;
-    Control& ctl = *reinterpret_cast<Control*>(vec_ring + kVectorRing * kVectorBytes);
+    Control& ctl = *reinterpret_cast<Control*>(vec_ring + p.vec_slots * kVectorBytes);
     volatile int* abort_flag = &ctl.abort_flag;
 
     const int tid = threadIdx.x;
@@ -315,7 +322,7 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                         if (lane == 0) {
                             mbar_arrive(&ctl.vec_empty[vec.index]);
                         }
-                        vec.advance(kVectorRing);
+                        vec.advance(p.vec_slots);
                     }
                 }
             }
@@ -335,7 +342,7 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                     if (lane == 0) {
                         mbar_arrive(&ctl.vec_empty[released.index]);
                     }
-                    released.advance(kVectorRing);
+                    released.advance(p.vec_slots);
                 }
                 return true;
             };
@@ -372,8 +379,8 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                         // last slab wait on the slab's first entry, so that the whole warp
                         // waits and decides together): up to two trips round the ring away.
                         const int position = vec.index + (uv ? o : o_low);
-                        const int slot = position % kVectorRing;
-                        const uint32_t phase = vec.phase ^ static_cast<uint32_t>((position / kVectorRing) & 1);
+                        const int slot = position % p.vec_slots;
+                        const uint32_t phase = vec.phase ^ static_cast<uint32_t>((position / p.vec_slots) & 1);
                         if (!wait_warp(&ctl.vec_full[slot], phase)) {
                             ok = false;
                             break;
@@ -423,7 +430,7 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                     ok = false;
                 }
                 for (int i = 0; i < present; ++i) {
-                    vec.advance(kVectorRing);
+                    vec.advance(p.vec_slots);
                 }
             }
         }
@@ -434,33 +441,41 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                 fill_edgeless_rows(p, tile, warp, lane);
             }
         }
-    } else if (warp < 16) {
+    } else if (warp < kMmaWarp) {
         // ======================= epilogue =======================
-        const int ew = warp - 8;
+        const int ew = warp - kProducerWarps;
         const int quarter = ew & 3;       // TMEM lanes 32*quarter .. +31 (warp index % 4)
-        const int half_tile = ew >> 2;    // which 128-row half of the tile
-        const int tile_row = half_tile * 128 + quarter * 32 + lane;
+        const int first_half = kHalves == 1 ? ew >> 2 : 0;   // the 128-row halves this warp stores
         bool ok = true;
         int local_tile = 0;
-        // the output row and the offset mask of a tile are fetched one tile ahead
-        auto tile_output_row = [&](int tile) -> int {
-            const int position = tile * kTileRows + tile_row;
+        // the output rows and the offset mask of a tile are fetched one tile ahead
+        auto tile_output_row = [&](int tile, int half_tile) -> int {
+            const int position = tile * kTileRows + half_tile * 128 + quarter * 32 + lane;
             if (tile >= p.num_tiles || position >= p.out_capacity) {
                 return -1;
             }
             return p.row_order != nullptr ? __ldg(p.row_order + position) : position;
         };
-        int next_row = tile_output_row(blockIdx.x);
+        int next_row[kHalves];
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h) {
+            next_row[h] = tile_output_row(blockIdx.x, first_half + h);
+        }
         int2 next_info = load_info(p, blockIdx.x, active);
         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += grid, ++local_tile) {
-            int row = next_row;
+            int rows[kHalves];
             const int2 info = next_info;
-            next_row = tile_output_row(tile + grid);
-            next_info = load_info(p, tile + grid, active);
-            if (row >= p.out_capacity || (row < 0 && tile * kTileRows + tile_row < p.out_capacity)) {
-                raise_status(p.status, LAT_STATUS_BAD_INDEX);
-                row = -1;
+#pragma unroll
+            for (int h = 0; h < kHalves; ++h) {
+                rows[h] = next_row[h];
+                next_row[h] = tile_output_row(tile + grid, first_half + h);
+                const int position = tile * kTileRows + (first_half + h) * 128 + quarter * 32 + lane;
+                if (rows[h] >= p.out_capacity || (rows[h] < 0 && position < p.out_capacity)) {
+                    raise_status(p.status, LAT_STATUS_BAD_INDEX);
+                    rows[h] = -1;
+                }
             }
+            next_info = load_info(p, tile + grid, active);
             bool computed = false;
             int a = 0;
             if (tile < active) {
@@ -473,10 +488,12 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                 tc_fence_after();
                 computed = info.x != 0;
             }
-            __half* out_row = row >= 0 ? p.out + static_cast<size_t>(row) * p.c_out : nullptr;
             if (!computed) {
                 if (tile < active || !producers_fill(tile, grid)) {
-                    fill_edgeless_rows(p, tile, ew, lane);
+#pragma unroll
+                    for (int h = 0; h < kHalves; ++h) {
+                        fill_edgeless_rows(p, tile, (first_half + h) * 4 + quarter, lane);
+                    }
                 }
                 if (tile < active) {
                     tc_fence_before();
@@ -487,35 +504,40 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                 }
                 continue;
             }
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   static_cast<uint32_t>((2 * a + half_tile) * p.acc_cols);
-            for (int c0 = 0; c0 < p.c_out; c0 += 32) {
-                uint32_t v[32];
-                const int width = min(32, p.c_out - c0);  // 32 or 16
-                if (width == 32) {
-                    tmem_load_32(taddr + c0, v);
-                } else {
-                    tmem_load_16(taddr + c0, v);
-                }
-                tmem_load_wait();
-                if (out_row != nullptr) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        if (i < width) {
-                            __half2 h[4];
+            for (int h = 0; h < kHalves; ++h) {
+                const int half_tile = first_half + h;
+                __half* out_row = rows[h] >= 0 ? p.out + static_cast<size_t>(rows[h]) * p.c_out : nullptr;
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                       static_cast<uint32_t>((2 * a + half_tile) * p.acc_cols);
+                for (int c0 = 0; c0 < p.c_out; c0 += 32) {
+                    uint32_t v[32];
+                    const int width = min(32, p.c_out - c0);  // 32 or 16
+                    if (width == 32) {
+                        tmem_load_32(taddr + c0, v);
+                    } else {
+                        tmem_load_16(taddr + c0, v);
+                    }
+                    tmem_load_wait();
+                    if (out_row != nullptr) {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                __half hx = __float2half_rn(__uint_as_float(v[i + 2 * j]));
-                                __half hy = __float2half_rn(__uint_as_float(v[i + 2 * j + 1]));
-                                if (p.bias != nullptr) {
-                                    hx = __float2half_rn(__half2float(hx) +
-                                                         __half2float(__ldg(p.bias + c0 + i + 2 * j)));
-                                    hy = __float2half_rn(__half2float(hy) +
-                                                         __half2float(__ldg(p.bias + c0 + i + 2 * j + 1)));
+                        for (int i = 0; i < 32; i += 8) {
+                            if (i < width) {
+                                __half2 pair[4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    __half hx = __float2half_rn(__uint_as_float(v[i + 2 * j]));
+                                    __half hy = __float2half_rn(__uint_as_float(v[i + 2 * j + 1]));
+                                    if (p.bias != nullptr) {
+                                        hx = __float2half_rn(__half2float(hx) +
+                                                             __half2float(__ldg(p.bias + c0 + i + 2 * j)));
+                                        hy = __float2half_rn(__half2float(hy) +
+                                                             __half2float(__ldg(p.bias + c0 + i + 2 * j + 1)));
+                                    }
+                                    pair[j] = __halves2half2(hx, hy);
                                 }
-                                h[j] = __halves2half2(hx, hy);
+                                *reinterpret_cast<uint4*>(out_row + c0 + i) = *reinterpret_cast<uint4*>(pair);
                             }
-                            *reinterpret_cast<uint4*>(out_row + c0 + i) = *reinterpret_cast<uint4*>(h);
                         }
                     }
                 }
@@ -608,7 +630,7 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
             } else {
                 mbar_arrive(&ctl.vec_full[vec.index]);
             }
-            vec.advance(kVectorRing);
+            vec.advance(p.vec_slots);
             return true;
         };
         int2 batch = load_info(p, blockIdx.x + lane * grid, active);
@@ -733,24 +755,42 @@ int run_tc_conv_plan(
     p.status = status;
     p.wait_budget = wait_budget_cycles();
     p.acc_cols = pow2_at_least(out_channels, 32);
-    p.acc_stages = std::min(kMaxAccStages, 512 / (2 * p.acc_cols));
-    p.tmem_cols = p.acc_stages * 2 * p.acc_cols;
     // every B tile on a 1024-byte boundary (the swizzle pattern repeats every eight rows)
     p.stage_bytes = kSlabBytesA + static_cast<int>(align_up(static_cast<size_t>(out_channels) * 128, 1024));
     const int ctl_bytes = static_cast<int>(align_up(sizeof(Control), 16));
-    const int ring_bytes = kVectorRing * kVectorBytes;
-    const int smem_budget = 227 * 1024 - 1024 /*alignment slack*/ - ring_bytes - ctl_bytes;
-    p.stages = std::min(kMaxStages, smem_budget / p.stage_bytes);
-    LAT_REQUIRE(p.stages >= 2, "internal: shared-memory plan leaves no room for the stage ring.");
-    const size_t smem_bytes = 1024 + static_cast<size_t>(p.stages) * p.stage_bytes + ring_bytes + ctl_bytes;
+    // Two CTAs per SM where two tiles' accumulators fit half of the tensor memory (C_out up to
+    // 128): each gets half of the SM's shared memory (228 KB less 1 KB per CTA that the system
+    // keeps) and of its 512 TMEM columns. Otherwise one CTA with everything.
+    bool paired = out_channels <= 128;
+    int smem_per_cta = paired ? (228 * 1024) / 2 - 1024 : 227 * 1024;
+    p.vec_slots = paired ? kVectorRing / 2 : kVectorRing;
+    int budget = smem_per_cta - 1024 /*alignment slack*/ - p.vec_slots * kVectorBytes - ctl_bytes;
+    if (paired && budget / p.stage_bytes < 2) {
+        paired = false;
+        smem_per_cta = 227 * 1024;
+        p.vec_slots = kVectorRing;
+        budget = smem_per_cta - 1024 - p.vec_slots * kVectorBytes - ctl_bytes;
+    }
+    const int tmem_budget = paired ? 256 : 512;
+    p.acc_stages = std::min(kMaxAccStages, tmem_budget / (2 * p.acc_cols));
+    p.tmem_cols = p.acc_stages * 2 * p.acc_cols;
+    p.stages = std::min(kMaxStages, budget / p.stage_bytes);
+    LAT_REQUIRE(p.stages >= 2 && p.acc_stages >= 1,
+                "internal: shared-memory plan leaves no room for the stage ring.");
+    const size_t smem_bytes =
+        1024 + static_cast<size_t>(p.stages) * p.stage_bytes + p.vec_slots * kVectorBytes + ctl_bytes;
 
     int device = 0;
     LAT_CUDA_CHECK(cudaGetDevice(&device));
     int sm_count = 0;
     LAT_CUDA_CHECK(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
-    const int grid = std::max(1, std::min(p.num_tiles, sm_count));
+    const int grid = std::max(1, std::min(p.num_tiles, (paired ? 2 : 1) * sm_count));
+    auto kernel = paired ? tc_conv_plan_kernel<4> : tc_conv_plan_kernel<8>;
+    const int threads = (kProducerWarps + (paired ? 4 : 8) + 2) * 32;
     LAT_CUDA_CHECK(cudaFuncSetAttribute(
-        tc_conv_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes)));
+        kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes)));
+    LAT_CUDA_CHECK(cudaFuncSetAttribute(
+        kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     // B tiles by TMA when a slab's two units share their kernel offset (C_in a multiple of
     // 64): a 3-D map over the fp16 weights with the kernel offset as its own dimension
     CUtensorMap b_map{};
@@ -774,7 +814,7 @@ int run_tc_conv_plan(
             p.b_k_outer = k_outer ? 1 : 0;
         }
     }
-    tc_conv_plan_kernel<<<grid, kThreads, smem_bytes, stream>>>(p, b_map);
+    kernel<<<grid, threads, smem_bytes, stream>>>(p, b_map);
     LAT_LAUNCH_CHECK();
     return LAT_OK;
 }

@@ -264,7 +264,15 @@ class KernelRelation:
         if view.row_masks.shape[1] != 1:
             raise ValueError('sorted implicit GEMM view currently supports K <= 32.')
         masks = view.row_masks[:, 0]
-        order = torch.argsort(masks, stable=True).to(torch.int32)
+        if self.n_kernels is not None and self.n_kernels <= 31:
+            # the native stable radix sort of the masks; every row takes part, as in the
+            # reference's argsort (masks of at most 31 bits sort alike signed and unsigned)
+            from mlx_lattice_b200 import _ext
+
+            every_row = torch.tensor([0, int(masks.shape[0])], dtype=torch.int32, device=masks.device)
+            order = _ext.build_mask_row_order(view.row_masks, every_row, self.n_kernels)
+        else:
+            order = torch.argsort(masks, stable=True).to(torch.int32)
         sorted_map = view.out_in_map[order.long()]
         n = int(view.out_in_map.shape[0])
         tiles = (n + 63) // 64

@@ -325,3 +325,28 @@ def test_invalid_arguments_raise_value_error(cuda):
         _ext.build_kernel_relation(coords[:, :3], _active(10, cuda), 3, 1, 0, 1)
     with pytest.raises(RuntimeError, match='no CPU route'):
         _ext.build_kernel_relation(coords.cpu(), _active(10, cuda), 3, 1, 0, 1)
+
+
+def test_sorted_implicit_gemm_view_uses_the_reference_order(cuda):
+    """The mask-sorted view (mlx_lattice/core/relations/views.py:467-510): rows in the order
+    of a stable argsort of their offset masks (every row, active or not), the gathered map,
+    and the OR of the masks over 16-row groups -- built with the native radix sort."""
+    from mlx_lattice_b200.core import SparseTensor
+
+    coords = synthetic.lidar_batch(2, 2, 3000)
+    x = SparseTensor(torch.from_numpy(coords).to(cuda),
+                     torch.zeros((coords.shape[0], 4), dtype=torch.float16, device=cuda))
+    relation = x.coord_manager.kernel_relation(x.coord_key, kernel_size=3, stride=2)
+    view = relation.require_implicit_gemm()
+    masks = view.row_masks[:, 0].cpu().numpy()
+    got = relation.require_sorted_implicit_gemm()
+    order = np.argsort(masks, kind='stable').astype(np.int32)
+    assert np.array_equal(got.reorder_rows.cpu().numpy(), order)
+    sorted_map = view.out_in_map.cpu().numpy()[order]
+    assert np.array_equal(got.sorted_out_in_map.cpu().numpy(), sorted_map)
+    assert np.array_equal(got.sorted_kv_out_in_map.cpu().numpy(), sorted_map.T)
+    n = masks.shape[0]
+    padded = np.zeros(((n + 63) // 64) * 64, np.int32)
+    padded[:n] = masks[order]
+    want_tiles = np.bitwise_or.reduce(padded.reshape(-1, 16), axis=1)
+    assert np.array_equal(got.tile_masks.cpu().numpy(), want_tiles)

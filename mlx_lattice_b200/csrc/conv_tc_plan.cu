@@ -20,7 +20,7 @@
 //              no multicast) issued by one thread.
 //   warp 16    one thread issues the MMAs (8 per slab), commits the stage back to the
 //              producers and, per tile, the accumulator to the epilogue.
-//   warps 8-15 epilogue: tcgen05.ld, optional bias, one cast to fp16, 16-byte stores.
+//   warps 8-15 epilogue: tcgen05.ld, optional bias, one cast to fp16, 32-byte stores.
 // Every mbarrier wait is bounded by a clock budget (lat_set_wait_budget_cycles) and its
 // verdict is made uniform across the warp; on expiry the kernel records
 // LAT_STATUS_WAIT_TIMEOUT, every role leaves its loop, the CTA lets copies in flight land
@@ -79,6 +79,7 @@ struct PlanConvParams {
     int acc_cols;
     int acc_stages;
     int num_tiles;
+    int wide_stores;     // 1: `out` is 32-byte aligned and rows are stored 32 bytes at a time
     int b_tma;           // 1: the B tile of a slab is one TMA box (C_in a multiple of 64)
     int b_k_outer;       // tensor-map dimension order: 1 = (C_in, C_out, K), 0 = (C_in, K, C_out)
 };
@@ -147,6 +148,15 @@ __device__ __forceinline__ void fill_edgeless_rows(const PlanConvParams& p, int 
             reinterpret_cast<uint4*>(p.out + static_cast<size_t>(target) * p.c_out)[c] = piece;
         }
     }
+}
+
+// Sixteen fp16 values as one 32-byte store (dst 32-byte aligned): each lane of the epilogue
+// writes its own output row, so a 16-byte store fills half a 32-byte sector and the row's
+// next 16 bytes arrive as a second request; whole sectors halve the requests.
+__device__ __forceinline__ void store_f16x16(__half* dst, const uint4& lo, const uint4& hi) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(lo.x), "r"(lo.y),
+                 "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                 : "memory");
 }
 
 // the tiles past the last one with an edge are shared between the producer warps (which
@@ -521,11 +531,11 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                     tmem_load_wait();
                     if (out_row != nullptr) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
+                        for (int i = 0; i < 32; i += 16) {
                             if (i < width) {
-                                __half2 pair[4];
+                                __half2 pair[8];
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) {
+                                for (int j = 0; j < 8; ++j) {
                                     __half hx = __float2half_rn(__uint_as_float(v[i + 2 * j]));
                                     __half hy = __float2half_rn(__uint_as_float(v[i + 2 * j + 1]));
                                     if (p.bias != nullptr) {
@@ -536,7 +546,15 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                                     }
                                     pair[j] = __halves2half2(hx, hy);
                                 }
-                                *reinterpret_cast<uint4*>(out_row + c0 + i) = *reinterpret_cast<uint4*>(pair);
+                                const uint4 lo = *reinterpret_cast<uint4*>(pair);
+                                const uint4 hi = *reinterpret_cast<uint4*>(pair + 4);
+                                __half* const dst = out_row + c0 + i;
+                                if (p.wide_stores) {
+                                    store_f16x16(dst, lo, hi);
+                                } else {
+                                    *reinterpret_cast<uint4*>(dst) = lo;
+                                    *reinterpret_cast<uint4*>(dst + 8) = hi;
+                                }
                             }
                         }
                     }
@@ -753,6 +771,8 @@ int run_tc_conv_plan(
     p.bias = static_cast<const __half*>(bias);
     p.out = static_cast<__half*>(out);
     p.status = status;
+    // C_out is a multiple of 16, so every row starts on a 32-byte boundary when `out` does
+    p.wide_stores = reinterpret_cast<uintptr_t>(out) % 32 == 0 ? 1 : 0;
     p.wait_budget = wait_budget_cycles();
     p.acc_cols = pow2_at_least(out_channels, 32);
     // every B tile on a 1024-byte boundary (the swizzle pattern repeats every eight rows)

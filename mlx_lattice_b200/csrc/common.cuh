@@ -188,16 +188,31 @@ __device__ __forceinline__ int warp_exclusive_scan(int v, int& total) {
 using Slot = unsigned long long;
 constexpr Slot kEmptySlot = ~0ull;
 
-// Two 32-bit hashes of a coordinate. Both start from a linear form of the four ints
-// (hash_linear), so the form of `base + offset` is the sum of the forms: a kernel map
-// computes the form of each output row once and adds a per-offset constant. `index`
-// pushes its form through an integer finaliser and picks the bucket; `tag` is the
-// second form as it is and only has to differ between keys that share a bucket.
-__device__ __forceinline__ void hash_linear(Coord c, uint32_t& u, uint32_t& t) {
+// Two 32-bit hashes of a coordinate. Both start from a linear form of the four ints, so
+// the form of `base + offset` is the sum of the forms: a kernel map computes the form of
+// each output row once and adds a per-offset constant. `index` pushes its form through an
+// integer finaliser and picks the bucket; `tag` is the second form as it is and only has to
+// differ between keys that share a bucket.
+//
+// The index form takes z in groups of four (z >> 2, flooring): the four voxels of an aligned
+// z-run share their home bucket, which has exactly their four slots. A kernel map probes
+// z - 1, z, z + 1 of every (x, y) column of its footprint, and those lie in one group (two
+// when z sits at a group's edge): one bucket read answers them (see the probe loop of
+// map_single_pass_kernel). The tag keeps the full z, so the keys of a group differ in it.
+constexpr uint32_t kHashX = 0x9E3779B1u, kHashY = 0x85EBCA77u, kHashZ = 0xC2B2AE3Du, kHashB = 0x27D4EB2Fu;
+constexpr int kHashZShift = 2;
+
+// index form without its z term, and the tag form
+__device__ __forceinline__ void hash_linear(Coord c, uint32_t& u_xyb, uint32_t& t) {
     const uint32_t b = static_cast<uint32_t>(c.b), x = static_cast<uint32_t>(c.x);
     const uint32_t y = static_cast<uint32_t>(c.y), z = static_cast<uint32_t>(c.z);
-    u = x * 0x9E3779B1u + y * 0x85EBCA77u + z * 0xC2B2AE3Du + b * 0x27D4EB2Fu;
+    u_xyb = x * kHashX + y * kHashY + b * kHashB;
     t = x * 0x165667B1u + y * 0xD3A2646Du + z * 0xFD7046C5u + b * 0xB55A4F09u;
+}
+
+// z term of the index form
+__device__ __forceinline__ uint32_t hash_z_term(int z) {
+    return static_cast<uint32_t>(z >> kHashZShift) * kHashZ;
 }
 
 __device__ __forceinline__ uint32_t hash_finalize(uint32_t u) {
@@ -212,7 +227,7 @@ __device__ __forceinline__ uint32_t hash_finalize(uint32_t u) {
 __device__ __forceinline__ void hash_coord(Coord c, uint32_t& index, uint32_t& tag) {
     uint32_t u;
     hash_linear(c, u, tag);
-    index = hash_finalize(u);
+    index = hash_finalize(u + hash_z_term(c.z));
 }
 
 // Buckets of four consecutive slots (one 32-byte sector). Inserts take the first empty
@@ -267,6 +282,22 @@ __device__ __forceinline__ Bucket load_bucket(const Slot* slots, uint32_t base) 
     return b;
 }
 
+// The same load under a predicate, without a branch (the result is undefined when `wanted`
+// is false): independent probes of a loop body stay independent loads.
+__device__ __forceinline__ Bucket load_bucket_if(const Slot* slots, uint32_t base, bool wanted) {
+    Bucket b;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %9, 0;\n"
+        "@p ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
+        "}"
+        : "=r"(b.lo.x), "=r"(b.lo.y), "=r"(b.lo.z), "=r"(b.lo.w), "=r"(b.hi.x), "=r"(b.hi.y),
+          "=r"(b.hi.z), "=r"(b.hi.w)
+        : "l"(slots + base), "r"(wanted ? 1 : 0));
+    return b;
+}
+
 // Scan one loaded bucket without data-dependent branches except the rare verification
 // of a tag match: returns the row (>= 0), -1 when the key is absent for sure, -2 when
 // the bucket is full without a match (continue with the next bucket). A row word of all
@@ -290,17 +321,20 @@ scan_bucket(const Bucket& b, uint32_t tag, Coord key, KeyOf key_of) {
     return empty != 0 ? -1 : -2;
 }
 
-// Tag-only scan without branches: the row of the first slot before the first empty one
-// whose tag matches (the caller still has to compare coordinates), -1 when the key is
-// absent for sure, -2 when the bucket is full without a tag match.
+// Tag-only scan without branches: the row of the first slot, in slot order, whose tag
+// matches (the caller still has to compare coordinates), -1 when the key is absent for
+// sure, -2 when the bucket is full without a tag match. A bucket fills from the front and
+// an empty slot is all ones, tag word included: a key that is present sits before the
+// first empty slot and is met first; a tag of all ones that meets an empty slot reads its
+// row word, -1, which says "absent", as it should. The bucket is full exactly when its
+// last slot is taken.
 __device__ __forceinline__ int scan_bucket_tags(const Bucket& b, uint32_t tag) {
-    const unsigned empty = (b.lo.x == 0xFFFFFFFFu ? 1u : 0u) | (b.lo.z == 0xFFFFFFFFu ? 2u : 0u) |
-                           (b.hi.x == 0xFFFFFFFFu ? 4u : 0u) | (b.hi.z == 0xFFFFFFFFu ? 8u : 0u);
-    unsigned match = (b.lo.y == tag ? 1u : 0u) | (b.lo.w == tag ? 2u : 0u) |
-                     (b.hi.y == tag ? 4u : 0u) | (b.hi.w == tag ? 8u : 0u);
-    match &= ((empty & (0u - empty)) - 1u) & 0xFu;
-    const uint32_t row = (match & 1u) ? b.lo.x : (match & 2u) ? b.lo.z : (match & 4u) ? b.hi.x : b.hi.z;
-    return match != 0 ? static_cast<int>(row) : (empty != 0 ? -1 : -2);
+    const int none = b.hi.z != 0xFFFFFFFFu ? -2 : -1;
+    return b.lo.y == tag   ? static_cast<int>(b.lo.x)
+           : b.lo.w == tag ? static_cast<int>(b.lo.z)
+           : b.hi.y == tag ? static_cast<int>(b.hi.x)
+           : b.hi.w == tag ? static_cast<int>(b.hi.z)
+                           : none;
 }
 
 template <typename KeyOf>

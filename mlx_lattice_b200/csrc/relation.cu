@@ -17,6 +17,8 @@
 #include <algorithm>
 #include <cstdlib>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace lat {
@@ -531,23 +533,68 @@ __global__ void __launch_bounds__(kBlockThreads, 5) map_single_pass_kernel(
     }
     // 1. probe, lane = output row: K independent bucket reads per lane
     uint32_t u_row = 0, t_row = 0;  // linear hash forms of this row's base coordinate
+    const int z_row = mine.z * p.sz - p.pz;
     if (forward) {
-        hash_linear(Coord{mine.b, mine.x * p.sx - p.px, mine.y * p.sy - p.py, mine.z * p.sz - p.pz},
-                    u_row, t_row);
+        hash_linear(Coord{mine.b, mine.x * p.sx - p.px, mine.y * p.sy - p.py, z_row}, u_row, t_row);
     }
     unsigned my_mask = 0;
     unsigned my_overflow = 0;  // offsets whose first bucket was full without a tag match
     int* warp_hits = s_hits + warp * 32 * K;
     int* my_hits = warp_hits + lane * K;
     const bool row_live = my_row < n_out;
-    if (row0 < n_out) {
+    // Column probing: with the forward rule and a z extent of at most five voxels, the KZ
+    // candidates of one (x, y) column of the footprint lie in at most two z-groups of the
+    // table's hash, the group of the first and the group of the last: two bucket reads (one
+    // when the groups coincide) answer the column.
+    auto probe_columns = [&](auto kz_tag) {
+        constexpr int KZ = decltype(kz_tag)::value;
+        const int columns = K / KZ;
+#pragma unroll 1
+        for (int c = 0; c < columns; ++c) {
+            const int k0 = c * KZ;
+            const uint32_t u_col = u_row + static_cast<uint32_t>(s_offset_hash[k0].x);
+            const int z_first = z_row + s_offset[k0].z;
+            const int z_last = z_row + s_offset[k0 + KZ - 1].z;
+            const uint32_t base_a =
+                hash_finalize(u_col + hash_z_term(z_first)) & p.table_mask & ~(kBucketSlots - 1);
+            const uint32_t base_b =
+                hash_finalize(u_col + hash_z_term(z_last)) & p.table_mask & ~(kBucketSlots - 1);
+            const bool two = (z_first >> kHashZShift) != (z_last >> kHashZShift);
+            const Bucket a = load_bucket_if(p.table, base_a, row_live);
+            const Bucket b = load_bucket_if(p.table, base_b, row_live && two);
+#pragma unroll
+            for (int j = 0; j < KZ; ++j) {
+                const int k = k0 + j;
+                const bool in_a = ((z_row + s_offset[k].z) >> kHashZShift) == (z_first >> kHashZShift);
+                const uint32_t tag = t_row + static_cast<uint32_t>(s_offset_hash[k].y);
+                const int found_a = scan_bucket_tags(a, tag);
+                const int found_b = scan_bucket_tags(b, tag);
+                const int found = row_live ? (in_a ? found_a : found_b) : -1;
+                my_mask |= found >= 0 ? (1u << k) : 0u;
+                my_overflow |= found == -2 ? (1u << k) : 0u;
+                if (found >= 0) {
+                    my_hits[k] = found;
+                }
+            }
+        }
+    };
+    const int z_span = (p.geo.kz - 1) * p.geo.dz;
+    if (row0 >= n_out) {
+        // nothing to probe
+    } else if (forward && z_span <= 4 && p.geo.kz == 3) {
+        probe_columns(std::integral_constant<int, 3>{});
+    } else if (forward && z_span <= 4 && p.geo.kz == 2) {
+        probe_columns(std::integral_constant<int, 2>{});
+    } else if (forward && p.geo.kz == 1) {
+        probe_columns(std::integral_constant<int, 1>{});
+    } else {
 #pragma unroll 3
         for (int k = 0; k < K; ++k) {
             bool live = row_live;
             uint32_t index = 0, tag = 0;
             if (forward) {
                 const int2 h = s_offset_hash[k];
-                index = hash_finalize(u_row + static_cast<uint32_t>(h.x));
+                index = hash_finalize(u_row + static_cast<uint32_t>(h.x) + hash_z_term(z_row + s_offset[k].z));
                 tag = t_row + static_cast<uint32_t>(h.y);
             } else if (live) {
                 const int4 off = s_offset[k];
@@ -569,22 +616,39 @@ __global__ void __launch_bounds__(kBlockThreads, 5) map_single_pass_kernel(
     }
     __syncwarp();
 
-    // 2. verify this lane's row
+    // 2. verify this lane's row, four hits at a time (their coordinate loads overlap)
     {
         unsigned bits = my_mask;
         while (bits != 0) {
-            const int k = __ffs(bits) - 1;
-            bits &= bits - 1;
-            const int4 off = s_offset[k];
-            Coord expect;
-            candidate_of(p, mine, off.x, off.y, off.z, expect);
-            const int hit = warp_hits[lane * K + k];
-            if (!(key_of(hit) == expect)) {
-                const int exact = table_find(p.table, p.table_mask, expect, key_of);
-                if (exact >= 0) {
-                    warp_hits[lane * K + k] = exact;
-                } else {
-                    my_mask &= ~(1u << k);
+            int ks[4];
+            Coord got[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                ks[u] = bits != 0 ? __ffs(bits) - 1 : -1;
+                bits &= bits - 1;   // 0 stays 0
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (ks[u] >= 0) {
+                    got[u] = key_of(warp_hits[lane * K + ks[u]]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (ks[u] < 0) {
+                    continue;
+                }
+                const int k = ks[u];
+                const int4 off = s_offset[k];
+                Coord expect;
+                candidate_of(p, mine, off.x, off.y, off.z, expect);
+                if (!(got[u] == expect)) {
+                    const int exact = table_find(p.table, p.table_mask, expect, key_of);
+                    if (exact >= 0) {
+                        warp_hits[lane * K + k] = exact;
+                    } else {
+                        my_mask &= ~(1u << k);
+                    }
                 }
             }
         }

@@ -332,13 +332,15 @@ def kernel_map_benchmark(device, steps: int, peaks: dict, flush) -> dict:
         # HBM-class bytes of one build: coordinates read (16 B/row), table clear and insert
         # (8 B/slot, 8 B/row), the pairs (12 B/edge), row offsets, output coordinates when
         # strided; the zero tail of the three static-capacity edge arrays (27 n entries each)
-        # is counted apart; the 27 probes per output row read one 32-byte bucket each from
-        # the table, which lives in L2.
+        # is counted apart; the probes read 32-byte buckets from the table, which lives in
+        # L2: one or two per (x, y) column of the footprint, 13.5 per output row on average
+        # (the table hashes z in groups of four; ncu: 508 MB from L2 for the 1 M rows of the
+        # submanifold map, coordinates and verification loads included).
         useful = n * 16 + 8 * slots + 8 * n + 12 * edges + 4 * (n + 1)
         if stride != 1:
             useful += n * 16 + 8 * slots + 8 * n + 16 * n_out
         tail = 12 * (27 * n - edges)
-        probes = 32 * 27 * n_out
+        probes = int(32 * 13.5 * n_out)
         out[name] = {
             'mcoords_per_s': n / ms / 1e3, 'ms': ms, 'edges': edges, 'out_rows': n_out,
             'hbm_bytes': useful, 'hbm_gb_s': useful / ms / 1e6,
@@ -347,7 +349,8 @@ def kernel_map_benchmark(device, steps: int, peaks: dict, flush) -> dict:
             'with_zero_tail_gb_s': (useful + tail) / ms / 1e6,
             'with_zero_tail_frac_of_hbm_peak': (useful + tail) / ms / 1e6 / peaks['hbm_gbs'],
             'l2_probe_bytes': probes, 'l2_probe_gb_s': probes / ms / 1e6,
-            'bound': 'L2 latency of the probes (DRAM busy a few per cent: profiles/)',
+            'bound': 'instruction issue and the L2 latency of the probes (DRAM busy a few per cent: '
+                     'profiles/)',
         }
         del holder
     return out

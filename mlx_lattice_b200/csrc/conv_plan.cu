@@ -135,15 +135,18 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(int2* tile_info, int nu
     }
 }
 
-// pass 3: the row vectors
+// pass 3: the row vectors. Thread t owns vector slot t, that is tile row (t % 8) * 32 + t / 8:
+// the lanes of a warp then write 32 consecutive entries of a vector (one 128-byte line)
+// instead of 32 entries that lie 32 bytes apart.
 __global__ void __launch_bounds__(kPlanTileRows) plan_fill_kernel(PlanBuildParams p) {
     const int n_out = clamp_count(p.counts + 1, p.out_capacity);
     const int edge_total = clamp_count(p.counts, p.edge_capacity);
     const int2 info = p.tile_info[blockIdx.x];
     const uint32_t mask = static_cast<uint32_t>(info.x);
     const int present = __popc(mask);
-    const int r = threadIdx.x;
-    int32_t* mine = p.vectors + static_cast<size_t>(info.y) * kPlanTileRows + plan_slot(r);
+    const int slot = threadIdx.x;
+    const int r = (slot & 7) * 32 + (slot >> 3);   // plan_slot(r) == slot
+    int32_t* mine = p.vectors + static_cast<size_t>(info.y) * kPlanTileRows + slot;
     for (int o = 0; o < present; ++o) {
         mine[static_cast<size_t>(o) * kPlanTileRows] = -1;
     }

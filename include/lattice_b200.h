@@ -324,12 +324,15 @@ int lat_dequantize_conv_weights(
  * 256-row tiles; per tile the plan holds the mask of kernel offsets its rows use and,
  * per used offset, the input row of each tile row (-1 = none). Build it once per
  * relation after `row_order`, then pass `plan` together with the same `row_order` to
- * the convolutions over that relation. kernel_count <= 32. */
+ * the convolutions over that relation. kernel_count <= 32. Optional `row_masks`
+ * [out_capacity] (bit k = the row has an edge at offset k, as the kernel-map builders and
+ * lat_build_relation_implicit_gemm_view write them) spares the builder a walk over the
+ * edges; they must describe the same relation. */
 size_t lat_conv_plan_bytes(int32_t out_capacity, int32_t kernel_count);
 int lat_build_conv_plan(
     const int32_t* in_rows, const int32_t* kernel_ids, int32_t edge_capacity,
     const int32_t* counts, const int32_t* row_offsets, int32_t in_capacity,
-    int32_t out_capacity, int32_t kernel_count, const int32_t* row_order,
+    int32_t out_capacity, int32_t kernel_count, const int32_t* row_order, const int32_t* row_masks,
     void* plan, size_t plan_bytes, int32_t* status, void* stream);
 
 /* 1 when the tensor-core (tcgen05) route serves this shape, 0 when the CUDA-core

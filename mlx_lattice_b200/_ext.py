@@ -907,13 +907,18 @@ def conv_uses_tensor_cores(dtype, n_kernels, in_channels, out_channels, bits=0, 
 
 
 def build_conv_plan(in_rows, kernel_ids, counts, row_offsets, in_capacity: int,
-                    out_capacity: int, kernel_count: int, row_order=None) -> torch.Tensor:
+                    out_capacity: int, kernel_count: int, row_order=None, row_masks=None) -> torch.Tensor:
     """Gather plan of the tensor-core convolution over one relation
     (``lat_build_conv_plan``): per 256-row tile of ``row_order`` the mask of kernel
-    offsets in use and, per used offset, the input row of every tile row."""
+    offsets in use and, per used offset, the input row of every tile row. ``row_masks``
+    (optional, ``(out_capacity, 1)`` int32, the relation's own) saves a walk over the edges."""
     in_rows, kernel_ids = _i32(in_rows, 'in_rows'), _i32(kernel_ids, 'kernel_ids')
     counts, row_offsets = _i32(counts, 'counts'), _i32(row_offsets, 'row_offsets')
     device = in_rows.device
+    if row_masks is not None:
+        row_masks = _i32(row_masks, 'row_masks')
+        if row_masks.device != device or row_masks.numel() != int(out_capacity):
+            raise ValueError('row_masks must hold one int32 word per output row, on the relation device.')
     lib = _lib()
     plan = torch.empty(max(int(lib.lat_conv_plan_bytes(out_capacity, kernel_count)), 256),
                        dtype=torch.uint8, device=device)
@@ -921,7 +926,8 @@ def build_conv_plan(in_rows, kernel_ids, counts, row_offsets, in_capacity: int,
         check(lib.lat_build_conv_plan(
             _ptr(in_rows), _ptr(kernel_ids), int(in_rows.shape[0]), _ptr(counts),
             _ptr(row_offsets), int(in_capacity), int(out_capacity), int(kernel_count),
-            _ptr(row_order), _ptr(plan), plan.numel(), _ptr(status_word(device)), _stream(),
+            _ptr(row_order), _ptr(row_masks), _ptr(plan), plan.numel(), _ptr(status_word(device)),
+            _stream(),
         ))
     return plan
 

@@ -85,7 +85,7 @@ SIGNATURES = {
             c_size_t, P, P]),
     'lat_dequantize_conv_weights': (I, [P, P, P, I, I, I, I, I, I, P, P]),
     'lat_conv_plan_bytes': (c_size_t, [I, I]),
-    'lat_build_conv_plan': (I, [P, P, I, P, P, I, I, I, P, P, c_size_t, P, P]),
+    'lat_build_conv_plan': (I, [P, P, I, P, P, I, I, I, P, P, P, c_size_t, P, P]),
     'lat_conv_uses_tensor_cores': (I, [I, I, I, I, I, I]),
     'lat_mask_order_workspace_bytes': (c_size_t, [I]),
     'lat_build_mask_row_order': (I, [P, I, I, P, P, P, c_size_t, P, P]),

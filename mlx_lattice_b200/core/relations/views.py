@@ -316,5 +316,6 @@ class KernelRelation:
                 self.edges.in_rows, self.edges.kernel_ids, self.counts,
                 self.output_csr.row_offsets, int(self.n_in_capacity), int(self.n_out_capacity),
                 int(self.n_kernels), self.require_row_order(),
+                self.row_masks if self.row_masks is not None and self.row_masks.shape[1] == 1 else None,
             )
         return self._conv_plan

@@ -28,6 +28,7 @@ struct PlanBuildParams {
     const int32_t* row_offsets;
     const int32_t* counts;
     const int32_t* row_order;
+    const int32_t* row_masks;   // optional: bit k of row_masks[row] = the row has an edge at offset k
     int edge_capacity;
     int in_capacity;
     int out_capacity;
@@ -62,7 +63,15 @@ __global__ void __launch_bounds__(kPlanTileRows) plan_mask_kernel(PlanBuildParam
     const int edge_total = clamp_count(p.counts, p.edge_capacity);
     const int row = plan_row(p, blockIdx.x * kPlanTileRows + threadIdx.x);
     uint32_t mask = 0;
-    if (row >= 0 && row < n_out) {
+    if (p.row_masks != nullptr) {
+        // the kernel map already knows which offsets each row uses
+        if (row >= 0 && row < n_out) {
+            mask = static_cast<uint32_t>(__ldg(p.row_masks + row));
+            if (p.kernel_count < 32) {
+                mask &= (1u << p.kernel_count) - 1u;
+            }
+        }
+    } else if (row >= 0 && row < n_out) {
         const int begin = max(__ldg(p.row_offsets + row), 0);
         const int end = min(__ldg(p.row_offsets + row + 1), edge_total);
         for (int e0 = begin; e0 < end; e0 += 4) {
@@ -227,7 +236,7 @@ int lat_build_identity_conv_plan(int32_t rows, void* plan, size_t plan_bytes, vo
 int lat_build_conv_plan(
     const int32_t* in_rows, const int32_t* kernel_ids, int32_t edge_capacity,
     const int32_t* counts, const int32_t* row_offsets, int32_t in_capacity,
-    int32_t out_capacity, int32_t kernel_count, const int32_t* row_order,
+    int32_t out_capacity, int32_t kernel_count, const int32_t* row_order, const int32_t* row_masks,
     void* plan, size_t plan_bytes, int32_t* status, void* stream_ptr
 ) {
     LAT_REQUIRE(out_capacity >= 0 && edge_capacity >= 0 && in_capacity >= 0,
@@ -251,6 +260,7 @@ int lat_build_conv_plan(
     p.row_offsets = row_offsets;
     p.counts = counts;
     p.row_order = row_order;
+    p.row_masks = row_masks;
     p.edge_capacity = edge_capacity;
     p.in_capacity = in_capacity;
     p.out_capacity = out_capacity;

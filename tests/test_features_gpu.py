@@ -175,6 +175,35 @@ def test_conv_with_gather_plan(cuda, oracle, restatement, sphere, c_in, c_out):
     assert np.array_equal(got_q, _qconv(cuda, feats, q, rel, n, 27))
 
 
+def test_gather_plan_from_row_masks(cuda, oracle, sphere):
+    """The plan builder given the relation's row masks (what the kernel map writes) makes
+    the plan it makes from a walk over the edges: same convolution bits."""
+    from mlx_lattice_b200 import _ext
+
+    coords, rel = sphere
+    n = coords.shape[0]
+    r = _rel_dev(rel, cuda)
+    e = int(rel['counts'][0])
+    masks = np.zeros((n, 1), np.int32)
+    np.bitwise_or.at(masks[:, 0], rel['out_rows'][:e], (1 << rel['kernel_ids'][:e]).astype(np.int32))
+    order = _dev(np.random.default_rng(3).permutation(n).astype(np.int32), cuda)
+    rng = np.random.default_rng(41)
+    feats = _dev(rng.normal(size=(n, 64)).astype(np.float16), cuda)
+    w5 = _dev((rng.normal(size=(64, 3, 3, 3, 64)) * 0.05).astype(np.float16), cuda)
+    outs = []
+    for row_masks in (None, _dev(masks, cuda)):
+        plan = _ext.build_conv_plan(r['in_rows'], r['kernel_ids'], r['counts'], r['row_offsets'], n, n, 27,
+                                    order, row_masks)
+        outs.append(_ext.sparse_conv_features(
+            feats, w5, r['in_rows'], r['out_rows'], r['kernel_ids'], r['counts'], r['row_offsets'],
+            out_capacity=n, n_kernels=27, row_order=order, plan=plan))
+    assert torch.equal(outs[0], outs[1])
+    _ext.check_status()
+    with pytest.raises(ValueError, match='row_masks must hold one int32 word per output row'):
+        _ext.build_conv_plan(r['in_rows'], r['kernel_ids'], r['counts'], r['row_offsets'], n, n, 27, order,
+                             _dev(masks[:-1], cuda))
+
+
 def test_gather_plan_strided_and_padding_rows(cuda, oracle, restatement):
     """k=2, s=2 relation whose output capacity exceeds the live rows: plan tiles beyond
     the live rows are empty and their output rows are zero."""

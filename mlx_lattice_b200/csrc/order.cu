@@ -2,7 +2,7 @@
 // the 256-row tiles of the tensor-core convolution see few distinct offsets each
 // (the idea of the reference's mask-sorted view, core/relations/views.py:467-510,
 // built natively). Stable LSD radix sort of (mask, row) with 10-bit digits. A pass is
-// three launches over 2048-row tiles (8 warps x 256 rows): per-tile digit histograms,
+// three launches over 4096-row tiles (8 warps x 512 rows): per-tile digit histograms,
 // a column scan over the tiles, and a scatter that ranks equal digits inside a tile in
 // row order (warp match/ballot inside a 32-row step, running per-warp counters across
 // steps, a prefix over the warps) -- no atomics, so the permutation is a pure function
@@ -22,9 +22,9 @@ constexpr int kDigitBits = 10;
 constexpr int kBuckets = 1 << kDigitBits;
 constexpr int kBinsPerThread = kBuckets / 256;
 constexpr int kWarps = 8;
-constexpr int kSteps = 8;                         // 32-row steps per warp
+constexpr int kSteps = 16;                        // 32-row steps per warp
 constexpr int kRowsPerWarp = 32 * kSteps;
-constexpr int kTile = kWarps * kRowsPerWarp;      // 2048 rows
+constexpr int kTile = kWarps * kRowsPerWarp;      // 4096 rows
 
 struct OrderKeys {
     const uint32_t* keys;      // keys of the previous pass, or
@@ -42,7 +42,7 @@ struct OrderKeys {
     }
 };
 
-// digits of this warp's 256 rows, -1 - lane beyond the end (never equal to a real digit
+// digits of this warp's 512 rows, -1 - lane beyond the end (never equal to a real digit
 // or to another lane's filler)
 __device__ __forceinline__ void load_digits(
     const OrderKeys& in, int first, int shift, int lane, uint32_t (&key)[kSteps], int (&digit)[kSteps]

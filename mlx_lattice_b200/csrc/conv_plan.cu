@@ -98,61 +98,54 @@ __global__ void __launch_bounds__(kPlanTileRows) plan_mask_kernel(PlanBuildParam
     }
 }
 
-// pass 2: exclusive scan of the vectors per tile (one block); the entry after the last
-// tile receives (tiles up to the last one with a non-empty mask, vector total)
-__global__ void __launch_bounds__(1024) plan_scan_kernel(int2* tile_info, int num_tiles) {
-    __shared__ int warp_totals[32];
-    __shared__ int carry;
-    __shared__ int active_tiles;
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) {
-        carry = 0;
-        active_tiles = 0;
-    }
-    __syncthreads();
-    for (int first = 0; first < num_tiles; first += 1024) {
-        const int tile = first + threadIdx.x;
-        int2 info = make_int2(0, 0);
-        if (tile < num_tiles) {
-            info = tile_info[tile];
-        }
-        int wtotal;
-        const int prefix = warp_exclusive_scan(__popc(static_cast<uint32_t>(info.x)), wtotal);
-        if (lane == 0) {
-            warp_totals[warp] = wtotal;
-        }
-        __syncthreads();
-        int before = carry;
-        for (int w = 0; w < warp; ++w) {
-            before += warp_totals[w];
-        }
-        if (tile < num_tiles) {
-            tile_info[tile] = make_int2(info.x, before + prefix);
-            if (info.x != 0) {
-                atomicMax(&active_tiles, tile + 1);
-            }
-        }
-        __syncthreads();
-        if (threadIdx.x == 1023) {
-            carry = before + prefix + __popc(static_cast<uint32_t>(info.x));
-        }
-        __syncthreads();
-    }
-    if (threadIdx.x == 0) {
-        tile_info[num_tiles] = make_int2(active_tiles, carry);
-    }
-}
-
-// pass 3: the row vectors. Thread t owns vector slot t, that is tile row (t % 8) * 32 + t / 8:
-// the lanes of a warp then write 32 consecutive entries of a vector (one 128-byte line)
-// instead of 32 entries that lie 32 bytes apart.
+// pass 2: the row vectors. A block first finds where its tile's vectors start: the number
+// of offsets the tiles before it use (it adds up their masks' population counts itself, a
+// few KB from L2, rather than wait for a one-block scan kernel), and records it in
+// tile_info[tile].y for the convolution; the last tile also writes the closing entry
+// (tiles up to the last one with a non-empty mask, vector total). Thread t owns vector slot
+// t, that is tile row (t % 8) * 32 + t / 8: the lanes of a warp then write 32 consecutive
+// entries of a vector (one 128-byte line) instead of 32 entries that lie 32 bytes apart.
 __global__ void __launch_bounds__(kPlanTileRows) plan_fill_kernel(PlanBuildParams p) {
+    __shared__ int warp_before[kPlanTileRows / 32];
+    __shared__ int warp_last[kPlanTileRows / 32];
     const int n_out = clamp_count(p.counts + 1, p.out_capacity);
     const int edge_total = clamp_count(p.counts, p.edge_capacity);
-    const int2 info = p.tile_info[blockIdx.x];
-    const uint32_t mask = static_cast<uint32_t>(info.x);
+    const int tile = blockIdx.x;
+    const uint32_t mask = static_cast<uint32_t>(p.tile_info[tile].x);
     const int present = __popc(mask);
+    // masks live in the .x words; the .y words are being written by the other blocks
+    const bool closing = tile == p.num_tiles - 1;
+    int before = 0;
+    int last_used = 0;   // one past the last tile with a non-empty mask (closing block only)
+    for (int t = threadIdx.x; t < tile; t += kPlanTileRows) {
+        const uint32_t m = static_cast<uint32_t>(__ldg(&p.tile_info[t].x));
+        before += __popc(m);
+        last_used = m != 0 ? t + 1 : last_used;
+    }
+    before = warp_sum(before);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        last_used = max(last_used, __shfl_xor_sync(0xffffffffu, last_used, d));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        warp_before[threadIdx.x >> 5] = before;
+        warp_last[threadIdx.x >> 5] = last_used;
+    }
+    __syncthreads();
+    before = 0;
+    last_used = 0;
+#pragma unroll
+    for (int w = 0; w < kPlanTileRows / 32; ++w) {
+        before += warp_before[w];
+        last_used = max(last_used, warp_last[w]);
+    }
+    if (threadIdx.x == 0) {
+        p.tile_info[tile].y = before;
+        if (closing) {
+            p.tile_info[p.num_tiles] = make_int2(mask != 0 ? p.num_tiles : last_used, before + present);
+        }
+    }
+    const int2 info = make_int2(static_cast<int>(mask), before);
     const int slot = threadIdx.x;
     const int r = (slot & 7) * 32 + (slot >> 3);   // plan_slot(r) == slot
     int32_t* mine = p.vectors + static_cast<size_t>(info.y) * kPlanTileRows + slot;
@@ -270,8 +263,6 @@ int lat_build_conv_plan(
     p.vectors = reinterpret_cast<int32_t*>(static_cast<char*>(plan) + plan_info_bytes(p.num_tiles));
     p.status = status;
     plan_mask_kernel<<<p.num_tiles, kPlanTileRows, 0, stream>>>(p);
-    LAT_LAUNCH_CHECK();
-    plan_scan_kernel<<<1, 1024, 0, stream>>>(p.tile_info, p.num_tiles);
     LAT_LAUNCH_CHECK();
     plan_fill_kernel<<<p.num_tiles, kPlanTileRows, 0, stream>>>(p);
     LAT_LAUNCH_CHECK();

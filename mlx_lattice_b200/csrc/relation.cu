@@ -152,6 +152,38 @@ __device__ __forceinline__ int block_exclusive_scan(int value, int& block_total)
     return out;
 }
 
+// What a scan over the per-block totals would give block `block`: the sum of the totals of
+// the blocks before it, and the sum of all of them. Every block of a consumer kernel adds
+// them up itself (a few KB from L2) instead of waiting for a one-block scan kernel between
+// the counting kernel and itself. Call with the whole block (blockDim = kBlockThreads).
+__device__ __forceinline__ void block_prefix_of(
+    const int32_t* sums, int count, int block, int& before, int& total
+) {
+    __shared__ int partial_before[kWarpsPerBlock];
+    __shared__ int partial_total[kWarpsPerBlock];
+    int b = 0, t = 0;
+    for (int i = threadIdx.x; i < count; i += kBlockThreads) {
+        const int v = __ldg(sums + i);
+        t += v;
+        b += i < block ? v : 0;
+    }
+    b = warp_sum(b);
+    t = warp_sum(t);
+    if ((threadIdx.x & 31) == 0) {
+        partial_before[threadIdx.x >> 5] = b;
+        partial_total[threadIdx.x >> 5] = t;
+    }
+    __syncthreads();
+    before = 0;
+    total = 0;
+#pragma unroll
+    for (int w = 0; w < kWarpsPerBlock; ++w) {
+        before += partial_before[w];
+        total += partial_total[w];
+    }
+    __syncthreads();
+}
+
 // winners of the downsampled table -> per-block counts
 __global__ void mark_winners_kernel(
     const int32_t* coords, const int32_t* active_ptr, int rows, int sx, int sy, int sz,
@@ -220,12 +252,18 @@ __global__ void scan_blocks_kernel(
     }
 }
 
-// stable compaction of the winners: out_coords in first-seen order
+// stable compaction of the winners: out_coords in first-seen order; block_sums are the
+// per-block winner counts of mark_winners_kernel, *count_out receives their total
 __global__ void compact_winners_kernel(
     const int32_t* coords, const int32_t* active_ptr, int rows, int sx, int sy, int sz,
-    const Slot* table, uint32_t mask, const int32_t* block_offsets, int32_t* out_coords,
-    int out_capacity, int32_t* status
+    const Slot* table, uint32_t mask, const int32_t* block_sums, int32_t* count_out,
+    int32_t* out_coords, int out_capacity, int32_t* status
 ) {
+    int before, all;
+    block_prefix_of(block_sums, gridDim.x, blockIdx.x, before, all);
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        *count_out = all;
+    }
     int active = active_ptr ? clamp_count(active_ptr, rows) : rows;
     int row = blockIdx.x * blockDim.x + threadIdx.x;
     DownsampledKey key_of{coords, sx, sy, sz};
@@ -236,7 +274,7 @@ __global__ void compact_winners_kernel(
         win = table_find(table, mask, key, key_of) == row;
     }
     int total;
-    int pos = block_exclusive_scan(win, total) + block_offsets[blockIdx.x];
+    int pos = block_exclusive_scan(win, total) + before;
     if (win) {
         if (pos < out_capacity) {
             store_coord(out_coords, pos, key);
@@ -949,7 +987,7 @@ __global__ void target_transposed_count_kernel(
 __global__ void target_transposed_fill_kernel(
     const int32_t* target, const int32_t* target_active_ptr, int target_rows,
     int sx, int sy, int sz, int lox, int loy, int loz,
-    const int32_t* hit_rows, const int32_t* block_offsets, const int32_t* counts,
+    const int32_t* hit_rows, const int32_t* block_sums, int32_t* counts,
     int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
     int32_t* row_masks
 ) {
@@ -959,9 +997,15 @@ __global__ void target_transposed_fill_kernel(
     if (row < active) {
         in_row = hit_rows[row];
     }
+    // block_sums: the per-block hit counts of target_transposed_count_kernel
+    int before, edges;
+    block_prefix_of(block_sums, gridDim.x, blockIdx.x, before, edges);
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        counts[0] = edges;
+        counts[1] = active;
+    }
     int total;
-    int pos = block_exclusive_scan(in_row >= 0, total) + block_offsets[blockIdx.x];
-    int edges = __ldg(counts);
+    int pos = block_exclusive_scan(in_row >= 0, total) + before;
     if (row < active) {
         row_offsets[row] = pos;
         if (in_row >= 0) {
@@ -1671,11 +1715,8 @@ int lat_build_kernel_relation(
         mark_winners_kernel<<<nblocks, kBlockThreads, 0, stream>>>(
             coords, active_rows, rows, stride.x, stride.y, stride.z, table2, mask2, sums);
         LAT_LAUNCH_CHECK();
-        scan_blocks_kernel<<<1, kBlockThreads, 0, stream>>>(
-            sums, nblocks, out_count, nullptr, nullptr, 0, nullptr, 0, nullptr);
-        LAT_LAUNCH_CHECK();
         compact_winners_kernel<<<nblocks, kBlockThreads, 0, stream>>>(
-            coords, active_rows, rows, stride.x, stride.y, stride.z, table2, mask2, sums,
+            coords, active_rows, rows, stride.x, stride.y, stride.z, table2, mask2, sums, out_count,
             out_coords, rows, status);
         LAT_LAUNCH_CHECK();
     }
@@ -1919,9 +1960,6 @@ int lat_build_target_transposed_relation(
         coords, table.slots, table.mask, target_coords, target_active_rows, target_rows,
         stride.x, stride.y, stride.z, lox, loy, loz, hit_rows, sums);
     LAT_LAUNCH_CHECK();
-    scan_blocks_kernel<<<1, kBlockThreads, 0, stream>>>(
-        sums, nblocks, counts, counts + 1, target_active_rows, target_rows, nullptr, 0, nullptr);
-    LAT_LAUNCH_CHECK();
     target_transposed_fill_kernel<<<nblocks, kBlockThreads, 0, stream>>>(
         target_coords, target_active_rows, target_rows, stride.x, stride.y, stride.z, lox, loy,
         loz, hit_rows, sums, counts, in_rows, out_rows, kernel_ids, row_offsets, row_masks);
@@ -2085,12 +2123,9 @@ int lat_downsample_coords(
     mark_winners_kernel<<<nblocks, kBlockThreads, 0, stream>>>(
         coords, nullptr, rows, stride.x, stride.y, stride.z, table, mask, sums);
     LAT_LAUNCH_CHECK();
-    scan_blocks_kernel<<<1, kBlockThreads, 0, stream>>>(
-        sums, nblocks, count, nullptr, nullptr, 0, nullptr, 0, nullptr);
-    LAT_LAUNCH_CHECK();
     compact_winners_kernel<<<nblocks, kBlockThreads, 0, stream>>>(
-        coords, nullptr, rows, stride.x, stride.y, stride.z, table, mask, sums, out_coords, rows,
-        status);
+        coords, nullptr, rows, stride.x, stride.y, stride.z, table, mask, sums, count, out_coords,
+        rows, status);
     LAT_LAUNCH_CHECK();
     return LAT_OK;
 }

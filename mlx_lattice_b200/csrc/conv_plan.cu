@@ -22,6 +22,10 @@ namespace lat {
 
 namespace {
 
+// Up to this many tiles (1 M output rows) every block of the fill kernel sums the masks of
+// the tiles before it itself; above it a one-block scan runs first.
+constexpr int kSelfScanTiles = 4096;
+
 struct PlanBuildParams {
     const int32_t* in_rows;
     const int32_t* kernel_ids;
@@ -34,6 +38,7 @@ struct PlanBuildParams {
     int out_capacity;
     int kernel_count;
     int num_tiles;
+    int prescanned;         // 1: plan_scan_kernel has filled tile_info[].y and the closing entry
     int2* tile_info;
     int32_t* vectors;
     int32_t* status;
@@ -98,11 +103,60 @@ __global__ void __launch_bounds__(kPlanTileRows) plan_mask_kernel(PlanBuildParam
     }
 }
 
+// pass 1b, relations of more than kSelfScanTiles tiles only: exclusive scan of the vectors
+// per tile (one block); the entry after the last tile receives (tiles up to the last one
+// with a non-empty mask, vector total)
+__global__ void __launch_bounds__(1024) plan_scan_kernel(int2* tile_info, int num_tiles) {
+    __shared__ int warp_totals[32];
+    __shared__ int carry;
+    __shared__ int active_tiles;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        carry = 0;
+        active_tiles = 0;
+    }
+    __syncthreads();
+    for (int first = 0; first < num_tiles; first += 1024) {
+        const int tile = first + threadIdx.x;
+        int2 info = make_int2(0, 0);
+        if (tile < num_tiles) {
+            info = tile_info[tile];
+        }
+        int wtotal;
+        const int prefix = warp_exclusive_scan(__popc(static_cast<uint32_t>(info.x)), wtotal);
+        if (lane == 0) {
+            warp_totals[warp] = wtotal;
+        }
+        __syncthreads();
+        int before = carry;
+        for (int w = 0; w < warp; ++w) {
+            before += warp_totals[w];
+        }
+        if (tile < num_tiles) {
+            tile_info[tile] = make_int2(info.x, before + prefix);
+            if (info.x != 0) {
+                atomicMax(&active_tiles, tile + 1);
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 1023) {
+            carry = before + prefix + __popc(static_cast<uint32_t>(info.x));
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        tile_info[num_tiles] = make_int2(active_tiles, carry);
+    }
+}
+
 // pass 2: the row vectors. A block first finds where its tile's vectors start: the number
-// of offsets the tiles before it use (it adds up their masks' population counts itself, a
-// few KB from L2, rather than wait for a one-block scan kernel), and records it in
-// tile_info[tile].y for the convolution; the last tile also writes the closing entry
-// (tiles up to the last one with a non-empty mask, vector total). Thread t owns vector slot
+// of offsets the tiles before it use. Up to kSelfScanTiles tiles it adds up their masks'
+// population counts itself (a few KB from L2, rather than wait for a one-block scan kernel),
+// records the sum in tile_info[tile].y for the convolution, and the last tile also writes
+// the closing entry (tiles up to the last one with a non-empty mask, vector total); beyond
+// that size, where every block reading every mask before it would cost more than the scan,
+// plan_scan_kernel has left both in place. Thread t owns vector slot
 // t, that is tile row (t % 8) * 32 + t / 8: the lanes of a warp then write 32 consecutive
 // entries of a vector (one 128-byte line) instead of 32 entries that lie 32 bytes apart.
 __global__ void __launch_bounds__(kPlanTileRows) plan_fill_kernel(PlanBuildParams p) {
@@ -117,7 +171,7 @@ __global__ void __launch_bounds__(kPlanTileRows) plan_fill_kernel(PlanBuildParam
     const bool closing = tile == p.num_tiles - 1;
     int before = 0;
     int last_used = 0;   // one past the last tile with a non-empty mask (closing block only)
-    for (int t = threadIdx.x; t < tile; t += kPlanTileRows) {
+    for (int t = threadIdx.x; t < tile && !p.prescanned; t += kPlanTileRows) {
         const uint32_t m = static_cast<uint32_t>(__ldg(&p.tile_info[t].x));
         before += __popc(m);
         last_used = m != 0 ? t + 1 : last_used;
@@ -139,7 +193,9 @@ __global__ void __launch_bounds__(kPlanTileRows) plan_fill_kernel(PlanBuildParam
         before += warp_before[w];
         last_used = max(last_used, warp_last[w]);
     }
-    if (threadIdx.x == 0) {
+    if (p.prescanned) {
+        before = p.tile_info[tile].y;
+    } else if (threadIdx.x == 0) {
         p.tile_info[tile].y = before;
         if (closing) {
             p.tile_info[p.num_tiles] = make_int2(mask != 0 ? p.num_tiles : last_used, before + present);
@@ -259,11 +315,16 @@ int lat_build_conv_plan(
     p.out_capacity = out_capacity;
     p.kernel_count = kernel_count;
     p.num_tiles = plan_tiles(out_capacity);
+    p.prescanned = p.num_tiles > kSelfScanTiles ? 1 : 0;
     p.tile_info = static_cast<int2*>(plan);
     p.vectors = reinterpret_cast<int32_t*>(static_cast<char*>(plan) + plan_info_bytes(p.num_tiles));
     p.status = status;
     plan_mask_kernel<<<p.num_tiles, kPlanTileRows, 0, stream>>>(p);
     LAT_LAUNCH_CHECK();
+    if (p.prescanned) {
+        plan_scan_kernel<<<1, 1024, 0, stream>>>(p.tile_info, p.num_tiles);
+        LAT_LAUNCH_CHECK();
+    }
     plan_fill_kernel<<<p.num_tiles, kPlanTileRows, 0, stream>>>(p);
     LAT_LAUNCH_CHECK();
     return LAT_OK;

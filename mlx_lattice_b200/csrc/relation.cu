@@ -152,6 +152,11 @@ __device__ __forceinline__ int block_exclusive_scan(int value, int& block_total)
     return out;
 }
 
+// Consumers of per-block totals add them up themselves up to this many blocks (1 M rows);
+// above it scan_blocks_kernel runs first, because every block reading every total before it
+// grows with the square of the block count.
+constexpr int kSelfScanBlocks = 4096;
+
 // What a scan over the per-block totals would give block `block`: the sum of the totals of
 // the blocks before it, and the sum of all of them. Every block of a consumer kernel adds
 // them up itself (a few KB from L2) instead of waiting for a one-block scan kernel between
@@ -256,13 +261,18 @@ __global__ void scan_blocks_kernel(
 // per-block winner counts of mark_winners_kernel, *count_out receives their total
 __global__ void compact_winners_kernel(
     const int32_t* coords, const int32_t* active_ptr, int rows, int sx, int sy, int sz,
-    const Slot* table, uint32_t mask, const int32_t* block_sums, int32_t* count_out,
+    const Slot* table, uint32_t mask, const int32_t* block_sums, int prescanned, int32_t* count_out,
     int32_t* out_coords, int out_capacity, int32_t* status
 ) {
+    // prescanned: scan_blocks_kernel has turned block_sums into offsets and written the total
     int before, all;
-    block_prefix_of(block_sums, gridDim.x, blockIdx.x, before, all);
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
-        *count_out = all;
+    if (prescanned) {
+        before = block_sums[blockIdx.x];
+    } else {
+        block_prefix_of(block_sums, gridDim.x, blockIdx.x, before, all);
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+            *count_out = all;
+        }
     }
     int active = active_ptr ? clamp_count(active_ptr, rows) : rows;
     int row = blockIdx.x * blockDim.x + threadIdx.x;
@@ -987,7 +997,7 @@ __global__ void target_transposed_count_kernel(
 __global__ void target_transposed_fill_kernel(
     const int32_t* target, const int32_t* target_active_ptr, int target_rows,
     int sx, int sy, int sz, int lox, int loy, int loz,
-    const int32_t* hit_rows, const int32_t* block_sums, int32_t* counts,
+    const int32_t* hit_rows, const int32_t* block_sums, int prescanned, int32_t* counts,
     int32_t* in_rows, int32_t* out_rows, int32_t* kernel_ids, int32_t* row_offsets,
     int32_t* row_masks
 ) {
@@ -997,12 +1007,18 @@ __global__ void target_transposed_fill_kernel(
     if (row < active) {
         in_row = hit_rows[row];
     }
-    // block_sums: the per-block hit counts of target_transposed_count_kernel
+    // block_sums: the per-block hit counts of target_transposed_count_kernel, or (prescanned)
+    // what scan_blocks_kernel made of them, with the counts already written
     int before, edges;
-    block_prefix_of(block_sums, gridDim.x, blockIdx.x, before, edges);
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
-        counts[0] = edges;
-        counts[1] = active;
+    if (prescanned) {
+        before = block_sums[blockIdx.x];
+        edges = counts[0];
+    } else {
+        block_prefix_of(block_sums, gridDim.x, blockIdx.x, before, edges);
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+            counts[0] = edges;
+            counts[1] = active;
+        }
     }
     int total;
     int pos = block_exclusive_scan(in_row >= 0, total) + before;
@@ -1715,9 +1731,15 @@ int lat_build_kernel_relation(
         mark_winners_kernel<<<nblocks, kBlockThreads, 0, stream>>>(
             coords, active_rows, rows, stride.x, stride.y, stride.z, table2, mask2, sums);
         LAT_LAUNCH_CHECK();
+        const int prescanned = nblocks > kSelfScanBlocks ? 1 : 0;
+        if (prescanned) {
+            scan_blocks_kernel<<<1, kBlockThreads, 0, stream>>>(
+                sums, nblocks, out_count, nullptr, nullptr, 0, nullptr, 0, nullptr);
+            LAT_LAUNCH_CHECK();
+        }
         compact_winners_kernel<<<nblocks, kBlockThreads, 0, stream>>>(
-            coords, active_rows, rows, stride.x, stride.y, stride.z, table2, mask2, sums, out_count,
-            out_coords, rows, status);
+            coords, active_rows, rows, stride.x, stride.y, stride.z, table2, mask2, sums, prescanned,
+            out_count, out_coords, rows, status);
         LAT_LAUNCH_CHECK();
     }
     return run_map(ws, coords, table, out_coords, out_count, rows, rows, geo, stride, padding,
@@ -1960,9 +1982,15 @@ int lat_build_target_transposed_relation(
         coords, table.slots, table.mask, target_coords, target_active_rows, target_rows,
         stride.x, stride.y, stride.z, lox, loy, loz, hit_rows, sums);
     LAT_LAUNCH_CHECK();
+    const int prescanned = nblocks > kSelfScanBlocks ? 1 : 0;
+    if (prescanned) {
+        scan_blocks_kernel<<<1, kBlockThreads, 0, stream>>>(
+            sums, nblocks, counts, counts + 1, target_active_rows, target_rows, nullptr, 0, nullptr);
+        LAT_LAUNCH_CHECK();
+    }
     target_transposed_fill_kernel<<<nblocks, kBlockThreads, 0, stream>>>(
         target_coords, target_active_rows, target_rows, stride.x, stride.y, stride.z, lox, loy,
-        loz, hit_rows, sums, counts, in_rows, out_rows, kernel_ids, row_offsets, row_masks);
+        loz, hit_rows, sums, prescanned, counts, in_rows, out_rows, kernel_ids, row_offsets, row_masks);
     LAT_LAUNCH_CHECK();
     return LAT_OK;
 }
@@ -2123,9 +2151,15 @@ int lat_downsample_coords(
     mark_winners_kernel<<<nblocks, kBlockThreads, 0, stream>>>(
         coords, nullptr, rows, stride.x, stride.y, stride.z, table, mask, sums);
     LAT_LAUNCH_CHECK();
+    const int prescanned = nblocks > kSelfScanBlocks ? 1 : 0;
+    if (prescanned) {
+        scan_blocks_kernel<<<1, kBlockThreads, 0, stream>>>(
+            sums, nblocks, count, nullptr, nullptr, 0, nullptr, 0, nullptr);
+        LAT_LAUNCH_CHECK();
+    }
     compact_winners_kernel<<<nblocks, kBlockThreads, 0, stream>>>(
-        coords, nullptr, rows, stride.x, stride.y, stride.z, table, mask, sums, count, out_coords,
-        rows, status);
+        coords, nullptr, rows, stride.x, stride.y, stride.z, table, mask, sums, prescanned, count,
+        out_coords, rows, status);
     LAT_LAUNCH_CHECK();
     return LAT_OK;
 }

@@ -110,6 +110,57 @@ def test_config2_strided_map_one_million_coords(cuda):
     assert total == edges
 
 
+def test_inputs_beyond_the_self_scan_size(cuda):
+    """1,250,000 rows: more than 4096 blocks / tiles, where the strided support, the decoder
+    map and the gather plan run their one-block scan kernels instead of letting every block
+    add up the totals before it. Output support and decoder map against torch constructions,
+    the plan through a convolution that must equal the plan-free one bit for bit."""
+    from mlx_lattice_b200 import _ext
+
+    coords = torch.from_numpy(synthetic.lidar_batch(2, 10, 125000)).to(cuda)
+    n = coords.shape[0]
+    assert n > 4096 * 256
+    active = torch.tensor([n], dtype=torch.int32, device=cuda)
+    base, _, _ = _ext.build_kernel_relation_base(coords, active, 2, 2, 0, 1)
+    in_rows, out_rows, kernel_ids, row_offsets, out_coords, counts = base
+    _ext.check_status(cuda)
+    edges, n_out = counts.tolist()
+    cells = coords.clone()
+    cells[:, 1:] = torch.div(coords[:, 1:], 2, rounding_mode='floor')
+    keys = _keys(cells)
+    uniq, inverse = torch.unique(keys, return_inverse=True)
+    first = torch.full((uniq.shape[0],), n, dtype=torch.long, device=cuda)
+    first.scatter_reduce_(0, inverse, torch.arange(n, device=cuda), reduce='amin')
+    order = torch.sort(first).values
+    assert n_out == uniq.shape[0] and edges == n          # every voxel has exactly one parent
+    assert torch.equal(out_coords[:n_out], cells[order])
+    assert not out_coords[n_out:].any()
+    # decoder map: fine row -> (parent row, child offset)
+    coarse = out_coords[:n_out].contiguous()
+    coarse_active = torch.tensor([n_out], dtype=torch.int32, device=cuda)
+    up = _ext.build_target_transposed_relation_base(coarse, coarse_active, coords, active, 2)
+    up_in, up_out, up_k, up_offsets, _, up_counts = up
+    _ext.check_status(cuda)
+    assert up_counts.tolist() == [n, n]
+    assert torch.equal(up_out.long(), torch.arange(n, device=cuda))
+    assert torch.equal(up_offsets.long(), torch.arange(n + 1, device=cuda))
+    assert torch.equal(up_in.long(), _first_row_lookup(coarse, cells))
+    child = coords[:, 1:] - 2 * cells[:, 1:]
+    assert torch.equal(up_k.long(), ((child[:, 0] * 2 + child[:, 1]) * 2 + child[:, 2]).long())
+    # gather plan with more than 4096 tiles
+    rng = np.random.default_rng(8)
+    feats = torch.from_numpy(rng.normal(size=(n, 32)).astype(np.float16)).to(cuda)
+    weights = torch.from_numpy((rng.normal(size=(8, 32, 32)) * 0.1).astype(np.float16)).to(cuda)
+    plan = _ext.build_conv_plan(in_rows, kernel_ids, counts, row_offsets, n, n, 8)
+    with_plan = _ext.sparse_conv_features(feats, weights, in_rows, out_rows, kernel_ids, counts, row_offsets,
+                                          out_capacity=n, n_kernels=8, plan=plan)
+    without = _ext.sparse_conv_features(feats, weights, in_rows, out_rows, kernel_ids, counts, row_offsets,
+                                        out_capacity=n, n_kernels=8)
+    _ext.check_status(cuda)
+    assert torch.equal(with_plan, without)
+    assert not with_plan[n_out:].any()
+
+
 def _layer(cuda, c_in, c_out, seed):
     from mlx_lattice_b200.core import quantize_weight
 

@@ -915,9 +915,18 @@ def build_conv_plan(in_rows, kernel_ids, counts, row_offsets, in_capacity: int,
     in_rows, kernel_ids = _i32(in_rows, 'in_rows'), _i32(kernel_ids, 'kernel_ids')
     counts, row_offsets = _i32(counts, 'counts'), _i32(row_offsets, 'row_offsets')
     device = in_rows.device
+    out_capacity = int(out_capacity)
+    if kernel_ids.shape != in_rows.shape or any(t.device != device for t in (kernel_ids, counts, row_offsets)):
+        raise ValueError('in_rows and kernel_ids must have the same length, on one device.')
+    if row_offsets.numel() != out_capacity + 1 or counts.numel() != 2:
+        raise ValueError('row_offsets must have length out_capacity + 1 and counts two entries.')
+    if row_order is not None:
+        row_order = _i32(row_order, 'row_order')
+        if row_order.device != device or row_order.numel() != out_capacity:
+            raise ValueError('row_order must hold one int32 entry per output row, on the relation device.')
     if row_masks is not None:
         row_masks = _i32(row_masks, 'row_masks')
-        if row_masks.device != device or row_masks.numel() != int(out_capacity):
+        if row_masks.device != device or row_masks.numel() != out_capacity:
             raise ValueError('row_masks must hold one int32 word per output row, on the relation device.')
     lib = _lib()
     plan = torch.empty(max(int(lib.lat_conv_plan_bytes(out_capacity, kernel_count)), 256),
@@ -925,7 +934,7 @@ def build_conv_plan(in_rows, kernel_ids, counts, row_offsets, in_capacity: int,
     with torch.cuda.device(device):
         check(lib.lat_build_conv_plan(
             _ptr(in_rows), _ptr(kernel_ids), int(in_rows.shape[0]), _ptr(counts),
-            _ptr(row_offsets), int(in_capacity), int(out_capacity), int(kernel_count),
+            _ptr(row_offsets), int(in_capacity), out_capacity, int(kernel_count),
             _ptr(row_order), _ptr(row_masks), _ptr(plan), plan.numel(), _ptr(status_word(device)),
             _stream(),
         ))

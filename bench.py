@@ -411,7 +411,7 @@ def front_end_benchmark(device, steps: int, peaks: dict) -> dict:
 
 
 def config_figures(device, steps: int, peaks: dict, flush) -> dict:
-    """Event-timed figures of the other BASELINE configurations (the headline is config 4):
+    """Event-timed figures of the other benchmark configurations (the headline is configuration 4):
     config 0 (fp32 submanifold conv, 50,000 voxels, 32->32), config 1 (int4 kernel-2 stride-2
     conv 64->128 over 4 x 200,000 voxels) and config 3 (int8 block over 16 x 60,000 voxels),
     kernel maps prebuilt (the map build is config 2's figure)."""

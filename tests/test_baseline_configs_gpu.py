@@ -1,4 +1,4 @@
-"""The BASELINE configurations at their stated generators and sizes, GPU path (through
+"""The five benchmark configurations at their stated generators and sizes, GPU path (through
 the C ABI) against the oracle: config 0 exactly, both 1,000,000-coordinate kernel maps
 of config 2 exactly, one whole cloud of config 1. Configs 3 and 4 (one whole cloud each)
 are the full-size cases of tests/test_network_gpu.py. Bars: kernel maps bit-exact in

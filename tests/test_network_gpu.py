@@ -20,7 +20,7 @@ def _max_rel_err(got, want):
 @pytest.mark.parametrize('clouds,per', [(2, 5000), (1, 120000)],
                          ids=['two_small_clouds', 'config4_one_whole_cloud'])
 def test_minkunet_int4_matches_reference_composition(cuda, oracle, clouds, per):
-    """BASELINE config 4: the MinkUNet-style int4 network against the reference composition
+    """Benchmark configuration 4: the MinkUNet-style int4 network against the reference composition
     evaluated by the oracle; the second case is one cloud of the benchmark batch at its
     full size (120,000 voxels; the clouds of a batch are independent)."""
     from mlx_lattice_b200 import _ext, workloads
@@ -49,7 +49,7 @@ def test_minkunet_int4_matches_reference_composition(cuda, oracle, clouds, per):
 @pytest.mark.parametrize('clouds,per', [(3, 4000), (1, 60000)],
                          ids=['three_small_clouds', 'config3_one_whole_cloud'])
 def test_mixed_int8_block_config3_shape(cuda, oracle, restatement, clouds, per):
-    """BASELINE config 3: SubmConv3d int8 96->96, BatchNorm, ReLU, max_pool3d(k3, s2),
+    """Benchmark configuration 3: SubmConv3d int8 96->96, BatchNorm, ReLU, max_pool3d(k3, s2),
     QuantizedLinear int8 96->192, global_avg_pool, with the dtype plumbing the reference
     allows (pooling in float32); the second case is one cloud at its full size."""
     from mlx_lattice_b200 import _ext, nn, ops

@@ -4,6 +4,13 @@
 // For every tile the plan holds
 //   tile_info[tile] = (mask, base): the kernel offsets any row of the tile uses, and the
 //                     index of the tile's first row vector;
+//   tile_order:       the tiles by falling number of used offsets (equal counts in tile
+//                     order, tiles that use none last). A tile's cost in the convolution is
+//                     its number of used offsets, and with mask-sorted rows that number
+//                     varies from 1 to K along the tiles: handing the tiles out round-robin
+//                     in their natural order left the busiest CTA 19-39 % above the mean on
+//                     LiDAR-like supports; the serpentine over the sorted order (plan_position)
+//                     leaves it 2-5 % above;
 //   one row vector per used offset, in ascending offset order: the input row of each of
 //   the 256 tile rows at that offset, -1 where the row has no neighbour there.
 // The convolution kernel then streams these vectors instead of walking the CSR rows of
@@ -40,6 +47,7 @@ struct PlanBuildParams {
     int num_tiles;
     int prescanned;         // 1: plan_scan_kernel has filled tile_info[].y and the closing entry
     int2* tile_info;
+    int32_t* tile_order;
     int32_t* vectors;
     int32_t* status;
 };
@@ -104,17 +112,14 @@ __global__ void __launch_bounds__(kPlanTileRows) plan_mask_kernel(PlanBuildParam
 }
 
 // pass 1b, relations of more than kSelfScanTiles tiles only: exclusive scan of the vectors
-// per tile (one block); the entry after the last tile receives (tiles up to the last one
-// with a non-empty mask, vector total)
+// per tile (one block); the entry after the last tile receives the vector total
 __global__ void __launch_bounds__(1024) plan_scan_kernel(int2* tile_info, int num_tiles) {
     __shared__ int warp_totals[32];
     __shared__ int carry;
-    __shared__ int active_tiles;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     if (threadIdx.x == 0) {
         carry = 0;
-        active_tiles = 0;
     }
     __syncthreads();
     for (int first = 0; first < num_tiles; first += 1024) {
@@ -135,9 +140,6 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(int2* tile_info, int nu
         }
         if (tile < num_tiles) {
             tile_info[tile] = make_int2(info.x, before + prefix);
-            if (info.x != 0) {
-                atomicMax(&active_tiles, tile + 1);
-            }
         }
         __syncthreads();
         if (threadIdx.x == 1023) {
@@ -146,7 +148,65 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(int2* tile_info, int nu
         __syncthreads();
     }
     if (threadIdx.x == 0) {
-        tile_info[num_tiles] = make_int2(active_tiles, carry);
+        tile_info[num_tiles].y = carry;   // .x (tiles in use) comes from plan_order_kernel
+    }
+}
+
+// pass 1c: tile_order, a stable counting sort of the tiles by 32 - popcount(mask) (one block:
+// its 32 warps take contiguous runs of tiles, count per warp, scan over (key, warp), place),
+// and the number of tiles whose mask is not empty into the closing entry.
+constexpr int kOrderKeys = 33;
+
+__global__ void __launch_bounds__(1024) plan_order_kernel(
+    const int2* tile_info, int num_tiles, int32_t* tile_order, int2* closing
+) {
+    __shared__ int start[kOrderKeys][32];   // counts, then where (key, warp) starts
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < kOrderKeys * 32; i += 1024) {
+        (&start[0][0])[i] = 0;
+    }
+    __syncthreads();
+    const int run = (num_tiles + 31) / 32;
+    const int first = warp * run;
+    const int last = min(first + run, num_tiles);
+    for (int t0 = first; t0 < last; t0 += 32) {
+        const int t = t0 + lane;
+        const int key = t < last ? 32 - __popc(static_cast<uint32_t>(__ldg(&tile_info[t].x))) : -1 - lane;
+        const unsigned peers = __match_any_sync(0xffffffffu, key);
+        if (key >= 0 && (peers & lanemask_lt()) == 0) {
+            start[key][warp] += __popc(peers);
+        }
+        __syncwarp();
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int carry = 0;
+        for (int key = 0; key < kOrderKeys; ++key) {
+            int total;
+            const int count = start[key][lane];
+            const int before = warp_exclusive_scan(count, total);
+            start[key][lane] = carry + before;
+            if (key == kOrderKeys - 1 && lane == 0) {
+                closing->x = carry;   // tiles with at least one offset: everything before key 32
+            }
+            carry += total;
+        }
+    }
+    __syncthreads();
+    for (int t0 = first; t0 < last; t0 += 32) {
+        const int t = t0 + lane;
+        const int key = t < last ? 32 - __popc(static_cast<uint32_t>(__ldg(&tile_info[t].x))) : -1 - lane;
+        const unsigned peers = __match_any_sync(0xffffffffu, key);
+        const int rank = __popc(peers & lanemask_lt());
+        if (key >= 0) {
+            tile_order[start[key][warp] + rank] = t;
+        }
+        __syncwarp();
+        if (key >= 0 && rank == 0) {
+            start[key][warp] += __popc(peers);
+        }
+        __syncwarp();
     }
 }
 
@@ -154,14 +214,13 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(int2* tile_info, int nu
 // of offsets the tiles before it use. Up to kSelfScanTiles tiles it adds up their masks'
 // population counts itself (a few KB from L2, rather than wait for a one-block scan kernel),
 // records the sum in tile_info[tile].y for the convolution, and the last tile also writes
-// the closing entry (tiles up to the last one with a non-empty mask, vector total); beyond
-// that size, where every block reading every mask before it would cost more than the scan,
-// plan_scan_kernel has left both in place. Thread t owns vector slot
-// t, that is tile row (t % 8) * 32 + t / 8: the lanes of a warp then write 32 consecutive
-// entries of a vector (one 128-byte line) instead of 32 entries that lie 32 bytes apart.
+// the vector total into the closing entry; beyond that size, where every block reading
+// every mask before it would cost more than the scan, plan_scan_kernel has left both in
+// place. Thread t owns vector slot t, that is tile row (t % 8) * 32 + t / 8: the lanes of a
+// warp then write 32 consecutive entries of a vector (one 128-byte line) instead of 32
+// entries that lie 32 bytes apart.
 __global__ void __launch_bounds__(kPlanTileRows) plan_fill_kernel(PlanBuildParams p) {
     __shared__ int warp_before[kPlanTileRows / 32];
-    __shared__ int warp_last[kPlanTileRows / 32];
     const int n_out = clamp_count(p.counts + 1, p.out_capacity);
     const int edge_total = clamp_count(p.counts, p.edge_capacity);
     const int tile = blockIdx.x;
@@ -170,35 +229,25 @@ __global__ void __launch_bounds__(kPlanTileRows) plan_fill_kernel(PlanBuildParam
     // masks live in the .x words; the .y words are being written by the other blocks
     const bool closing = tile == p.num_tiles - 1;
     int before = 0;
-    int last_used = 0;   // one past the last tile with a non-empty mask (closing block only)
     for (int t = threadIdx.x; t < tile && !p.prescanned; t += kPlanTileRows) {
-        const uint32_t m = static_cast<uint32_t>(__ldg(&p.tile_info[t].x));
-        before += __popc(m);
-        last_used = m != 0 ? t + 1 : last_used;
+        before += __popc(static_cast<uint32_t>(__ldg(&p.tile_info[t].x)));
     }
     before = warp_sum(before);
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) {
-        last_used = max(last_used, __shfl_xor_sync(0xffffffffu, last_used, d));
-    }
     if ((threadIdx.x & 31) == 0) {
         warp_before[threadIdx.x >> 5] = before;
-        warp_last[threadIdx.x >> 5] = last_used;
     }
     __syncthreads();
     before = 0;
-    last_used = 0;
 #pragma unroll
     for (int w = 0; w < kPlanTileRows / 32; ++w) {
         before += warp_before[w];
-        last_used = max(last_used, warp_last[w]);
     }
     if (p.prescanned) {
         before = p.tile_info[tile].y;
     } else if (threadIdx.x == 0) {
         p.tile_info[tile].y = before;
         if (closing) {
-            p.tile_info[p.num_tiles] = make_int2(mask != 0 ? p.num_tiles : last_used, before + present);
+            p.tile_info[p.num_tiles].y = before + present;   // .x comes from plan_order_kernel
         }
     }
     const int2 info = make_int2(static_cast<int>(mask), before);
@@ -240,12 +289,13 @@ __global__ void __launch_bounds__(kPlanTileRows) plan_fill_kernel(PlanBuildParam
 // the plan of the identity relation (output row i reads input row i at the only offset):
 // every tile uses offset 0 and its row vector is the tile's own rows
 __global__ void __launch_bounds__(kPlanTileRows) identity_plan_kernel(int rows, int num_tiles, int2* tile_info,
-                                                                    int32_t* vectors) {
+                                                                    int32_t* tile_order, int32_t* vectors) {
     const int tile = blockIdx.x;
     const int row = tile * kPlanTileRows + threadIdx.x;
     vectors[static_cast<size_t>(tile) * kPlanTileRows + plan_slot(threadIdx.x)] = row < rows ? row : -1;
     if (threadIdx.x == 0) {
         tile_info[tile] = make_int2(1, tile);
+        tile_order[tile] = tile;
         if (tile == 0) {
             tile_info[num_tiles] = make_int2(num_tiles, num_tiles);
         }
@@ -262,7 +312,7 @@ extern "C" {
 
 size_t lat_conv_plan_bytes(int32_t out_capacity, int32_t kernel_count) {
     const size_t tiles = static_cast<size_t>(plan_tiles(out_capacity));
-    return plan_info_bytes(static_cast<int>(tiles)) +
+    return plan_vectors_offset(static_cast<int>(tiles)) +
            tiles * static_cast<size_t>(std::max(kernel_count, 1)) * kPlanTileRows * sizeof(int32_t);
 }
 
@@ -277,7 +327,8 @@ int lat_build_identity_conv_plan(int32_t rows, void* plan, size_t plan_bytes, vo
     const int tiles = plan_tiles(rows);
     identity_plan_kernel<<<tiles, kPlanTileRows, 0, as_stream(stream_ptr)>>>(
         rows, tiles, static_cast<int2*>(plan),
-        reinterpret_cast<int32_t*>(static_cast<char*>(plan) + plan_info_bytes(tiles)));
+        reinterpret_cast<int32_t*>(static_cast<char*>(plan) + plan_info_bytes(tiles)),
+        reinterpret_cast<int32_t*>(static_cast<char*>(plan) + plan_vectors_offset(tiles)));
     LAT_LAUNCH_CHECK();
     return LAT_OK;
 }
@@ -317,9 +368,13 @@ int lat_build_conv_plan(
     p.num_tiles = plan_tiles(out_capacity);
     p.prescanned = p.num_tiles > kSelfScanTiles ? 1 : 0;
     p.tile_info = static_cast<int2*>(plan);
-    p.vectors = reinterpret_cast<int32_t*>(static_cast<char*>(plan) + plan_info_bytes(p.num_tiles));
+    p.tile_order = reinterpret_cast<int32_t*>(static_cast<char*>(plan) + plan_info_bytes(p.num_tiles));
+    p.vectors = reinterpret_cast<int32_t*>(static_cast<char*>(plan) + plan_vectors_offset(p.num_tiles));
     p.status = status;
     plan_mask_kernel<<<p.num_tiles, kPlanTileRows, 0, stream>>>(p);
+    LAT_LAUNCH_CHECK();
+    plan_order_kernel<<<1, 1024, 0, stream>>>(p.tile_info, p.num_tiles, p.tile_order,
+                                              p.tile_info + p.num_tiles);
     LAT_LAUNCH_CHECK();
     if (p.prescanned) {
         plan_scan_kernel<<<1, 1024, 0, stream>>>(p.tile_info, p.num_tiles);

@@ -64,7 +64,8 @@ struct PlanConvParams {
     const __half* weights;
     long long w_k_bytes;
     long long w_co_bytes;
-    const int2* tile_info;     // [num_tiles + 1]; the last entry holds (active tiles, vectors)
+    const int2* tile_info;     // [num_tiles + 1]; the last entry holds (tiles in use, vectors)
+    const int32_t* tile_order; // [num_tiles]: tiles by falling number of used offsets
     const int32_t* vectors;
     const int32_t* row_order;
     int out_capacity;
@@ -113,8 +114,16 @@ __device__ __forceinline__ int32_t make_header(int k, int present) { return k | 
 __device__ __forceinline__ int header_k(int32_t h) { return h & 31; }
 __device__ __forceinline__ int header_present(int32_t h) { return (h >> 8) & 63; }
 
-__device__ __forceinline__ int2 load_info(const PlanConvParams& p, int tile, int active) {
-    return tile < active ? __ldg(p.tile_info + tile) : make_int2(0, 0);
+// The turn-th tile of CTA `cta`: the CTAs walk the plan's tile order (tiles by falling cost)
+// in a serpentine, so that every pair of rounds hands each of them about the same work.
+// -1 at and beyond position `limit`; positions grow with the turn.
+__device__ __forceinline__ int tile_of_turn(const PlanConvParams& p, int turn, int cta, int grid, int limit) {
+    const int position = plan_position(turn, cta, grid);
+    return position < limit ? __ldg(p.tile_order + position) : -1;
+}
+
+__device__ __forceinline__ int2 load_info(const PlanConvParams& p, int tile) {
+    return tile >= 0 ? __ldg(p.tile_info + tile) : make_int2(0, 0);
 }
 
 // Rows of a tile none of whose rows has an edge: zeros plus bias. Warp `w` (0-7) of a role
@@ -159,9 +168,9 @@ __device__ __forceinline__ void store_f16x16(__half* dst, const uint4& lo, const
                  : "memory");
 }
 
-// the tiles past the last one with an edge are shared between the producer warps (which
-// run out of work first) and the epilogue warps: even and odd rounds of the tile loop
-__device__ __forceinline__ bool producers_fill(int tile, int grid) { return ((tile / grid) & 1) == 0; }
+// the tiles without an edge (the end of the tile order) are shared between the producer
+// warps (which run out of work first) and the epilogue warps: even and odd rounds over them
+__device__ __forceinline__ bool producers_fill(int index, int grid) { return ((index / grid) & 1) == 0; }
 
 // kEpilogueWarps = 8: one CTA per SM, a warp per 32-row quarter of each 128-row half (C_out
 // above 128, where one tile's accumulators fill the tensor memory). kEpilogueWarps = 4: TWO
@@ -221,8 +230,10 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = ctl.tmem_base;
-    // tiles at and beyond `active` use no kernel offset at all
-    const int active = min(max(__ldg(&p.tile_info[p.num_tiles].x), 0), p.num_tiles);
+    // positions [0, used) of the tile order hold the tiles that use a kernel offset, the
+    // rest use none at all
+    const int used = min(max(__ldg(&p.tile_info[p.num_tiles].x), 0), p.num_tiles);
+    const int idle = p.num_tiles - used;
 
     if (warp < 8) {
         // ======================= producers =======================
@@ -445,10 +456,9 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
             }
         }
         cp_async_wait<0>();
-        for (int tile = blockIdx.x + ((active - blockIdx.x + grid - 1) / grid) * grid;
-             tile < p.num_tiles; tile += grid) {
-            if (producers_fill(tile, grid)) {
-                fill_edgeless_rows(p, tile, warp, lane);
+        for (int index = blockIdx.x; index < idle; index += grid) {
+            if (producers_fill(index, grid)) {
+                fill_edgeless_rows(p, __ldg(p.tile_order + used + index), warp, lane);
             }
         }
     } else if (warp < kMmaWarp) {
@@ -458,62 +468,41 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
         const int first_half = kHalves == 1 ? ew >> 2 : 0;   // the 128-row halves this warp stores
         bool ok = true;
         int local_tile = 0;
-        // the output rows and the offset mask of a tile are fetched one tile ahead
+        // the output rows of a tile are fetched one tile ahead
         auto tile_output_row = [&](int tile, int half_tile) -> int {
             const int position = tile * kTileRows + half_tile * 128 + quarter * 32 + lane;
-            if (tile >= p.num_tiles || position >= p.out_capacity) {
+            if (tile < 0 || position >= p.out_capacity) {
                 return -1;
             }
             return p.row_order != nullptr ? __ldg(p.row_order + position) : position;
         };
+        int next_tile = tile_of_turn(p, 0, blockIdx.x, grid, used);
         int next_row[kHalves];
 #pragma unroll
         for (int h = 0; h < kHalves; ++h) {
-            next_row[h] = tile_output_row(blockIdx.x, first_half + h);
+            next_row[h] = tile_output_row(next_tile, first_half + h);
         }
-        int2 next_info = load_info(p, blockIdx.x, active);
-        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += grid, ++local_tile) {
+        for (int turn = 0; next_tile >= 0 && ok; ++turn, ++local_tile) {
+            const int tile = next_tile;
+            next_tile = tile_of_turn(p, turn + 1, blockIdx.x, grid, used);
             int rows[kHalves];
-            const int2 info = next_info;
 #pragma unroll
             for (int h = 0; h < kHalves; ++h) {
                 rows[h] = next_row[h];
-                next_row[h] = tile_output_row(tile + grid, first_half + h);
+                next_row[h] = tile_output_row(next_tile, first_half + h);
                 const int position = tile * kTileRows + (first_half + h) * 128 + quarter * 32 + lane;
                 if (rows[h] >= p.out_capacity || (rows[h] < 0 && position < p.out_capacity)) {
                     raise_status(p.status, LAT_STATUS_BAD_INDEX);
                     rows[h] = -1;
                 }
             }
-            next_info = load_info(p, tile + grid, active);
-            bool computed = false;
-            int a = 0;
-            if (tile < active) {
-                a = local_tile % p.acc_stages;
-                const uint32_t parity = (local_tile / p.acc_stages) & 1;
-                if (!wait_warp(&ctl.acc_full[a], parity)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                computed = info.x != 0;
+            const int a = local_tile % p.acc_stages;
+            const uint32_t parity = (local_tile / p.acc_stages) & 1;
+            if (!wait_warp(&ctl.acc_full[a], parity)) {
+                ok = false;
+                break;
             }
-            if (!computed) {
-                if (tile < active || !producers_fill(tile, grid)) {
-#pragma unroll
-                    for (int h = 0; h < kHalves; ++h) {
-                        fill_edgeless_rows(p, tile, (first_half + h) * 4 + quarter, lane);
-                    }
-                }
-                if (tile < active) {
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(&ctl.acc_empty[a]);
-                    }
-                }
-                continue;
-            }
+            tc_fence_after();
 #pragma unroll
             for (int h = 0; h < kHalves; ++h) {
                 const int half_tile = first_half + h;
@@ -566,6 +555,16 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                 mbar_arrive(&ctl.acc_empty[a]);
             }
         }
+        // this role's share of the tiles without an edge
+        for (int index = blockIdx.x; index < idle && ok; index += grid) {
+            if (!producers_fill(index, grid)) {
+                const int tile = __ldg(p.tile_order + used + index);
+#pragma unroll
+                for (int h = 0; h < kHalves; ++h) {
+                    fill_edgeless_rows(p, tile, (first_half + h) * 4 + quarter, lane);
+                }
+            }
+        }
     } else if (warp == kMmaWarp) {
         // ======================= MMA issuer =======================
         // Lane 0 issues; the warp as a whole fetches the offset masks of the CTA's next 32
@@ -578,11 +577,12 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
         bool ok = true;
         Ring ring{0, 0u};
         int local_tile = 0;
-        int2 batch = load_info(p, blockIdx.x + lane * grid, active);
-        for (int first = blockIdx.x; first < active && ok; first += 32 * grid) {
-            const int2 mine = batch;
-            batch = load_info(p, first + (32 + lane) * grid, active);
-            for (int j = 0; j < 32 && first + j * grid < active && ok; ++j, ++local_tile) {
+        int2 batch = load_info(p, tile_of_turn(p, lane, blockIdx.x, grid, used));
+        for (int first = 0; ok; first += 32) {
+            const int2 mine = batch;   // masks of turns first .. first + 31 (0 past the end)
+            batch = load_info(p, tile_of_turn(p, first + 32 + lane, blockIdx.x, grid, used));
+            const int count = __popc(__ballot_sync(0xffffffffu, mine.x != 0));
+            for (int j = 0; j < count && ok; ++j, ++local_tile) {
                 const int mask = __shfl_sync(0xffffffffu, mine.x, j);
                 if (lane == 0) {
                     const int a = local_tile % p.acc_stages;
@@ -628,6 +628,9 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             }
+            if (count < 32) {
+                break;
+            }
         }
     } else if (warp == kLoaderWarp) {
         // ======================= row-vector loader =======================
@@ -651,11 +654,12 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
             vec.advance(p.vec_slots);
             return true;
         };
-        int2 batch = load_info(p, blockIdx.x + lane * grid, active);
-        for (int first = blockIdx.x; first < active && ok; first += 32 * grid) {
+        int2 batch = load_info(p, tile_of_turn(p, lane, blockIdx.x, grid, used));
+        for (int first = 0; ok; first += 32) {
             const int2 mine = batch;
-            batch = load_info(p, first + (32 + lane) * grid, active);
-            for (int j = 0; j < 32 && first + j * grid < active && ok; ++j) {
+            batch = load_info(p, tile_of_turn(p, first + 32 + lane, blockIdx.x, grid, used));
+            const int count = __popc(__ballot_sync(0xffffffffu, mine.x != 0));
+            for (int j = 0; j < count && ok; ++j) {
                 const int mask = __shfl_sync(0xffffffffu, mine.x, j);
                 const int vector0 = __shfl_sync(0xffffffffu, mine.y, j);
                 if (lane == 0) {
@@ -669,6 +673,9 @@ tc_conv_plan_kernel(PlanConvParams p, const __grid_constant__ CUtensorMap b_map)
                     }
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            }
+            if (count < 32) {
+                break;
             }
         }
         if (lane == 0 && ok) {
@@ -764,7 +771,8 @@ int run_tc_conv_plan(
     p.w_co_bytes = w_stride_co * 2;
     p.num_tiles = plan_tiles(out_capacity);
     p.tile_info = static_cast<const int2*>(plan);
-    p.vectors = reinterpret_cast<const int32_t*>(static_cast<const char*>(plan) + plan_info_bytes(p.num_tiles));
+    p.tile_order = reinterpret_cast<const int32_t*>(static_cast<const char*>(plan) + plan_info_bytes(p.num_tiles));
+    p.vectors = reinterpret_cast<const int32_t*>(static_cast<const char*>(plan) + plan_vectors_offset(p.num_tiles));
     LAT_REQUIRE(reinterpret_cast<uintptr_t>(p.vectors) % 16 == 0, "plan must be a 16-byte aligned device buffer.");
     p.row_order = row_order;
     p.out_capacity = out_capacity;

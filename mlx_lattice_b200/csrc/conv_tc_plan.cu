@@ -1,8 +1,11 @@
 // Tensor-core sparse convolution driven by a gather plan (conv_plan.cu): an output-stationary
 // implicit GEMM on tcgen05 -- 256-row tiles of output rows in the plan's row order, a unit =
 // (kernel offset used by the tile, 32-channel slice of C_in), two units per 64-wide K slab,
-// fp32 accumulators in TMEM, one deterministic store per output row. No role touches the
-// relation's CSR arrays and no thread waits for a copy of its own:
+// fp32 accumulators in TMEM, one deterministic store per output row. The persistent CTAs take
+// the tiles in the plan's tile order (tiles by falling number of used offsets) in a
+// serpentine, so that each of them gets about the same number of slabs; every role of a CTA
+// computes that sequence for itself. No role touches the relation's CSR arrays and no
+// thread waits for a copy of its own:
 //   warp 17    row-vector loader: streams the plan's row vectors of the CTA's tiles (one
 //              per tile and used kernel offset, 1 KB each) into a 16-slot shared-memory
 //              ring by bulk copies, in the order the producers consume them, so that no

@@ -322,7 +322,9 @@ int lat_dequantize_conv_weights(
  * implicit-GEMM view, native/features/coordinates/cpu/relations.cpp, prepares on the
  * host side). The output rows in `row_order` (natural order when NULL) are cut into
  * 256-row tiles; per tile the plan holds the mask of kernel offsets its rows use and,
- * per used offset, the input row of each tile row (-1 = none). Build it once per
+ * per used offset, the input row of each tile row (-1 = none), and it lists the tiles by
+ * falling number of used offsets, the order in which the convolution hands them to its
+ * thread blocks. Build it once per
  * relation after `row_order`, then pass `plan` together with the same `row_order` to
  * the convolutions over that relation. kernel_count <= 32. Optional `row_masks`
  * [out_capacity] (bit k = the row has an edge at offset k, as the kernel-map builders and

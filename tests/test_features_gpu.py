@@ -204,6 +204,55 @@ def test_gather_plan_from_row_masks(cuda, oracle, sphere):
                              _dev(masks[:-1], cuda))
 
 
+def test_gather_plan_layout(cuda, oracle, sphere):
+    """The plan buffer as the header describes it: per tile (mask, first vector), the closing
+    entry (tiles in use, vector total), the tile order (every tile once, by falling number
+    of used offsets, equal counts in tile order), and the row vectors in gather order."""
+    from mlx_lattice_b200 import _ext
+
+    coords, rel = sphere
+    n = coords.shape[0]
+    active = n - 300                                   # some tiles at the end use no offset
+    rel = oracle.build_submanifold_kernel_relation(coords, active)
+    r = _rel_dev(rel, cuda)
+    order = np.random.default_rng(21).permutation(n).astype(np.int32)
+    plan = _ext.build_conv_plan(r['in_rows'], r['kernel_ids'], r['counts'], r['row_offsets'], n, n, 27,
+                                _dev(order, cuda)).cpu().numpy()
+    _ext.check_status()
+    tiles = (n + 255) // 256
+    info_bytes = -(-(tiles + 1) * 8 // 256) * 256
+    order_bytes = -(-tiles * 4 // 256) * 256
+    info = plan[:(tiles + 1) * 8].view(np.int32).reshape(tiles + 1, 2)
+    tile_order = plan[info_bytes:info_bytes + tiles * 4].view(np.int32)
+    vectors = plan[info_bytes + order_bytes:].view(np.int32)
+    # expected masks from the relation
+    e = int(rel['counts'][0])
+    row_masks = np.zeros(n, np.int64)
+    np.bitwise_or.at(row_masks, rel['out_rows'][:e], np.int64(1) << rel['kernel_ids'][:e].astype(np.int64))
+    padded = np.zeros(tiles * 256, np.int64)
+    padded[:n] = row_masks[order]
+    masks = np.bitwise_or.reduce(padded.reshape(tiles, 256), axis=1)
+    counts = np.array([bin(int(m)).count('1') for m in masks])
+    assert np.array_equal(info[:tiles, 0].astype(np.int64), masks)
+    assert np.array_equal(info[:tiles, 1], np.concatenate([[0], np.cumsum(counts)[:-1]]))
+    assert info[tiles, 0] == int((counts > 0).sum()) and info[tiles, 1] == int(counts.sum())
+    assert np.array_equal(tile_order, np.argsort(-counts, kind='stable'))
+    # row vectors: tile row r sits at (r % 32) * 8 + r / 32
+    in_of = {}
+    for edge in range(e):
+        in_of[(int(rel['out_rows'][edge]), int(rel['kernel_ids'][edge]))] = int(rel['in_rows'][edge])
+    slot = lambda row: (row % 32) * 8 + row // 32
+    rng = np.random.default_rng(2)
+    for tile in rng.choice(tiles, size=6, replace=False):
+        used = [k for k in range(27) if (int(masks[tile]) >> k) & 1]
+        for o, k in enumerate(used):
+            vector = vectors[(info[tile, 1] + o) * 256:(info[tile, 1] + o + 1) * 256]
+            for row in range(0, 256, 7):
+                position = tile * 256 + row
+                want = in_of.get((int(order[position]), k), -1) if position < n else -1
+                assert vector[slot(row)] == want
+
+
 def test_gather_plan_strided_and_padding_rows(cuda, oracle, restatement):
     """k=2, s=2 relation whose output capacity exceeds the live rows: plan tiles beyond
     the live rows are empty and their output rows are zero."""
